@@ -1,0 +1,221 @@
+/* mok_b200: C-ABI of the B200-native MoE-layer hot path.
+ *
+ * Drop-in boundary for the `_C` extension of cursor/mixture-of-kittens: every
+ * entry point below replaces one function that the reference binds in
+ * csrc/bindings.cu:6-94 (the pybind11 module `_C`), with at::Tensor arguments
+ * flattened to raw device pointers + sizes.  No PyTorch type appears here.
+ *
+ * Conventions
+ *   - every function returns MOKB_OK (0) or a negative error code and leaves a
+ *     message retrievable with mokb_last_error() (thread-local);
+ *   - all pointers are device pointers on the current CUDA device unless the
+ *     name ends in `_host`; tensors are contiguous, row-major;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued, never
+ *     synchronised: no entry point blocks the host;
+ *   - "peer pointer lists" (`*_ptrs_host`) are host arrays of `ep_size` device
+ *     addresses, index = EP rank, as produced by a symmetric-memory rendezvous
+ *     (mok/functional.py:224 of the reference);
+ *   - the caller allocates every output (the reference's callee-allocates
+ *     convention, csrc/megakernel/forward.cuh:345-368, lives in the Python shim);
+ *   - `status` is a device int32 that kernels set to a MOKB_ST_* code instead of
+ *     trapping or spinning for ever (the reference traps on schedule overflow,
+ *     csrc/scheduler.cuh:86, and spins without bound, csrc/utils.cuh:274-277).
+ *     It is only ever written when something went wrong; the caller zeroes it.
+ */
+#ifndef MOK_B200_H
+#define MOK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOKB_OK 0
+#define MOKB_ERR_INVALID (-1)   /* bad argument */
+#define MOKB_ERR_CUDA (-2)      /* a CUDA runtime/driver call failed */
+#define MOKB_ERR_UNSUPPORTED (-3)
+
+#define MOKB_MAX_EP 64          /* EP sizes 1..64 (the reference: 1,4,8,16,32,64; mok/functional.py:156) */
+
+/* device status codes */
+#define MOKB_ST_OK 0
+#define MOKB_ST_SCHEDULE_OVERFLOW 1   /* padded rows exceed schedule_capacity */
+#define MOKB_ST_BARRIER_TIMEOUT 2     /* a peer never arrived at barrier_all */
+#define MOKB_ST_PIPELINE_TIMEOUT 3    /* an mbarrier wait inside a GEMM ran out */
+#define MOKB_ST_MACROBATCH_OVERFLOW 4 /* padded rows exceed macrobatch_size */
+
+const char* mokb_last_error(void);
+/* Compute capability major*10+minor of the current device, or a negative error. */
+int mokb_device_arch(void);
+int mokb_sm_count(void);
+/* sizeof() of {mokb_fwd_bf16_args, mokb_bwd_bf16_args, mokb_gemm_args}: lets a binding verify its struct layout. */
+int mokb_struct_sizes(int* out, int n);
+/* Number of kernels this library has launched in this process (all threads). */
+unsigned long long mokb_launch_count(void);
+
+/* ---- route all-gather: replaces `_C.all_gather_top_experts`
+ * (csrc/utils.cuh:191-249).  Copies this rank's [numel] int32 routes into slot
+ * `rank` of every peer's [ep_size, numel] buffer with plain peer stores. */
+int mokb_all_gather_top_experts(const int32_t* top_experts, const uint64_t* gather_buffer_ptrs_host,
+                                int ep_size, int rank, int64_t numel, void* stream);
+
+/* ---- device barrier over all EP ranks: replaces `_C.barrier_all`
+ * (csrc/utils.cuh:251-299).  `target` (device int32, local) grows by ep_size per
+ * call; each rank adds 1 to every rank's barrier word and waits, with a bounded
+ * spin, until its own word reaches the target. */
+int mokb_barrier_all(const uint64_t* barrier_ptrs_host, int ep_size, int rank, int32_t* target,
+                     int32_t* status, void* stream);
+/* How long a rank waits for its peers before giving up with MOKB_ST_BARRIER_TIMEOUT (default 10 s). */
+int mokb_set_barrier_timeout_ms(int ms);
+
+/* ---- routing schedule: replaces `_C.schedule` (csrc/scheduler.cuh:149-183).
+ * topk_all [ep_size, num_local_tokens, topk] int32 -> peer_rank [capacity],
+ * peer_token_idx [capacity], num_tokens [1], tokens_per_expert [num_local_experts].
+ * Padding rows get peer_rank = peer_token_idx = -1.  `scratch` must hold
+ * mokb_schedule_scratch_bytes() bytes; it needs no initialisation. */
+size_t mokb_schedule_scratch_bytes(int ep_size, int num_local_experts);
+int mokb_schedule(const int32_t* topk_all, int ep_size, int num_local_tokens, int topk,
+                  int num_local_experts, int schedule_capacity, int rank,
+                  int32_t* peer_rank, int32_t* peer_token_idx, int32_t* num_tokens,
+                  int32_t* tokens_per_expert, void* scratch, int32_t* status, void* stream);
+
+/* ---- MXFP8 quantiser: replaces `_C.mxfp8_quantize` (csrc/mxfp8.cuh:234-278).
+ * x [E, M, N] bf16 (E = 1 for a matrix); outputs may be NULL pairwise:
+ * fp8 [E, M, N] + sc [E*M/128, N/128, 32, 16]; fp8_t [E, N, M] + sc_t [E*N/128, M/128, 32, 16]. */
+int mokb_mxfp8_quantize(const void* x_bf16, int64_t E, int64_t M, int64_t N,
+                        void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, void* stream);
+
+/* ---- epilogues: replace `_C.fwd_epilogue` / `_C.bwd_epilogue` (csrc/utils.cuh:12-189). */
+int mokb_fwd_epilogue(const void* y_shared, const void* combine_buffer, const float* topk_weights,
+                      void* output, int64_t num_local_tokens, int64_t hidden, int topk, void* stream);
+int mokb_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* d_x,
+                      int64_t num_local_tokens, int64_t hidden, int topk, void* stream);
+
+/* ---- the fused layer: replace `_C.dispatch_mlp_swiglu_combine_{fwd,bwd}_bf16`
+ * (csrc/megakernel/entrypoints.cuh:101-164, 425-503; host launchers
+ * forward.cuh:432-540, backward.cuh:684-873) and `_C.recompute_forward_context_bf16`
+ * (recompute_forward_context.cuh).  One struct carries what the reference passes
+ * positionally; fields are named after the reference's arguments. */
+typedef struct {
+    /* sizes */
+    int ep_size, ep_rank;
+    int num_local_tokens, hidden, intermediate, num_local_experts, topk;
+    int schedule_capacity, macrobatch_size, minibatch_size, num_comm_sms;
+    int has_swiglu_limit;
+    float swiglu_limit;
+    /* schedule */
+    const int32_t* peer_rank;
+    const int32_t* peer_token_idx;
+    const int32_t* num_tokens;
+    const int32_t* tokens_per_expert;
+    /* symmetric buffers (host arrays of ep_size device addresses) */
+    const uint64_t* x_ptrs_host;              /* [T, H] bf16 per rank */
+    const uint64_t* combine_ptrs_host;        /* [T*K, H] bf16 per rank (forward output) */
+    /* weights */
+    const void *w_shared_gate, *w_shared_up, *w_shared_down;   /* [I,H] [I,H] [H,I] bf16 */
+    const void *w_routed_gate, *w_routed_up, *w_routed_down;   /* [E_l,I,H] [E_l,I,H] [E_l,H,I] bf16 */
+    /* outputs, caller-allocated (ops.py:432-441 of the reference) */
+    void *x_routed;                            /* [MB, H] */
+    void *gate_shared, *up_shared, *hidden_shared;   /* [T, I] */
+    void *gate_routed, *up_routed, *hidden_routed;   /* [MB, I] */
+    void *y_shared;                            /* [T, H] */
+    void *y_routed;                            /* [MB, H]; may be NULL when skip_down_combine */
+    /* scratch: mokb_layer_scratch_bytes() bytes, no initialisation needed */
+    void* scratch;
+    int32_t* status;
+    int skip_down_combine;                     /* 1 = recompute_forward_context */
+} mokb_fwd_bf16_args;
+
+typedef struct {
+    int ep_size, ep_rank;
+    int num_local_tokens, hidden, intermediate, num_local_experts, topk;
+    int schedule_capacity, macrobatch_size, minibatch_size, num_comm_sms;
+    int has_swiglu_limit;
+    float swiglu_limit;
+    const int32_t* peer_rank;
+    const int32_t* peer_token_idx;
+    const int32_t* num_tokens;
+    const int32_t* tokens_per_expert;
+    const uint64_t* d_y_ptrs_host;             /* [T, H] bf16 per rank */
+    const uint64_t* d_x_routed_ptrs_host;      /* [T*K, H] bf16 per rank (output) */
+    const uint64_t* router_weight_ptrs_host;   /* [T, K] f32 per rank */
+    const uint64_t* d_router_weight_ptrs_host; /* [T, K] f32 per rank (output) */
+    const uint64_t* x_ptrs_host;               /* [T, H] bf16 per rank */
+    const void *w_shared_gate, *w_shared_up, *w_shared_down;
+    const void *w_routed_gate, *w_routed_up, *w_routed_down;
+    /* saved forward context (macrobatch 0) */
+    const void *x_routed, *gate_shared, *gate_routed, *up_shared, *up_routed, *hidden_shared, *hidden_routed;
+    /* outputs (ops.py:1169-1184 of the reference) */
+    void *d_x_shared, *d_x_routed;             /* [T,H] [MB,H] */
+    void *d_gate_shared, *d_gate_routed, *d_up_shared, *d_up_routed;   /* [T,I] [MB,I] */
+    void *d_hidden_shared, *d_hidden_routed;   /* [T,I] [MB,I] */
+    void *d_y_routed;                          /* [MB,H] */
+    void *d_w_shared_gate, *d_w_routed_gate, *d_w_shared_up, *d_w_routed_up;
+    void *d_w_shared_down, *d_w_routed_down;
+    void* scratch;                             /* mokb_layer_scratch_bytes() */
+    int32_t* status;
+} mokb_bwd_bf16_args;
+
+size_t mokb_layer_scratch_bytes(int schedule_capacity, int num_local_experts, int macrobatch_size);
+int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_args* args, void* stream);
+int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_args* args, void* stream);
+
+/* ---- building blocks, exported for tests and micro-benchmarks.  They are the
+ * kernels the two layer calls above are made of. */
+
+/* Grouped GEMM D = A * B^T over row groups: rows [0, *num_rows) of A in blocks of
+ * 128, block b using weight matrix group_of_block[b] (NULL = one group).
+ *   mode 0: B [G, N, K] (K contiguous)            -> D [rows, N]
+ *   mode 1: same as 0 with B = gate and B2 = up   -> D = gate, D2 = up, D3 = SwiGLU(gate, up), all [rows, N]
+ *   mode 2: B [G, K, N] (N contiguous; "dgrad")   -> D [rows, N]; if A2/B2 given, D = A*B + A2*B2
+ * Weight-gradient GEMM (mode 3): for each group g with rows [off[g], off[g+1]) of
+ * A [rows, M] and B [rows, N]: D[g] [M, N] = A_g^T * B_g (zero if the group is empty). */
+typedef struct {
+    int mode;
+    int rows_static;            /* used when num_rows is NULL */
+    const int32_t* num_rows;    /* device, optional */
+    const int32_t* group_of_block;   /* device [rows/128], optional */
+    const int32_t* group_offsets;    /* device [G+1] (mode 3) */
+    int G, M, N, K;             /* mode 0-2: N,K; mode 3: M,N */
+    const void *A, *B, *A2, *B2;
+    int lda, ldb;               /* row strides in elements */
+    void *D, *D2, *D3;
+    int ldd;
+    int has_swiglu_limit;
+    float swiglu_limit;
+    int32_t* status;
+} mokb_gemm_args;
+int mokb_grouped_gemm_bf16(const mokb_gemm_args* args, void* stream);
+
+/* Row gather from peers (dispatch, csrc/megakernel/dispatch_combine.cuh:1-150):
+ * dst[i] = src_rank(peer_rank[i])[peer_token_idx[i] / row_divisor] for i < *num_rows;
+ * rows with peer_rank < 0 are zero-filled.  If row_scale_ptrs_host is given, the row is
+ * multiplied in fp32 by scale_rank[peer_token_idx[i]] and rounded to bf16, and the scale
+ * is also written to row_scale_out[i] (0 for padding rows). */
+int mokb_dispatch_rows(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
+                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows,
+                       int row_divisor, int64_t hidden, void* dst,
+                       const uint64_t* row_scale_ptrs_host, float* row_scale_out, void* stream);
+/* Row scatter to peers (combine, dispatch_combine.cuh:152-266):
+ * dst_rank(peer_rank[i])[peer_token_idx[i]] = src[i]; optionally also
+ * val_rank(peer_rank[i])[peer_token_idx[i]] = row_values[i] (router-weight gradients). */
+int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_size,
+                      const int32_t* peer_rank, const int32_t* peer_token_idx,
+                      const int32_t* num_rows, int max_rows, int64_t hidden,
+                      const float* row_values, const uint64_t* value_ptrs_host, void* stream);
+
+/* SwiGLU forward / backward on [rows, cols] bf16 (csrc/megakernel/swiglu.cuh:38-207, 209-566).
+ * Backward also emits per-row sum(d_hidden * silu(g)*u) / w (w = row_scale[i], 1/w := 0 if w <= 0)
+ * when row_grad_out is given. */
+int mokb_swiglu_fwd(const void* gate, const void* up, void* hidden, const int32_t* num_rows, int64_t max_rows,
+                    int64_t cols, int has_limit, float limit, void* stream);
+int mokb_swiglu_bwd(const void* gate, const void* up, const void* d_hidden, void* d_gate, void* d_up,
+                    const float* row_scale, float* row_grad_out, const int32_t* num_rows,
+                    int64_t max_rows, int64_t cols, int has_limit, float limit, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

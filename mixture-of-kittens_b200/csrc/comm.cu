@@ -1,0 +1,261 @@
+// Cross-GPU pieces of the layer, all over plain peer-to-peer loads and stores
+// through NVLink/NVSwitch unicast addresses (no NCCL, no multicast object):
+//   * route all-gather   (reference: csrc/utils.cuh:191-249, NVLS multicast store)
+//   * device barrier     (reference: csrc/utils.cuh:251-299, multimem.red)
+//   * dispatch = row pull from the token's home rank
+//                        (reference: csrc/megakernel/dispatch_combine.cuh:1-150)
+//   * combine  = row push into the home rank's [T*K, H] buffer
+//                        (reference: dispatch_combine.cuh:152-266)
+// With ep_size == 1 the same kernels run against the local pointers.
+#include "common.cuh"
+
+namespace mokb {
+namespace {
+
+__device__ __forceinline__ uint4 ld_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_v4(void* p, uint4 v) {
+    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__global__ void all_gather_kernel(const uint4* __restrict__ src, PeerPtrs peers, int R, int rank, int64_t nvec) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const uint4 v = src[i];
+        for (int r = 0; r < R; ++r) st_v4(static_cast<uint4*>(peers.p[r]) + rank * nvec + i, v);
+    }
+}
+
+// One CTA.  Thread r adds 1 to rank r's barrier word (release, system scope);
+// thread 0 then waits until the local word reaches the new target.
+__global__ void barrier_kernel(PeerPtrs peers, int R, int rank, int32_t* target, int32_t* status,
+                               unsigned long long timeout_ns) {
+    __shared__ int new_target;
+    if (threadIdx.x == 0) {
+        new_target = *target + R;
+        *target = new_target;
+    }
+    __syncthreads();
+    if (threadIdx.x < R) {
+        __threadfence_system();
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(peers.p[threadIdx.x]) : "memory");
+    }
+    if (threadIdx.x == 0) {
+        const int32_t* mine = static_cast<const int32_t*>(peers.p[rank]);
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (uint32_t i = 0;; ++i) {
+            int32_t v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (v - new_target >= 0) break;
+            if ((i & 63) == 63) {
+                unsigned long long t1;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                if (t1 - t0 > timeout_ns) {
+                    atomicCAS(status, MOKB_ST_OK, MOKB_ST_BARRIER_TIMEOUT);
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+        __threadfence_system();
+    }
+}
+
+// One warp per schedule row, 16-byte vectors, four loads in flight per lane.
+template <bool SCALE>
+__global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t* __restrict__ peer_rank,
+                                const int32_t* __restrict__ peer_token_idx, const int32_t* __restrict__ num_rows,
+                                int max_rows, int row_divisor, int vec_per_row, uint4* __restrict__ dst,
+                                float* __restrict__ row_scale_out) {
+    int rows = num_rows ? *num_rows : max_rows;
+    rows = rows < 0 ? 0 : (rows > max_rows ? 0 : rows);
+    const int lane = threadIdx.x & 31;
+    const int warps_per_block = blockDim.x >> 5;
+    const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int nwarps = gridDim.x * warps_per_block;
+    for (int row = warp; row < rows; row += nwarps) {
+        const int pr = peer_rank[row];
+        uint4* out = dst + static_cast<size_t>(row) * vec_per_row;
+        if (pr < 0) {
+            for (int v = lane; v < vec_per_row; v += 32) out[v] = make_uint4(0, 0, 0, 0);
+            if (SCALE && lane == 0 && row_scale_out) row_scale_out[row] = 0.f;
+            continue;
+        }
+        const int tok = peer_token_idx[row];
+        const uint4* in = static_cast<const uint4*>(src.p[pr]) + static_cast<size_t>(tok / row_divisor) * vec_per_row;
+        float w = 1.f;
+        if (SCALE) {
+            w = static_cast<const float*>(scale_src.p[pr])[tok];
+            if (lane == 0 && row_scale_out) row_scale_out[row] = w;
+        }
+        for (int v0 = lane; v0 < vec_per_row; v0 += 128) {
+            uint4 r[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (v0 + 32 * u < vec_per_row) r[u] = ld_v4(in + v0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (v0 + 32 * u >= vec_per_row) continue;
+                if (SCALE) {
+                    uint32_t* q = reinterpret_cast<uint32_t*>(&r[u]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = unpack_bf16(q[k]);
+                        q[k] = pack_bf16(f.x * w, f.y * w);
+                    }
+                }
+                out[v0 + 32 * u] = r[u];
+            }
+        }
+    }
+}
+
+__global__ void combine_kernel(const uint4* __restrict__ src, PeerPtrs dst, PeerPtrs val_dst,
+                               const int32_t* __restrict__ peer_rank, const int32_t* __restrict__ peer_token_idx,
+                               const int32_t* __restrict__ num_rows, int max_rows, int vec_per_row,
+                               const float* __restrict__ row_values) {
+    int rows = num_rows ? *num_rows : max_rows;
+    rows = rows < 0 ? 0 : (rows > max_rows ? 0 : rows);
+    const int lane = threadIdx.x & 31;
+    const int warps_per_block = blockDim.x >> 5;
+    const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int nwarps = gridDim.x * warps_per_block;
+    for (int row = warp; row < rows; row += nwarps) {
+        const int pr = peer_rank[row];
+        if (pr < 0) continue;
+        const int tok = peer_token_idx[row];
+        const uint4* in = src + static_cast<size_t>(row) * vec_per_row;
+        uint4* out = static_cast<uint4*>(dst.p[pr]) + static_cast<size_t>(tok) * vec_per_row;
+        for (int v0 = lane; v0 < vec_per_row; v0 += 128) {
+            uint4 r[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (v0 + 32 * u < vec_per_row) r[u] = in[v0 + 32 * u];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (v0 + 32 * u < vec_per_row) st_v4(out + v0 + 32 * u, r[u]);
+        }
+        if (row_values && lane == 0) static_cast<float*>(val_dst.p[pr])[tok] = row_values[row];
+    }
+}
+
+int fill_peers(PeerPtrs* out, const uint64_t* host, int R, const char* what) {
+    MOKB_REQUIRE(host != nullptr, "%s: null pointer list", what);
+    for (int r = 0; r < kPeerMax; ++r) out->p[r] = nullptr;
+    for (int r = 0; r < R; ++r) {
+        MOKB_REQUIRE(host[r] != 0 && (host[r] & 15) == 0, "%s[%d] = 0x%llx is null or not 16-byte aligned", what, r,
+                     (unsigned long long)host[r]);
+        out->p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(host[r]));
+    }
+    return MOKB_OK;
+}
+
+unsigned long long g_barrier_timeout_ns = 10ull * 1000 * 1000 * 1000;
+
+}  // namespace
+}  // namespace mokb
+
+using namespace mokb;
+
+extern "C" int mokb_set_barrier_timeout_ms(int ms) {
+    MOKB_REQUIRE(ms > 0, "barrier timeout must be positive");
+    g_barrier_timeout_ns = static_cast<unsigned long long>(ms) * 1000ull * 1000ull;
+    return MOKB_OK;
+}
+
+extern "C" int mokb_all_gather_top_experts(const int32_t* top_experts, const uint64_t* gather_buffer_ptrs_host,
+                                           int ep_size, int rank, int64_t numel, void* stream) {
+    MOKB_REQUIRE(top_experts != nullptr, "all_gather_top_experts: null input");
+    MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP && rank >= 0 && rank < ep_size, "all_gather_top_experts: bad ep_size/rank");
+    MOKB_REQUIRE(numel > 0 && numel % 4 == 0, "all_gather_top_experts: numel must be a positive multiple of 4");
+    MOKB_REQUIRE((reinterpret_cast<uintptr_t>(top_experts) & 15) == 0, "all_gather_top_experts: input not 16-byte aligned");
+    PeerPtrs peers;
+    MOKB_TRY(fill_peers(&peers, gather_buffer_ptrs_host, ep_size, "gather_buffer_ptrs"));
+    const int64_t nvec = numel / 4;
+    const int threads = 256;
+    int64_t blocks = (nvec + threads - 1) / threads;
+    if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+    all_gather_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint4*>(top_experts), peers, ep_size, rank, nvec);
+    MOKB_CUDA(cudaGetLastError());
+    note_launch();
+    return MOKB_OK;
+}
+
+extern "C" int mokb_barrier_all(const uint64_t* barrier_ptrs_host, int ep_size, int rank, int32_t* target,
+                                int32_t* status, void* stream) {
+    MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP && rank >= 0 && rank < ep_size, "barrier_all: bad ep_size/rank");
+    MOKB_REQUIRE(target && status, "barrier_all: null pointer");
+    PeerPtrs peers;
+    MOKB_REQUIRE(barrier_ptrs_host != nullptr, "barrier_all: null pointer list");
+    for (int r = 0; r < kPeerMax; ++r) peers.p[r] = nullptr;
+    for (int r = 0; r < ep_size; ++r) {
+        MOKB_REQUIRE(barrier_ptrs_host[r] != 0 && (barrier_ptrs_host[r] & 3) == 0, "barrier_all: bad pointer for rank %d", r);
+        peers.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(barrier_ptrs_host[r]));
+    }
+    barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(peers, ep_size, rank, target, status, g_barrier_timeout_ns);
+    MOKB_CUDA(cudaGetLastError());
+    note_launch();
+    return MOKB_OK;
+}
+
+extern "C" int mokb_dispatch_rows(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
+                                  const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows,
+                                  int row_divisor, int64_t hidden, void* dst,
+                                  const uint64_t* row_scale_ptrs_host, float* row_scale_out, void* stream) {
+    MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "dispatch_rows: bad ep_size");
+    MOKB_REQUIRE(peer_rank && peer_token_idx && dst, "dispatch_rows: null pointer");
+    MOKB_REQUIRE(max_rows >= 0 && row_divisor >= 1 && hidden > 0 && hidden % 8 == 0, "dispatch_rows: bad sizes");
+    MOKB_REQUIRE((reinterpret_cast<uintptr_t>(dst) & 15) == 0, "dispatch_rows: dst not 16-byte aligned");
+    PeerPtrs src, scale;
+    MOKB_TRY(fill_peers(&src, src_ptrs_host, ep_size, "src_ptrs"));
+    for (int r = 0; r < kPeerMax; ++r) scale.p[r] = nullptr;
+    if (max_rows == 0) return MOKB_OK;
+    const int threads = 256;
+    const int blocks = sm_count() * 8;
+    const int vec = static_cast<int>(hidden / 8);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (row_scale_ptrs_host) {
+        for (int r = 0; r < ep_size; ++r) {
+            MOKB_REQUIRE(row_scale_ptrs_host[r] != 0, "dispatch_rows: null scale pointer for rank %d", r);
+            scale.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(row_scale_ptrs_host[r]));
+        }
+        dispatch_kernel<true><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows,
+                                                         row_divisor, vec, static_cast<uint4*>(dst), row_scale_out);
+    } else {
+        dispatch_kernel<false><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows,
+                                                          row_divisor, vec, static_cast<uint4*>(dst), nullptr);
+    }
+    MOKB_CUDA(cudaGetLastError());
+    note_launch();
+    return MOKB_OK;
+}
+
+extern "C" int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_size,
+                                 const int32_t* peer_rank, const int32_t* peer_token_idx,
+                                 const int32_t* num_rows, int max_rows, int64_t hidden,
+                                 const float* row_values, const uint64_t* value_ptrs_host, void* stream) {
+    MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "combine_rows: bad ep_size");
+    MOKB_REQUIRE(src && peer_rank && peer_token_idx, "combine_rows: null pointer");
+    MOKB_REQUIRE(max_rows >= 0 && hidden > 0 && hidden % 8 == 0, "combine_rows: bad sizes");
+    MOKB_REQUIRE((row_values == nullptr) == (value_ptrs_host == nullptr), "combine_rows: row_values and value_ptrs go together");
+    PeerPtrs dst, val;
+    MOKB_TRY(fill_peers(&dst, dst_ptrs_host, ep_size, "dst_ptrs"));
+    for (int r = 0; r < kPeerMax; ++r) val.p[r] = nullptr;
+    if (value_ptrs_host)
+        for (int r = 0; r < ep_size; ++r) {
+            MOKB_REQUIRE(value_ptrs_host[r] != 0, "combine_rows: null value pointer for rank %d", r);
+            val.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(value_ptrs_host[r]));
+        }
+    if (max_rows == 0) return MOKB_OK;
+    combine_kernel<<<sm_count() * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
+        static_cast<int>(hidden / 8), row_values);
+    MOKB_CUDA(cudaGetLastError());
+    note_launch();
+    return MOKB_OK;
+}

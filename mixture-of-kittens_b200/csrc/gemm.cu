@@ -1,0 +1,420 @@
+// Grouped BF16 GEMM for the expert FFN, forward and backward, on the 5th-gen
+// tensor cores: tcgen05.mma with the fp32 accumulator in tensor memory, operands
+// staged in 128B-swizzled shared memory by TMA, and a persistent, warp-specialised
+// CTA per SM.
+//
+//   warp 0      TMA producer   (one elected lane)  : global -> smem ring, 4 stages of 48 KB
+//   warp 1      MMA issuer     (one elected lane)  : 4 x tcgen05.mma (128 x 256 x 16) per stage
+//   warps 2..5  epilogue                           : TMEM -> registers -> bf16 -> global
+//
+// The 512 TMEM columns hold two 128x256 fp32 accumulators, so the epilogue of
+// tile i overlaps the main loop of tile i+1 (the reference keeps a single
+// accumulator per CTA, csrc/megakernel/forward.cuh:84).
+//
+// One kernel template covers the operand layouts the layer needs
+// (reference: csrc/megakernel/grouped_gemm.cuh:1-381):
+//   MODE_NT      D[rows,N] = A[rows,K] * W[g][N,K]^T                 (down projection)
+//   MODE_SWIGLU  gate,up = A * Wg[g]^T, A * Wu[g]^T; hidden = SwiGLU  (one 128+128 column tile)
+//   MODE_NN      D[rows,N] = A[rows,K] * W[g][K,N] (+ A2 * W2[g])    (input gradients)
+//   MODE_WGRAD   D[g][M,N] = A[rows_g,M]^T * B[rows_g,N]             (weight gradients)
+// Rows are grouped in blocks of 128 (expert segments are multiples of 256 rows),
+// so a tile never straddles two experts.
+#include "common.cuh"
+
+namespace mokb {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;            // 16 KB
+constexpr int B_BYTES = BN * BK * 2;            // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KB
+constexpr int CHUNK_BYTES = 64 * BK * 2;        // one 64-wide MN-major chunk: 8 KB
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;                      // m-blocks per raster super-group
+constexpr size_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+enum { MODE_NT = 0, MODE_SWIGLU = 1, MODE_NN = 2, MODE_WGRAD = 3 };
+
+struct KParams {
+    int rows_cap;                    // static upper bound of rows
+    const int32_t* num_rows;         // device, optional
+    const int32_t* group_of_block;   // device [rows/128], optional
+    const int32_t* group_offsets;    // device [G+1], MODE_WGRAD
+    int G, M, N, K;
+    int b_rows_per_group;            // rows of the flattened weight tensor per group
+    int dual;                        // MODE_NN: second (A2, B2) pair accumulates into the same tile
+    __nv_bfloat16 *D, *D2, *D3;
+    int ldd;
+    int has_limit;
+    float limit;
+    int32_t* status;
+};
+
+struct Tile {
+    int m_blk, n_blk, group, k_iters, k_row0;
+};
+
+template <int MODE>
+struct Sched {
+    int m_blocks, n_blocks, total;
+    __device__ Sched(const KParams& p) {
+        if (MODE == MODE_WGRAD) {
+            m_blocks = p.M / BM;
+            n_blocks = (p.N + BN - 1) / BN;
+            total = p.G * m_blocks * n_blocks;
+        } else {
+            int rows = p.num_rows ? *p.num_rows : p.rows_cap;
+            if (rows < 0 || rows > p.rows_cap) rows = 0;
+            m_blocks = rows / BM;
+            n_blocks = MODE == MODE_SWIGLU ? p.N / 128 : (p.N + BN - 1) / BN;
+            total = m_blocks * n_blocks;
+        }
+    }
+    __device__ Tile get(const KParams& p, int t) const {
+        Tile ti;
+        if (MODE == MODE_WGRAD) {
+            const int per = m_blocks * n_blocks;
+            ti.group = t / per;
+            const int rem = t - ti.group * per;
+            ti.n_blk = rem / m_blocks;
+            ti.m_blk = rem - ti.n_blk * m_blocks;
+            ti.k_row0 = p.group_offsets[ti.group];
+            ti.k_iters = (p.group_offsets[ti.group + 1] - ti.k_row0) / BK;
+        } else {
+            const int per = GROUP_M * n_blocks;
+            const int sg = t / per;
+            const int first = sg * GROUP_M;
+            const int gsize = min(GROUP_M, m_blocks - first);
+            const int in = t - sg * per;
+            ti.n_blk = in / gsize;
+            ti.m_blk = first + (in - ti.n_blk * gsize);
+            ti.group = p.group_of_block ? p.group_of_block[ti.m_blk] : 0;
+            ti.k_row0 = 0;
+            ti.k_iters = (p.K / BK) * (p.dual ? 2 : 1);
+        }
+        return ti;
+    }
+};
+
+__device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// 32 fp32 accumulator columns of one row -> 32 bf16 (64 bytes) in global memory
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const uint32_t (&r)[32]) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        st_global_v4(dst + 8 * q,
+                     pack_bf16(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1])),
+                     pack_bf16(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3])),
+                     pack_bf16(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5])),
+                     pack_bf16(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7])));
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                    const KParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+    // barrier block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem_ptr | abort
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+    uint8_t* bar_gen = smem_gen + STAGES * STAGE_BYTES;
+    volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * STAGES + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * (2 * STAGES + 4) + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 128);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        if (MODE == MODE_SWIGLU || (MODE == MODE_NN && p.dual)) {
+            tma_prefetch_desc(&tmB2);
+            if (MODE == MODE_NN) tma_prefetch_desc(&tmA2);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_slot;
+
+    const Sched<MODE> sched(p);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < sched.total; t += gridDim.x) {
+                const Tile ti = sched.get(p, t);
+                const int kh = p.K / BK;
+                for (int it = 0; it < ti.k_iters; ++it) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
+                    const uint32_t fb = full_bar(s);
+                    mbar_expect_tx(fb, STAGE_BYTES);
+                    const uint32_t a_dst = smem_base + s * STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + A_BYTES;
+                    if (MODE == MODE_NT) {
+                        tma_load_2d(a_dst, &tmA, fb, it * BK, ti.m_blk * BM);
+                        tma_load_2d(b_dst, &tmB, fb, it * BK, ti.group * p.b_rows_per_group + ti.n_blk * BN);
+                    } else if (MODE == MODE_SWIGLU) {
+                        tma_load_2d(a_dst, &tmA, fb, it * BK, ti.m_blk * BM);
+                        const int brow = ti.group * p.b_rows_per_group + ti.n_blk * 128;
+                        tma_load_2d(b_dst, &tmB, fb, it * BK, brow);
+                        tma_load_2d(b_dst + B_BYTES / 2, &tmB2, fb, it * BK, brow);
+                    } else if (MODE == MODE_NN) {
+                        const bool second = it >= kh;
+                        const int kk = (second ? it - kh : it) * BK;
+                        const CUtensorMap* ta = second ? &tmA2 : &tmA;
+                        const CUtensorMap* tb = second ? &tmB2 : &tmB;
+                        tma_load_2d(a_dst, ta, fb, kk, ti.m_blk * BM);
+                        const int brow = ti.group * p.b_rows_per_group + kk;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) tma_load_2d(b_dst + c * CHUNK_BYTES, tb, fb, ti.n_blk * BN + 64 * c, brow);
+                    } else {
+                        const int krow = ti.k_row0 + it * BK;
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) tma_load_2d(a_dst + c * CHUNK_BYTES, &tmA, fb, ti.m_blk * BM + 64 * c, krow);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) tma_load_2d(b_dst + c * CHUNK_BYTES, &tmB, fb, ti.n_blk * BN + 64 * c, krow);
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t a_mn = MODE == MODE_WGRAD ? 1u : 0u;
+            constexpr uint32_t b_mn = (MODE == MODE_NN || MODE == MODE_WGRAD) ? 1u : 0u;
+            // instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 256
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (a_mn << 15) | (b_mn << 16) |
+                                       (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+            constexpr uint32_t a_step = a_mn ? (2048u >> 4) : (32u >> 4);   // descriptor advance per 16 elements of K
+            constexpr uint32_t b_step = b_mn ? (2048u >> 4) : (32u >> 4);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            int local = 0;
+            for (int t = blockIdx.x; ok && t < sched.total; t += gridDim.x, ++local) {
+                const Tile ti = sched.get(p, t);
+                const int acc = local & 1;
+                const uint32_t acc_ph = (local >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int it = 0; it < ti.k_iters; ++it) {
+                    if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * STAGE_BYTES;
+                    const uint32_t b_addr = a_addr + A_BYTES;
+                    const uint64_t a_desc = a_mn ? make_smem_desc(a_addr, CHUNK_BYTES, 1024) : make_smem_desc(a_addr, 16, 1024);
+                    const uint64_t b_desc = b_mn ? make_smem_desc(b_addr, CHUNK_BYTES, 1024) : make_smem_desc(b_addr, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16(d_tmem, a_desc + static_cast<uint64_t>(k * a_step), b_desc + static_cast<uint64_t>(k * b_step),
+                                  idesc, (it | k) != 0 ? 1u : 0u);
+                    umma_commit(empty_bar(s));          // frees the smem stage once these MMAs retire
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(acc));            // accumulator complete -> epilogue
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;                   // TMEM lanes [32q, 32q+32) belong to warps with id % 4 == q
+        const int row_in_tile = quarter * 32 + lane;
+        int local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; ok && t < sched.total; t += gridDim.x, ++local) {
+            const Tile ti = sched.get(p, t);
+            const int acc = local & 1;
+            const uint32_t acc_ph = (local >> 1) & 1u;
+            if (!mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+            const bool empty_k = ti.k_iters == 0;
+            if (MODE == MODE_SWIGLU) {
+                const size_t row = static_cast<size_t>(ti.m_blk) * BM + row_in_tile;
+                const size_t off = row * p.ldd + static_cast<size_t>(ti.n_blk) * 128;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t g[32], u[32];
+                    tmem_ld_32x32(t_addr + c * 32, g);
+                    tmem_ld_32x32(t_addr + 128 + c * 32, u);
+                    tmem_ld_wait();
+                    uint32_t h[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float gf = bf16_round(__uint_as_float(g[i]));
+                        float uf = bf16_round(__uint_as_float(u[i]));
+                        g[i] = __float_as_uint(gf);
+                        u[i] = __float_as_uint(uf);
+                        if (p.has_limit) {
+                            gf = fminf(gf, p.limit);
+                            uf = fminf(fmaxf(uf, -p.limit), p.limit);
+                        }
+                        h[i] = __float_as_uint(gf / (1.0f + __expf(-gf)) * uf);
+                    }
+                    store_row32(p.D + off + c * 32, g);
+                    store_row32(p.D2 + off + c * 32, u);
+                    store_row32(p.D3 + off + c * 32, h);
+                }
+            } else {
+                size_t row;
+                if (MODE == MODE_WGRAD) row = static_cast<size_t>(ti.group) * p.M + static_cast<size_t>(ti.m_blk) * BM + row_in_tile;
+                else row = static_cast<size_t>(ti.m_blk) * BM + row_in_tile;
+                __nv_bfloat16* dst = p.D + row * p.ldd + static_cast<size_t>(ti.n_blk) * BN;
+                const int cols_left = p.N - ti.n_blk * BN;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    if (c * 32 >= cols_left) break;
+                    uint32_t r[32];
+                    if (empty_k) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = 0u;
+                    } else {
+                        tmem_ld_32x32(t_addr + c * 32, r);
+                        tmem_ld_wait();
+                    }
+                    store_row32(dst + c * 32, r);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tempty_bar(acc));
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // a wait ran out: give copies still in flight time to land before the CTA's smem is released
+        const unsigned long long t0 = clock64();
+        while (clock64() - t0 < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int MODE>
+int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2, const KParams& p,
+           int tiles_upper_bound, cudaStream_t stream) {
+    MOKB_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    int grid = sm_count();
+    if (tiles_upper_bound < grid) grid = tiles_upper_bound;
+    if (grid < 1) return MOKB_OK;
+    grouped_gemm_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(a, b, a2, b2, p);
+    MOKB_CUDA(cudaGetLastError());
+    note_launch();
+    return MOKB_OK;
+}
+
+}  // namespace
+}  // namespace mokb
+
+using namespace mokb;
+
+extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    MOKB_REQUIRE(g != nullptr, "grouped_gemm: null args");
+    MOKB_REQUIRE(g->mode >= 0 && g->mode <= 3, "grouped_gemm: unknown mode %d", g->mode);
+    MOKB_REQUIRE(g->A && g->B && g->D && g->status, "grouped_gemm: null pointer");
+    MOKB_REQUIRE(g->G >= 1, "grouped_gemm: G must be >= 1");
+    MOKB_REQUIRE(g->rows_static >= 0 && g->rows_static % BM == 0, "grouped_gemm: rows must be a multiple of 128");
+    KParams p;
+    memset(&p, 0, sizeof(p));
+    p.rows_cap = g->rows_static;
+    p.num_rows = g->num_rows;
+    p.group_of_block = g->group_of_block;
+    p.group_offsets = g->group_offsets;
+    p.G = g->G; p.M = g->M; p.N = g->N; p.K = g->K;
+    p.D = static_cast<__nv_bfloat16*>(g->D);
+    p.D2 = static_cast<__nv_bfloat16*>(g->D2);
+    p.D3 = static_cast<__nv_bfloat16*>(g->D3);
+    p.ldd = g->ldd;
+    p.has_limit = g->has_swiglu_limit;
+    p.limit = g->swiglu_limit;
+    p.status = g->status;
+    p.dual = 0;
+    MOKB_REQUIRE(g->ldd % 8 == 0 && g->lda % 8 == 0 && g->ldb % 8 == 0, "grouped_gemm: leading dimensions must be multiples of 8");
+    MOKB_REQUIRE((reinterpret_cast<uintptr_t>(g->D) & 15) == 0, "grouped_gemm: D not 16-byte aligned");
+    if (g->rows_static == 0) return MOKB_OK;
+    const uint64_t rows = static_cast<uint64_t>(g->rows_static);
+    CUtensorMap ta, tb, ta2, tb2;
+    memset(&ta2, 0, sizeof(ta2));
+    memset(&tb2, 0, sizeof(tb2));
+    switch (g->mode) {
+    case MODE_NT: {
+        MOKB_REQUIRE(g->K > 0 && g->K % BK == 0 && g->N > 0 && g->N % BN == 0, "grouped_gemm NT: K %% 64 and N %% 256 must be 0");
+        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->K, rows, 2ull * g->lda, 64, BM));
+        MOKB_TRY(make_tmap_2d(&tb, g->B, 2, g->K, static_cast<uint64_t>(g->G) * g->N, 2ull * g->ldb, 64, BN));
+        p.b_rows_per_group = g->N;
+        ta2 = ta; tb2 = tb;
+        return launch<MODE_NT>(ta, tb, ta2, tb2, p, (g->rows_static / BM) * (g->N / BN), stream);
+    }
+    case MODE_SWIGLU: {
+        MOKB_REQUIRE(g->K > 0 && g->K % BK == 0 && g->N > 0 && g->N % 128 == 0, "grouped_gemm SWIGLU: K %% 64 and N %% 128 must be 0");
+        MOKB_REQUIRE(g->B2 && g->D2 && g->D3, "grouped_gemm SWIGLU: B2, D2, D3 required");
+        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->K, rows, 2ull * g->lda, 64, BM));
+        MOKB_TRY(make_tmap_2d(&tb, g->B, 2, g->K, static_cast<uint64_t>(g->G) * g->N, 2ull * g->ldb, 64, 128));
+        MOKB_TRY(make_tmap_2d(&tb2, g->B2, 2, g->K, static_cast<uint64_t>(g->G) * g->N, 2ull * g->ldb, 64, 128));
+        p.b_rows_per_group = g->N;
+        ta2 = ta;
+        return launch<MODE_SWIGLU>(ta, tb, ta2, tb2, p, (g->rows_static / BM) * (g->N / 128), stream);
+    }
+    case MODE_NN: {
+        MOKB_REQUIRE(g->K > 0 && g->K % BK == 0 && g->N > 0 && g->N % 64 == 0, "grouped_gemm NN: K %% 64 and N %% 64 must be 0");
+        MOKB_REQUIRE((g->A2 == nullptr) == (g->B2 == nullptr), "grouped_gemm NN: A2 and B2 go together");
+        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->K, rows, 2ull * g->lda, 64, BM));
+        MOKB_TRY(make_tmap_2d(&tb, g->B, 2, g->N, static_cast<uint64_t>(g->G) * g->K, 2ull * g->ldb, 64, 64));
+        ta2 = ta; tb2 = tb;
+        if (g->A2) {
+            MOKB_TRY(make_tmap_2d(&ta2, g->A2, 2, g->K, rows, 2ull * g->lda, 64, BM));
+            MOKB_TRY(make_tmap_2d(&tb2, g->B2, 2, g->N, static_cast<uint64_t>(g->G) * g->K, 2ull * g->ldb, 64, 64));
+            p.dual = 1;
+        }
+        p.b_rows_per_group = g->K;
+        return launch<MODE_NN>(ta, tb, ta2, tb2, p, (g->rows_static / BM) * ((g->N + BN - 1) / BN), stream);
+    }
+    default: {
+        MOKB_REQUIRE(g->M > 0 && g->M % BM == 0 && g->N > 0 && g->N % 64 == 0, "grouped_gemm WGRAD: M %% 128 and N %% 64 must be 0");
+        MOKB_REQUIRE(g->group_offsets != nullptr, "grouped_gemm WGRAD: group_offsets required");
+        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->M, rows, 2ull * g->lda, 64, 64));
+        MOKB_TRY(make_tmap_2d(&tb, g->B, 2, g->N, rows, 2ull * g->ldb, 64, 64));
+        ta2 = ta; tb2 = tb;
+        return launch<MODE_WGRAD>(ta, tb, ta2, tb2, p, g->G * (g->M / BM) * ((g->N + BN - 1) / BN), stream);
+    }
+    }
+}

@@ -1,0 +1,425 @@
+"""ctypes binding of libmok_b200.so: the module that plays the role of the
+reference's pybind11 extension `mok._C` (csrc/bindings.cu:6-94 of the reference).
+
+Each function takes the arguments the reference's `_C` function of the same
+name takes (torch tensors, Python ints, pointer lists), allocates the outputs
+the reference allocates (with torch.empty, i.e. through the caching allocator:
+no cudaMalloc on the step path), and calls the C-ABI entry point on torch's
+current stream.  There is no fallback: if the shared library is missing the
+import fails, and a failed call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmok_b200.so")
+if not os.path.exists(_LIB_PATH):
+    raise ImportError(
+        f"{_LIB_PATH} is missing: build it with `python mixture-of-kittens_b200/build.py` "
+        "(the CUDA path has no CPU or PyTorch fallback)")
+lib = ctypes.CDLL(_LIB_PATH)
+
+c_int, c_i64, c_f32, c_vp, c_sz = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
+c_u64p = ctypes.POINTER(ctypes.c_uint64)
+
+ST_OK, ST_SCHEDULE_OVERFLOW, ST_BARRIER_TIMEOUT, ST_PIPELINE_TIMEOUT, ST_MACROBATCH_OVERFLOW = range(5)
+STATUS_TEXT = {
+    ST_OK: "ok",
+    ST_SCHEDULE_OVERFLOW: "the padded routed rows exceed schedule_capacity",
+    ST_BARRIER_TIMEOUT: "a rank did not arrive at barrier_all in time",
+    ST_PIPELINE_TIMEOUT: "a pipeline wait inside a GEMM kernel ran out",
+    ST_MACROBATCH_OVERFLOW: "the padded routed rows exceed macrobatch_size",
+}
+
+
+class FwdArgs(ctypes.Structure):
+    _fields_ = (
+        [(n, c_int) for n in ("ep_size", "ep_rank", "num_local_tokens", "hidden", "intermediate", "num_local_experts",
+                              "topk", "schedule_capacity", "macrobatch_size", "minibatch_size", "num_comm_sms",
+                              "has_swiglu_limit")]
+        + [("swiglu_limit", c_f32)]
+        + [(n, c_vp) for n in ("peer_rank", "peer_token_idx", "num_tokens", "tokens_per_expert")]
+        + [("x_ptrs_host", c_u64p), ("combine_ptrs_host", c_u64p)]
+        + [(n, c_vp) for n in ("w_shared_gate", "w_shared_up", "w_shared_down", "w_routed_gate", "w_routed_up",
+                               "w_routed_down", "x_routed", "gate_shared", "up_shared", "hidden_shared", "gate_routed",
+                               "up_routed", "hidden_routed", "y_shared", "y_routed", "scratch", "status")]
+        + [("skip_down_combine", c_int)])
+
+
+class BwdArgs(ctypes.Structure):
+    _fields_ = (
+        [(n, c_int) for n in ("ep_size", "ep_rank", "num_local_tokens", "hidden", "intermediate", "num_local_experts",
+                              "topk", "schedule_capacity", "macrobatch_size", "minibatch_size", "num_comm_sms",
+                              "has_swiglu_limit")]
+        + [("swiglu_limit", c_f32)]
+        + [(n, c_vp) for n in ("peer_rank", "peer_token_idx", "num_tokens", "tokens_per_expert")]
+        + [(n, c_u64p) for n in ("d_y_ptrs_host", "d_x_routed_ptrs_host", "router_weight_ptrs_host",
+                                 "d_router_weight_ptrs_host", "x_ptrs_host")]
+        + [(n, c_vp) for n in ("w_shared_gate", "w_shared_up", "w_shared_down", "w_routed_gate", "w_routed_up",
+                               "w_routed_down", "x_routed", "gate_shared", "gate_routed", "up_shared", "up_routed",
+                               "hidden_shared", "hidden_routed", "d_x_shared", "d_x_routed", "d_gate_shared",
+                               "d_gate_routed", "d_up_shared", "d_up_routed", "d_hidden_shared", "d_hidden_routed",
+                               "d_y_routed", "d_w_shared_gate", "d_w_routed_gate", "d_w_shared_up", "d_w_routed_up",
+                               "d_w_shared_down", "d_w_routed_down", "scratch", "status")])
+
+
+class GemmArgs(ctypes.Structure):
+    _fields_ = [("mode", c_int), ("rows_static", c_int), ("num_rows", c_vp), ("group_of_block", c_vp),
+                ("group_offsets", c_vp), ("G", c_int), ("M", c_int), ("N", c_int), ("K", c_int),
+                ("A", c_vp), ("B", c_vp), ("A2", c_vp), ("B2", c_vp), ("lda", c_int), ("ldb", c_int),
+                ("D", c_vp), ("D2", c_vp), ("D3", c_vp), ("ldd", c_int), ("has_swiglu_limit", c_int),
+                ("swiglu_limit", c_f32), ("status", c_vp)]
+
+
+def _sig(name, restype, *argtypes):
+    fn = getattr(lib, name)
+    fn.restype = restype
+    fn.argtypes = list(argtypes)
+    return fn
+
+
+_last_error = _sig("mokb_last_error", ctypes.c_char_p)
+_sig("mokb_device_arch", c_int)
+_sig("mokb_sm_count", c_int)
+_sig("mokb_struct_sizes", c_int, ctypes.POINTER(c_int), c_int)
+_sig("mokb_set_barrier_timeout_ms", c_int, c_int)
+_sig("mokb_launch_count", ctypes.c_ulonglong)
+_sig("mokb_all_gather_top_experts", c_int, c_vp, c_u64p, c_int, c_int, c_i64, c_vp)
+_sig("mokb_barrier_all", c_int, c_u64p, c_int, c_int, c_vp, c_vp, c_vp)
+_sig("mokb_schedule_scratch_bytes", c_sz, c_int, c_int)
+_sig("mokb_schedule", c_int, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp)
+_sig("mokb_mxfp8_quantize", c_int, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp)
+_sig("mokb_fwd_epilogue", c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_vp)
+_sig("mokb_bwd_epilogue", c_int, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_vp)
+_sig("mokb_layer_scratch_bytes", c_sz, c_int, c_int, c_int)
+_sig("mokb_dispatch_mlp_swiglu_combine_fwd_bf16", c_int, ctypes.POINTER(FwdArgs), c_vp)
+_sig("mokb_dispatch_mlp_swiglu_combine_bwd_bf16", c_int, ctypes.POINTER(BwdArgs), c_vp)
+_sig("mokb_grouped_gemm_bf16", c_int, ctypes.POINTER(GemmArgs), c_vp)
+_sig("mokb_dispatch_rows", c_int, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_i64, c_vp, c_u64p, c_vp, c_vp)
+_sig("mokb_combine_rows", c_int, c_vp, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_vp, c_u64p, c_vp)
+_sig("mokb_swiglu_fwd", c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_f32, c_vp)
+_sig("mokb_swiglu_bwd", c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_f32, c_vp)
+
+EXPORTED = [
+    "mokb_last_error", "mokb_device_arch", "mokb_sm_count", "mokb_struct_sizes", "mokb_set_barrier_timeout_ms", "mokb_launch_count",
+    "mokb_all_gather_top_experts", "mokb_barrier_all", "mokb_schedule_scratch_bytes", "mokb_schedule",
+    "mokb_mxfp8_quantize", "mokb_fwd_epilogue", "mokb_bwd_epilogue", "mokb_layer_scratch_bytes",
+    "mokb_dispatch_mlp_swiglu_combine_fwd_bf16", "mokb_dispatch_mlp_swiglu_combine_bwd_bf16",
+    "mokb_grouped_gemm_bf16", "mokb_dispatch_rows", "mokb_combine_rows", "mokb_swiglu_fwd", "mokb_swiglu_bwd",
+]
+
+
+def _check_struct_layout():
+    sizes = (c_int * 3)()
+    lib.mokb_struct_sizes(sizes, 3)
+    mine = (ctypes.sizeof(FwdArgs), ctypes.sizeof(BwdArgs), ctypes.sizeof(GemmArgs))
+    if tuple(sizes) != mine:
+        raise ImportError(f"struct layout mismatch between _C.py {mine} and libmok_b200.so {tuple(sizes)}")
+
+
+_check_struct_layout()
+
+
+class MokError(RuntimeError):
+    pass
+
+
+def _ck(rc: int) -> None:
+    if rc != 0:
+        raise MokError(f"mok_b200 error {rc}: {_last_error().decode(errors='replace')}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _ptr_array(ptrs: list[int]):
+    return (ctypes.c_uint64 * len(ptrs))(*ptrs)
+
+
+_STATUS: dict[int, torch.Tensor] = {}
+
+
+def status_tensor(device: torch.device | None = None) -> torch.Tensor:
+    """The per-device status word kernels write a code into when something goes wrong."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    t = _STATUS.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _STATUS[idx] = t
+    return t
+
+
+def check_status(device: torch.device | None = None, *, reset: bool = True) -> int:
+    """Reads the status word (synchronises the host: for tests and debugging, never called by the layer)."""
+    t = status_tensor(device)
+    code = int(t.item())
+    if reset and code:
+        t.zero_()
+    return code
+
+
+def raise_for_status(device: torch.device | None = None) -> None:
+    code = check_status(device)
+    if code:
+        raise MokError(f"device status {code}: {STATUS_TEXT.get(code, 'unknown')}")
+
+
+def launch_count() -> int:
+    return int(lib.mokb_launch_count())
+
+
+def set_barrier_timeout_ms(ms: int) -> None:
+    _ck(lib.mokb_set_barrier_timeout_ms(int(ms)))
+
+
+# ----------------------------------------------------------------------------
+# The 14 functions of the reference's `_C` (BF16 ones here; MXFP8 in _C_mxfp8)
+# ----------------------------------------------------------------------------
+def all_gather_top_experts(top_experts, all_gather_top_experts_buffer, multicast_ptr, rank, chunk_bytes, peer_ptrs=None):
+    """`multicast_ptr` and `chunk_bytes` are accepted for signature compatibility; the gather uses
+    plain stores to each peer's buffer, so the caller passes the peers' unicast addresses."""
+    if peer_ptrs is None:
+        raise MokError("all_gather_top_experts needs the peers' buffer addresses (peer_ptrs)")
+    ep_size = all_gather_top_experts_buffer.shape[0]
+    _ck(lib.mokb_all_gather_top_experts(_p(top_experts), _ptr_array(peer_ptrs), ep_size, rank,
+                                        top_experts.numel(), _stream()))
+
+
+def barrier_all(barrier_buffer, barrier_buffer_ptrs, multicast_ptr, target, rank=None):
+    ep_size = len(barrier_buffer_ptrs)
+    if rank is None:
+        rank = barrier_buffer_ptrs.index(barrier_buffer.data_ptr())
+    _ck(lib.mokb_barrier_all(_ptr_array(barrier_buffer_ptrs), ep_size, rank, _p(target),
+                             _p(status_tensor(barrier_buffer.device)), _stream()))
+
+
+def schedule(topk_all, num_local_experts, schedule_capacity, rank):
+    ep_size, T, K = topk_all.shape
+    dev = topk_all.device
+    peer_rank = torch.empty(schedule_capacity, dtype=torch.int32, device=dev)
+    peer_token_idx = torch.empty(schedule_capacity, dtype=torch.int32, device=dev)
+    num_tokens = torch.empty(1, dtype=torch.int32, device=dev)
+    tokens_per_expert = torch.empty(num_local_experts, dtype=torch.int32, device=dev)
+    scratch = torch.empty(lib.mokb_schedule_scratch_bytes(ep_size, num_local_experts), dtype=torch.uint8, device=dev)
+    _ck(lib.mokb_schedule(_p(topk_all), ep_size, T, K, num_local_experts, schedule_capacity, rank,
+                          _p(peer_rank), _p(peer_token_idx), _p(num_tokens), _p(tokens_per_expert),
+                          _p(scratch), _p(status_tensor(dev)), _stream()))
+    return peer_rank, peer_token_idx, num_tokens, tokens_per_expert
+
+
+def mxfp8_quantize(x_bf16, return_normal, return_transposed):
+    dev = x_bf16.device
+    if x_bf16.ndim == 2:
+        E, (M, N) = 1, x_bf16.shape
+        lead = ()
+    else:
+        E, M, N = x_bf16.shape
+        lead = (E,)
+    q = s = qt = st = None
+    if return_normal:
+        q = torch.empty(*lead, M, N, dtype=torch.float8_e4m3fn, device=dev)
+        s = torch.empty(E * M // 128, N // 128, 32, 16, dtype=torch.uint8, device=dev)
+    if return_transposed:
+        qt = torch.empty(*lead, N, M, dtype=torch.float8_e4m3fn, device=dev)
+        st = torch.empty(E * N // 128, M // 128, 32, 16, dtype=torch.uint8, device=dev)
+    _ck(lib.mokb_mxfp8_quantize(_p(x_bf16.contiguous()), E, M, N, _p(q), _p(s), _p(qt), _p(st), _stream()))
+    return q, s, qt, st
+
+
+def fwd_epilogue(y_shared, combine_buffer, topk_weights):
+    out = torch.empty_like(y_shared)
+    T, H = y_shared.shape
+    _ck(lib.mokb_fwd_epilogue(_p(y_shared), _p(combine_buffer), _p(topk_weights), _p(out), T, H,
+                              topk_weights.shape[1], _stream()))
+    return out
+
+
+def bwd_epilogue(d_x_shared, d_x_routed_buffer):
+    out = torch.empty_like(d_x_shared)
+    T, H = d_x_shared.shape
+    _ck(lib.mokb_bwd_epilogue(_p(d_x_shared), _p(d_x_routed_buffer), _p(out), T, H,
+                              d_x_routed_buffer.shape[0] // T, _stream()))
+    return out
+
+
+def _common(args, *, x_ptrs, x_like, w_shared_gate, w_routed_gate, schedule_peer_rank, schedule_peer_token_idx,
+            num_tokens, tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+    T, H = x_like.shape
+    I = w_shared_gate.shape[0]
+    E_l = w_routed_gate.shape[0]
+    ep_size = len(x_ptrs)
+    try:
+        ep_rank = x_ptrs.index(x_like.data_ptr())
+    except ValueError:
+        raise MokError("the local buffer's address is not in its peer pointer list") from None
+    args.ep_size, args.ep_rank = ep_size, ep_rank
+    args.num_local_tokens, args.hidden, args.intermediate, args.num_local_experts, args.topk = T, H, I, E_l, topk
+    args.schedule_capacity = schedule_peer_rank.numel()
+    args.macrobatch_size, args.minibatch_size, args.num_comm_sms = macrobatch_size, minibatch_size, num_comm_sms
+    args.has_swiglu_limit = 0 if swiglu_limit is None else 1
+    args.swiglu_limit = 0.0 if swiglu_limit is None else float(swiglu_limit)
+    args.peer_rank, args.peer_token_idx = _p(schedule_peer_rank), _p(schedule_peer_token_idx)
+    args.num_tokens, args.tokens_per_expert = _p(num_tokens), _p(tokens_per_expert)
+    dev = x_like.device
+    scratch = torch.empty(lib.mokb_layer_scratch_bytes(args.schedule_capacity, E_l, macrobatch_size),
+                          dtype=torch.uint8, device=dev)
+    args.scratch = _p(scratch)
+    args.status = _p(status_tensor(dev))
+    return T, H, I, E_l, dev, scratch
+
+
+def _fwd_bf16(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_routed_gate, w_shared_up, w_routed_up,
+              w_shared_down, w_routed_down, schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert,
+              topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size, skip_down_combine):
+    a = FwdArgs()
+    T, H, I, E_l, dev, scratch = _common(
+        a, x_ptrs=x_ptrs, x_like=x, w_shared_gate=w_shared_gate, w_routed_gate=w_routed_gate,
+        schedule_peer_rank=schedule_peer_rank, schedule_peer_token_idx=schedule_peer_token_idx, num_tokens=num_tokens,
+        tokens_per_expert=tokens_per_expert, topk=topk, swiglu_limit=swiglu_limit, num_comm_sms=num_comm_sms,
+        macrobatch_size=macrobatch_size, minibatch_size=minibatch_size)
+    MB = macrobatch_size
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    x_routed = torch.empty(MB, H, **bf)
+    gate_shared, up_shared, hidden_shared = (torch.empty(T, I, **bf) for _ in range(3))
+    gate_routed, up_routed, hidden_routed = (torch.empty(MB, I, **bf) for _ in range(3))
+    y_shared = y_routed = None
+    keep = [_ptr_array(x_ptrs)]
+    a.x_ptrs_host = keep[0]
+    if not skip_down_combine:
+        y_shared = torch.empty(T, H, **bf)
+        y_routed = torch.empty(MB, H, **bf)
+        keep.append(_ptr_array(combine_buffer_ptrs))
+        a.combine_ptrs_host = keep[1]
+    a.w_shared_gate, a.w_shared_up, a.w_shared_down = _p(w_shared_gate), _p(w_shared_up), _p(w_shared_down)
+    a.w_routed_gate, a.w_routed_up, a.w_routed_down = _p(w_routed_gate), _p(w_routed_up), _p(w_routed_down)
+    a.x_routed = _p(x_routed)
+    a.gate_shared, a.up_shared, a.hidden_shared = _p(gate_shared), _p(up_shared), _p(hidden_shared)
+    a.gate_routed, a.up_routed, a.hidden_routed = _p(gate_routed), _p(up_routed), _p(hidden_routed)
+    a.y_shared, a.y_routed = _p(y_shared), _p(y_routed)
+    a.skip_down_combine = 1 if skip_down_combine else 0
+    _ck(lib.mokb_dispatch_mlp_swiglu_combine_fwd_bf16(ctypes.byref(a), _stream()))
+    return x_routed, gate_shared, gate_routed, up_shared, up_routed, hidden_shared, hidden_routed, y_shared, y_routed
+
+
+def dispatch_mlp_swiglu_combine_fwd_bf16(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_routed_gate,
+                                         w_shared_up, w_routed_up, w_shared_down, w_routed_down, schedule_peer_rank,
+                                         schedule_peer_token_idx, num_tokens, tokens_per_expert, topk, swiglu_limit,
+                                         num_comm_sms, macrobatch_size, minibatch_size):
+    return _fwd_bf16(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_routed_gate, w_shared_up,
+                     w_routed_up, w_shared_down, w_routed_down, schedule_peer_rank, schedule_peer_token_idx,
+                     num_tokens, tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size,
+                     minibatch_size, False)
+
+
+def recompute_forward_context_bf16(x, x_ptrs, w_shared_gate, w_routed_gate, w_shared_up, w_routed_up,
+                                   schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert, topk,
+                                   swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+    return _fwd_bf16(x, x_ptrs, None, None, w_shared_gate, w_routed_gate, w_shared_up, w_routed_up, None, None,
+                     schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert, topk, swiglu_limit,
+                     num_comm_sms, macrobatch_size, minibatch_size, True)[:7]
+
+
+def dispatch_mlp_swiglu_combine_bwd_bf16(d_y_buffer, d_y_buffer_ptrs, d_x_routed_buffer, d_x_routed_buffer_ptrs,
+                                         router_weight_buffer, router_weight_buffer_ptrs, d_router_weight_buffer,
+                                         d_router_weight_buffer_ptrs, w_shared_gate, w_routed_gate, w_shared_up,
+                                         w_routed_up, w_shared_down, w_routed_down, x_routed, gate_shared, gate_routed,
+                                         up_shared, up_routed, hidden_shared, hidden_routed, x, x_ptrs,
+                                         schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert,
+                                         topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+    a = BwdArgs()
+    T, H, I, E_l, dev, scratch = _common(
+        a, x_ptrs=x_ptrs, x_like=x, w_shared_gate=w_shared_gate, w_routed_gate=w_routed_gate,
+        schedule_peer_rank=schedule_peer_rank, schedule_peer_token_idx=schedule_peer_token_idx, num_tokens=num_tokens,
+        tokens_per_expert=tokens_per_expert, topk=topk, swiglu_limit=swiglu_limit, num_comm_sms=num_comm_sms,
+        macrobatch_size=macrobatch_size, minibatch_size=minibatch_size)
+    MB = macrobatch_size
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    keep = [_ptr_array(p) for p in (d_y_buffer_ptrs, d_x_routed_buffer_ptrs, router_weight_buffer_ptrs,
+                                    d_router_weight_buffer_ptrs, x_ptrs)]
+    (a.d_y_ptrs_host, a.d_x_routed_ptrs_host, a.router_weight_ptrs_host, a.d_router_weight_ptrs_host,
+     a.x_ptrs_host) = keep
+    a.w_shared_gate, a.w_shared_up, a.w_shared_down = _p(w_shared_gate), _p(w_shared_up), _p(w_shared_down)
+    a.w_routed_gate, a.w_routed_up, a.w_routed_down = _p(w_routed_gate), _p(w_routed_up), _p(w_routed_down)
+    a.x_routed = _p(x_routed)
+    a.gate_shared, a.gate_routed, a.up_shared, a.up_routed = _p(gate_shared), _p(gate_routed), _p(up_shared), _p(up_routed)
+    a.hidden_shared, a.hidden_routed = _p(hidden_shared), _p(hidden_routed)
+    d_x_shared = torch.empty(T, H, **bf)
+    d_x_routed = torch.empty(MB, H, **bf)
+    d_gate_shared, d_up_shared, d_hidden_shared = (torch.empty(T, I, **bf) for _ in range(3))
+    d_gate_routed, d_up_routed, d_hidden_routed = (torch.empty(MB, I, **bf) for _ in range(3))
+    d_y_routed = torch.empty(MB, H, **bf)
+    d_w_shared_gate, d_w_shared_up = torch.empty(I, H, **bf), torch.empty(I, H, **bf)
+    d_w_shared_down = torch.empty(H, I, **bf)
+    d_w_routed_gate, d_w_routed_up = torch.empty(E_l, I, H, **bf), torch.empty(E_l, I, H, **bf)
+    d_w_routed_down = torch.empty(E_l, H, I, **bf)
+    a.d_x_shared, a.d_x_routed = _p(d_x_shared), _p(d_x_routed)
+    a.d_gate_shared, a.d_gate_routed, a.d_up_shared, a.d_up_routed = (_p(d_gate_shared), _p(d_gate_routed),
+                                                                     _p(d_up_shared), _p(d_up_routed))
+    a.d_hidden_shared, a.d_hidden_routed, a.d_y_routed = _p(d_hidden_shared), _p(d_hidden_routed), _p(d_y_routed)
+    a.d_w_shared_gate, a.d_w_routed_gate, a.d_w_shared_up, a.d_w_routed_up = (_p(d_w_shared_gate), _p(d_w_routed_gate),
+                                                                             _p(d_w_shared_up), _p(d_w_routed_up))
+    a.d_w_shared_down, a.d_w_routed_down = _p(d_w_shared_down), _p(d_w_routed_down)
+    _ck(lib.mokb_dispatch_mlp_swiglu_combine_bwd_bf16(ctypes.byref(a), _stream()))
+    return (d_x_shared, d_x_routed, d_gate_shared, d_gate_routed, d_up_shared, d_up_routed, d_hidden_shared,
+            d_hidden_routed, d_y_routed, d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up,
+            d_w_shared_down, d_w_routed_down)
+
+
+# ----------------------------------------------------------------------------
+# Building blocks (tests, micro-benchmarks)
+# ----------------------------------------------------------------------------
+def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None, group_offsets=None, G=1,
+                 M=0, N=0, K=0, A2=None, B2=None, D2=None, D3=None, lda=None, ldb=None, ldd=None, swiglu_limit=None):
+    g = GemmArgs()
+    g.mode = mode
+    g.rows_static = A.shape[0] if rows is None else rows
+    g.num_rows, g.group_of_block, g.group_offsets = _p(num_rows), _p(group_of_block), _p(group_offsets)
+    g.G, g.M, g.N, g.K = G, M, N, K
+    g.A, g.B, g.A2, g.B2 = _p(A), _p(B), _p(A2), _p(B2)
+    g.lda = A.shape[-1] if lda is None else lda
+    g.ldb = B.shape[-1] if ldb is None else ldb
+    g.D, g.D2, g.D3 = _p(D), _p(D2), _p(D3)
+    g.ldd = D.shape[-1] if ldd is None else ldd
+    g.has_swiglu_limit = 0 if swiglu_limit is None else 1
+    g.swiglu_limit = 0.0 if swiglu_limit is None else float(swiglu_limit)
+    g.status = _p(status_tensor(A.device))
+    _ck(lib.mokb_grouped_gemm_bf16(ctypes.byref(g), _stream()))
+
+
+def dispatch_rows(src_ptrs, peer_rank, peer_token_idx, num_rows, max_rows, row_divisor, hidden, dst,
+                  row_scale_ptrs=None, row_scale_out=None):
+    _ck(lib.mokb_dispatch_rows(_ptr_array(src_ptrs), len(src_ptrs), _p(peer_rank), _p(peer_token_idx), _p(num_rows),
+                               max_rows, row_divisor, hidden, _p(dst),
+                               None if row_scale_ptrs is None else _ptr_array(row_scale_ptrs), _p(row_scale_out),
+                               _stream()))
+
+
+def combine_rows(src, dst_ptrs, peer_rank, peer_token_idx, num_rows, max_rows, hidden, row_values=None, value_ptrs=None):
+    _ck(lib.mokb_combine_rows(_p(src), _ptr_array(dst_ptrs), len(dst_ptrs), _p(peer_rank), _p(peer_token_idx),
+                              _p(num_rows), max_rows, hidden, _p(row_values),
+                              None if value_ptrs is None else _ptr_array(value_ptrs), _stream()))
+
+
+def swiglu_fwd(gate, up, swiglu_limit=None, num_rows=None):
+    hidden = torch.empty_like(gate)
+    _ck(lib.mokb_swiglu_fwd(_p(gate), _p(up), _p(hidden), _p(num_rows), gate.shape[0], gate.shape[1],
+                            0 if swiglu_limit is None else 1, 0.0 if swiglu_limit is None else float(swiglu_limit),
+                            _stream()))
+    return hidden
+
+
+def swiglu_bwd(gate, up, d_hidden, swiglu_limit=None, row_scale=None, want_row_grad=False, num_rows=None):
+    d_gate, d_up = torch.empty_like(gate), torch.empty_like(up)
+    row_grad = torch.empty(gate.shape[0], dtype=torch.float32, device=gate.device) if want_row_grad else None
+    _ck(lib.mokb_swiglu_bwd(_p(gate), _p(up), _p(d_hidden), _p(d_gate), _p(d_up), _p(row_scale), _p(row_grad),
+                            _p(num_rows), gate.shape[0], gate.shape[1], 0 if swiglu_limit is None else 1,
+                            0.0 if swiglu_limit is None else float(swiglu_limit), _stream()))
+    return d_gate, d_up, row_grad

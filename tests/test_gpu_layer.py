@@ -1,0 +1,119 @@
+"""GPU parity tests of the whole layer through mok.functional (EP = 1): against the CPU
+oracle on every intermediate, and against the golden fixtures produced by the reference's
+own PyTorch implementation."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import mok_oracle as O
+from tests.golden import make_golden as G
+from tests.gpu_common import assert_close, init_single_rank_group, to_dev
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+CTX_KEYS = ("x_routed", "gate_shared", "gate_routed", "up_shared", "up_routed", "hidden_shared", "hidden_routed")
+GRAD_KEYS = ("d_x", "d_router_weights", "d_w_routed_gate", "d_w_routed_up", "d_w_routed_down",
+             "d_w_shared_gate", "d_w_shared_up", "d_w_shared_down")
+
+
+def run_layer(inp_cpu, E_l, *, limit=None, MB=None, mb=256, recompute=False, mult=0.5):
+    import mok
+    from mok import _C, functional as F
+    group = init_single_rank_group()
+    inp = to_dev(inp_cpu)
+    T, H = inp.x.shape
+    K = inp.top_experts.shape[1]
+    cfg = F.MoKConfig(minibatch_size=mb, macrobatch_size=MB or T * K * 2, schedule_capacity_multiplier=mult)
+    ws = F.get_workspace(cfg, group, device=torch.device("cuda", 0), num_local_tokens=T, hidden_size=H, topk=K)
+    sched = F.build_schedule(ws, cfg, inp.top_experts, num_local_experts=E_l)
+    out, ctx = F.forward(cfg, ws, sched, inp.x, inp.router_weights, inp.w_shared_gate, inp.w_shared_up,
+                         inp.w_shared_down, inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down, limit)
+    ctx2 = None
+    if recompute:
+        ctx2 = F.recompute_forward_context(cfg, ws, sched, inp.x, inp.w_shared_gate, inp.w_shared_up,
+                                           inp.w_routed_gate, inp.w_routed_up, limit)
+    grads = F.backward(cfg, ws, sched, ctx, inp.grad_output, inp.x, inp.router_weights, inp.w_shared_gate,
+                       inp.w_shared_up, inp.w_shared_down, inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down, limit)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0
+    return sched, out, ctx, ctx2, grads, ws
+
+
+@pytest.mark.parametrize("shape", [
+    dict(T=512, H=256, I=256, E=4, K=2, routing="router", limit=None),
+    dict(T=1024, H=1024, I=512, E=8, K=2, routing="router", limit=None),     # config 1 of the benchmark
+    dict(T=512, H=512, I=384, E=6, K=3, routing="gaussian", limit=2.0),      # I not a multiple of 256, clamped
+    dict(T=512, H=256, I=128, E=16, K=1, routing="zipf", limit=None),        # empty experts likely, top-1
+], ids=["min", "c1", "i384_clamp", "zipf_top1"])
+def test_layer_bf16_vs_oracle(shape):
+    limit = shape.pop("limit")
+    ranks = O.make_inputs(R=1, seed=3, **shape)
+    ref = O.layer_forward_backward(ranks, swiglu_limit=limit)[0]
+    sched, out, ctx, _, grads, ws = run_layer(ranks[0], shape["E"], limit=limit)
+    # schedule: bit exact
+    np.testing.assert_array_equal(sched.peer_rank.cpu().numpy(), ref["peer_rank"])
+    np.testing.assert_array_equal(sched.peer_token_idx.cpu().numpy(), ref["peer_token_idx"])
+    np.testing.assert_array_equal(sched.tokens_per_expert.cpu().numpy(), ref["tokens_per_expert"])
+    N = int(ref["num_tokens"][0])
+    # dispatch is an exact copy
+    assert torch.equal(ctx.x_routed[:N].cpu(), ref["x_routed"])
+    tol = O.BF16_TOLERANCE
+    tight = (0.13, 4e-3)
+    for k in CTX_KEYS[1:]:
+        got = getattr(ctx, k)
+        r = ref[k]
+        assert_close(k, r, got[: r.shape[0]], tight)
+    assert_close("combine_buffer", ref["combine_buffer"], ws.combine_buffer, tight)
+    assert_close("output", ref["output"], out, tight)
+    for k, got in zip(GRAD_KEYS, grads):
+        assert_close(k, ref[k], got, tol)
+        mx, rel = O.error_stats(ref[k], got.cpu())
+        assert rel < 8e-3, (k, rel)
+
+
+@pytest.mark.parametrize("case", G.LAYER_CASES[:2], ids=lambda c: c[0])
+def test_layer_bf16_vs_reference_golden(case):
+    golden = np.load(os.path.join(HERE, "golden", "layer_golden.npz"))
+    name, R, T, H, I, E, K, routing, limit = case
+    ranks = O.make_inputs(R=R, T=T, H=H, I=I, E=E, K=K, seed=5, routing=routing)
+    sched, out, ctx, _, grads, ws = run_layer(ranks[0], E, limit=limit)
+    got = dict(zip(GRAD_KEYS, grads), output=out)
+    for k in G.LAYER_OUT:
+        ref = golden[f"layer_{name}_rank0_{k}"]
+        ref = torch.from_numpy(ref) if ref.dtype == np.float32 else torch.from_numpy(ref.view(np.int16).copy()).view(torch.bfloat16)
+        g = got[k]
+        if k.startswith("d_w_routed"):
+            g = g[:, ::4]
+        assert_close(k, ref, g, O.BF16_TOLERANCE)
+
+
+def test_recompute_is_bit_identical_and_runs_are_deterministic():
+    ranks = O.make_inputs(R=1, T=512, H=512, I=256, E=8, K=4, seed=11, routing="gaussian")
+    s1, out1, ctx1, ctx1b, g1, _ = run_layer(ranks[0], 8, recompute=True)
+    s2, out2, ctx2, _, g2, _ = run_layer(ranks[0], 8)
+    N = int(s1.num_tokens.item())
+    for k in CTX_KEYS:
+        a, b, c = getattr(ctx1, k), getattr(ctx1b, k), getattr(ctx2, k)
+        n = N if a.shape[0] != 512 else 512
+        assert torch.equal(a[:n], b[:n]), f"recompute differs from forward on {k}"
+        assert torch.equal(a[:n], c[:n]), f"two runs differ on {k}"
+    assert torch.equal(out1, out2)
+    for a, b in zip(g1, g2):
+        assert torch.equal(a, b)
+
+
+def test_macrobatch_too_small_is_reported_not_fatal():
+    from mok import _C, functional as F
+    ranks = O.make_inputs(R=1, T=512, H=256, I=256, E=4, K=2, seed=3, routing="gaussian")
+    group = init_single_rank_group()
+    inp = to_dev(ranks[0])
+    cfg = F.MoKConfig(minibatch_size=256, macrobatch_size=512)
+    ws = F.get_workspace(cfg, group, device=torch.device("cuda", 0), num_local_tokens=512, hidden_size=256, topk=2)
+    sched = F.build_schedule(ws, cfg, inp.top_experts, num_local_experts=4)
+    F.forward(cfg, ws, sched, inp.x, inp.router_weights, inp.w_shared_gate, inp.w_shared_up, inp.w_shared_down,
+              inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down)
+    torch.cuda.synchronize()
+    assert _C.check_status() == _C.ST_MACROBATCH_OVERFLOW
