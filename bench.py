@@ -1,0 +1,380 @@
+"""Benchmark of the MoE layer hot path: build_schedule + forward + backward per step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c5|small]
+
+For N > 1 launch under torch.distributed.run with one rank per GPU (RANK / LOCAL_RANK /
+WORLD_SIZE / MASTER_* from the environment).  Rank 0 prints ONE JSON line.
+
+Workload (default "c2"): 16384 tokens per rank, hidden 7168, 256 routed experts in total
+(256 / N per rank) + one shared expert, top-8, expert width 2048 SwiGLU, balanced Gaussian
+routing, BF16, minibatch 8192, capacity multiplier 0.5 -- synthetic data of that shape.
+Per-GPU work is fixed as N grows (weak scaling).
+
+  value      tokens/s over all ranks with the step's inputs already resident in HBM
+  e2e        the same through mok.functional with the inputs in pinned HOST memory: host->device
+             copies of x, top_experts, router_weights, grad_output and a device->host read of
+             the result checksums are inside the timed region
+  roofline   the dominant kernel (routed gate/up grouped GEMM with fused SwiGLU): algorithmic
+             FLOPs per launch / its mean launch time (CUDA events, timed alone) over the
+             measured cuBLAS BF16 burst peak of this pool (MEASURED_PEAKS.json)
+  cpu_baseline  the CPU oracle (a port of the reference's PyTorch path) on a bounded sample
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "mixture-of-kittens_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+WORKLOADS = {
+    # name: (tokens per rank, hidden, intermediate, total experts, topk, minibatch, capacity multiplier, routing)
+    "c2": (16384, 7168, 2048, 256, 8, 8192, 0.5, "gaussian"),
+    "c1": (1024, 1024, 512, 8, 2, 256, 0.5, "router"),
+    "c4": (16384, 4096, 1536, 128, 8, 8192, 1.0, "zipf"),
+    "c5": (16384, 5120, 1408, 64, 6, 8192, 0.5, "gaussian"),
+    "small": (4096, 2048, 1024, 32, 4, 2048, 0.5, "gaussian"),   # for profiler captures: a few GB on the device
+}
+METRIC = "moe_layer_fwd_bwd_tokens_per_s"
+
+
+def layer_flops(T, K, H, I):
+    """fwd + bwd algorithmic FLOPs per rank: 18 * T * (K + 1) * H * I (shared expert included,
+    padding and replay not counted) -- the reference's formula, benchmarks/utils.py:19-23."""
+    return 18.0 * T * (K + 1) * H * I
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_oracle_sample(H, I, K, threads_note=True):
+    """One fwd+bwd of the CPU oracle on a bounded sample with the workload's per-token cost:
+    512 tokens, K experts, top-K = K (every token visits K experts + the shared one)."""
+    from oracle import mok_oracle as O
+    Ts, Es = 512, K
+    ranks = O.make_inputs(R=1, T=Ts, H=H, I=I, E=Es, K=K, seed=0, routing="gaussian")
+    t0 = time.perf_counter()
+    O.layer_forward_backward(ranks)
+    dt = time.perf_counter() - t0
+    return Ts, Es, dt
+
+
+def run_reference_arm(args, rank, world):
+    """The reference's CPU implementation of the path (the oracle port of its PyTorch code) on
+    the host cores: rank 0 only."""
+    if rank != 0:
+        return
+    T, H, I, E, K, mb, mult, routing = WORKLOADS[args.workload]
+    times = []
+    for i in range(args.warmup + args.steps):
+        Ts, Es, dt = cpu_oracle_sample(H, I, K)
+        if i >= args.warmup:
+            times.append(dt)
+    ms = 1000.0 * sum(times) / len(times)
+    value = Ts / (ms / 1000.0)
+    cores = torch.get_num_threads()
+    sample = f"{Ts} tokens x top-{K} over {Es} experts + shared expert, H={H}, I={I}, fwd+bwd (same FLOPs per token as the workload)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.workload, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def workload_config(name, n):
+    T, H, I, E, K, mb, mult, routing = WORKLOADS[name]
+    return {"workload": f"{name}: MoE layer fwd+bwd, {T} tokens/rank, hidden {H}, {E} routed experts ({E // n}/rank) + 1 shared, "
+                        f"top-{K}, expert width {I} SwiGLU, {routing} routing, EP={n}",
+            "tokens_per_rank": T, "hidden": H, "intermediate": I, "experts": E, "topk": K, "minibatch_size": mb,
+            "schedule_capacity_multiplier": mult, "ep_size": n, "l2": "inputs_larger_than_l2"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true", help="time only the dominant GEMM (profiler captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if not args.kernel_only else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+
+    from mok import _C, functional as F
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29551")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    group = dist.group.WORLD
+
+    T, H, I, E, K, mb, mult, routing = WORKLOADS[args.workload]
+    assert E % world == 0
+    E_l = E // world
+    MB = int(math.ceil((T * K + E_l * 256) / mb) * mb)
+    cfg = F.MoKConfig(minibatch_size=mb, macrobatch_size=MB, schedule_capacity_multiplier=mult)
+
+    # ---- synthetic inputs: per-step tensors in pinned host memory + device copies; weights on the device
+    g = torch.Generator().manual_seed(1000 + rank)
+    x_h = torch.randn(T, H, generator=g).to(torch.bfloat16).pin_memory()
+    gy_h = torch.randn(T, H, generator=g).to(torch.bfloat16).pin_memory()
+    logits = torch.randn(T, E, generator=g)
+    if routing == "zipf":
+        perm = torch.randperm(E, generator=torch.Generator().manual_seed(7))
+        bias = torch.empty(E)
+        bias[perm] = -1.2 * torch.log(torch.arange(1, E + 1, dtype=torch.float32))
+        logits = logits + bias
+    vals, idx = torch.topk(logits, K, dim=1)
+    te_h = idx.to(torch.int64).pin_memory()
+    rw_h = torch.softmax(vals.float(), -1).pin_memory()
+    gd = torch.Generator(device=device).manual_seed(2000 + rank)
+
+    def w(*shape):
+        t = torch.empty(*shape, dtype=torch.bfloat16, device=device)
+        t.normal_(0.0, 0.02, generator=gd)
+        return t
+    wsg, wsu, wsd = w(I, H), w(I, H), w(H, I)
+    wrg, wru, wrd = w(E_l, I, H), w(E_l, I, H), w(E_l, H, I)
+    x_d, gy_d, te_d, rw_d = (t.to(device) for t in (x_h, gy_h, te_h, rw_h))
+    ws = F.get_workspace(cfg, group, device=device, num_local_tokens=T, hidden_size=H, topk=K)
+
+    marks = {}
+
+    def step(x, te, rw, gy, mark=False):
+        sched = F.build_schedule(ws, cfg, te, num_local_experts=E_l)
+        out, ctx = F.forward(cfg, ws, sched, x, rw, wsg, wsu, wsd, wrg, wru, wrd)
+        if mark:
+            marks["mid"].record()
+        grads = F.backward(cfg, ws, sched, ctx, gy, x, rw, wsg, wsu, wsd, wrg, wru, wrd)
+        return sched, out, grads
+
+    def timed(fn, steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([start.elapsed_time(end)], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if args.kernel_only:
+        sched, _, _ = step(x_d, te_d, rw_d, gy_d)
+        torch.cuda.synchronize()
+        kern = time_dominant_kernel(_C, sched, x_d, wrg, wru, T, H, I, K, E_l, MB, args.steps, args.warmup, device)
+        if rank == 0:
+            print(json.dumps({"kernel_only": True, **kern}), flush=True)
+        dist.destroy_process_group()
+        return
+
+    # ---- device-resident steps
+    for _ in range(args.warmup):
+        step(x_d, te_d, rw_d, gy_d)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0, "device status word set during warm-up"
+    launches_before = _C.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        total_ms = timed(lambda: step(x_d, te_d, rw_d, gy_d), args.steps)
+    launches = _C.launch_count() - launches_before
+    clock_summary = clocks.summary()
+    ms_per_step = total_ms / args.steps
+
+    # forward / backward split (one extra measured step each, events on the same stream)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    marks["mid"] = ev[1]
+    fwd_ms, bwd_ms = [], []
+    for _ in range(max(2, args.steps // 2)):
+        torch.cuda.synchronize()
+        ev[0].record()
+        step(x_d, te_d, rw_d, gy_d, mark=True)
+        ev[2].record()
+        torch.cuda.synchronize()
+        fwd_ms.append(ev[0].elapsed_time(ev[1]))
+        bwd_ms.append(ev[1].elapsed_time(ev[2]))
+
+    # ---- end to end: inputs start in pinned host memory, result checksums come back to the host
+    x_e, gy_e, te_e, rw_e = (torch.empty_like(t, device=device) for t in (x_h, gy_h, te_h, rw_h))
+    res_h = torch.empty(2, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        x_e.copy_(x_h, non_blocking=True)
+        te_e.copy_(te_h, non_blocking=True)
+        rw_e.copy_(rw_h, non_blocking=True)
+        gy_e.copy_(gy_h, non_blocking=True)
+        _, out, grads = step(x_e, te_e, rw_e, gy_e)
+        res = torch.stack([out.float().sum(), grads[0].float().sum()])
+        res_h.copy_(res, non_blocking=True)
+        torch.cuda.current_stream().synchronize()     # the caller consumes the result on the host
+    for _ in range(2):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps) / args.steps
+    h2d = sum(t.numel() * t.element_size() for t in (x_h, te_h, rw_h, gy_h))
+    assert _C.check_status() == 0, "device status word set during the timed region"
+
+    # ---- roofline of the dominant kernel
+    sched, _, _ = step(x_d, te_d, rw_d, gy_d)
+    kern = time_dominant_kernel(_C, sched, x_d, wrg, wru, T, H, I, K, E_l, MB, 5, 2, device)
+    peak_tf, peak_gbs, peak_kind = measured_peaks()
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            tj = json.load(f)
+        per_flop = tj.get("gate_up_gemm_dram_bytes_per_algorithmic_flop")
+        if per_flop:
+            traffic = per_flop * kern["flops_per_launch"]
+    roofline = {"bound": "tensor", "kernel": "grouped_gemm_kernel<MODE_SWIGLU> (routed gate/up + SwiGLU)",
+                "achieved": kern["tflops"], "peak": peak_tf, "unit": "TFLOP/s", "frac": kern["tflops"] / peak_tf,
+                "peak_source": f"{peak_kind} cuBLAS bf16 burst", "traffic": traffic,
+                "launch_ms": kern["ms"], "flops_per_launch": kern["flops_per_launch"]}
+
+    if rank == 0:
+        tokens = T * world
+        flops = layer_flops(T, K, H, I)
+        line = {
+            "metric": METRIC, "value": tokens / (ms_per_step / 1000.0), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args.workload, world),
+            "tokens_per_s_per_gpu": T / (ms_per_step / 1000.0),
+            "tflops_per_gpu": flops / (ms_per_step / 1000.0) / 1e12,
+            "fwd_ms": statistics.median(fwd_ms), "bwd_ms": statistics.median(bwd_ms),
+            "roofline": roofline,
+            "e2e": {"value": tokens / (e2e_ms / 1000.0), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": 8, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches),
+            "clocks": clock_summary,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            Ts, Es, dt = cpu_oracle_sample(H, I, K)
+            line["cpu_baseline"] = {
+                "value": Ts / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                "sample": f"{Ts} tokens x top-{K} over {Es} experts + shared expert, H={H}, I={I}, one fwd+bwd of the CPU oracle "
+                          f"({dt:.1f} s; same FLOPs per token as the workload)"}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
+def time_dominant_kernel(_C, sched, x, wrg, wru, T, H, I, K, E_l, MB, steps, warmup, device):
+    """Times the routed gate/up + SwiGLU grouped GEMM alone, on this step's real schedule."""
+    tpe = sched.tokens_per_expert
+    offs = torch.cat([torch.zeros(1, dtype=torch.int64, device=device), tpe.to(torch.int64).cumsum(0)])
+    gob = torch.repeat_interleave(torch.arange(E_l, device=device, dtype=torch.int32), (tpe // 128).to(torch.int64))
+    gob = torch.cat([gob, torch.full((MB // 128 - gob.numel(),), -1, dtype=torch.int32, device=device)])
+    x_routed = torch.empty(MB, H, dtype=torch.bfloat16, device=device)
+    _C.dispatch_rows([x.data_ptr()], sched.peer_rank, sched.peer_token_idx, sched.num_tokens, MB, K, H, x_routed)
+    gate, up, hid = (torch.empty(MB, I, dtype=torch.bfloat16, device=device) for _ in range(3))
+
+    def launch():
+        _C.grouped_gemm(1, x_routed, wrg, gate, rows=MB, num_rows=sched.num_tokens, group_of_block=gob, G=E_l, N=I, K=H,
+                        B2=wru, D2=up, D3=hid)
+    for _ in range(warmup):
+        launch()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        launch()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    real_rows = int((sched.peer_rank >= 0).sum().item())
+    flops = 4.0 * real_rows * H * I              # 2 GEMMs x 2 * rows * H * I, padding rows not counted
+    padded = int(sched.num_tokens.item())
+    return {"ms": ms, "flops_per_launch": flops, "tflops": flops / (ms / 1000.0) / 1e12,
+            "rows": real_rows, "padded_rows": padded}
+
+
+if __name__ == "__main__":
+    main()

@@ -46,13 +46,14 @@ def run_layer(inp_cpu, E_l, *, limit=None, MB=None, mb=256, recompute=False, mul
     dict(T=512, H=256, I=256, E=4, K=2, routing="router", limit=None),
     dict(T=1024, H=1024, I=512, E=8, K=2, routing="router", limit=None),     # config 1 of the benchmark
     dict(T=512, H=512, I=384, E=6, K=3, routing="gaussian", limit=2.0),      # I not a multiple of 256, clamped
-    dict(T=512, H=256, I=128, E=16, K=1, routing="zipf", limit=None),        # empty experts likely, top-1
+    dict(T=512, H=256, I=128, E=16, K=1, routing="zipf", limit=None, mult=9.0, MB=4608),   # mostly padding, top-1
 ], ids=["min", "c1", "i384_clamp", "zipf_top1"])
 def test_layer_bf16_vs_oracle(shape):
-    limit = shape.pop("limit")
+    shape = dict(shape)
+    limit, mult, MB = shape.pop("limit"), shape.pop("mult", 0.5), shape.pop("MB", None)
     ranks = O.make_inputs(R=1, seed=3, **shape)
-    ref = O.layer_forward_backward(ranks, swiglu_limit=limit)[0]
-    sched, out, ctx, _, grads, ws = run_layer(ranks[0], shape["E"], limit=limit)
+    ref = O.layer_forward_backward(ranks, swiglu_limit=limit, schedule_capacity_factor=max(2, int(mult)))[0]
+    sched, out, ctx, _, grads, ws = run_layer(ranks[0], shape["E"], limit=limit, mult=mult, MB=MB)
     # schedule: bit exact
     np.testing.assert_array_equal(sched.peer_rank.cpu().numpy(), ref["peer_rank"])
     np.testing.assert_array_equal(sched.peer_token_idx.cpu().numpy(), ref["peer_token_idx"])
