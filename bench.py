@@ -250,7 +250,7 @@ def main():
         return float(t.item())
 
     if args.kernel_only:
-        sched, _, _ = step(x_d, te_d, rw_d, gy_d)
+        sched = F.build_schedule(ws, cfg, te_d, num_local_experts=E_l)
         torch.cuda.synchronize()
         kern = time_dominant_kernel(_C, sched, x_d, wrg, wru, T, H, I, K, E_l, MB, args.steps, args.warmup, device)
         if rank == 0:

@@ -207,6 +207,29 @@ def test_dispatch_and_combine_rows_single_rank(mods):
     assert torch.equal(vals.cpu(), inv)
 
 
+def test_barrier_wait_is_bounded_and_reports_through_the_status_word(mods):
+    # failure made on the host: a 2-rank pointer list whose second "rank" is a local word nobody signals from,
+    # so this rank's own word only ever receives its own arrival.  The wait must give up and set the status.
+    _C, ops = mods
+    mine = torch.zeros(1, dtype=torch.int32, device="cuda")
+    other = torch.zeros(1, dtype=torch.int32, device="cuda")
+    target = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _C.set_barrier_timeout_ms(200)
+    try:
+        _C.barrier_all(mine, [mine.data_ptr(), other.data_ptr()], 0, target, rank=0)
+        torch.cuda.synchronize()
+        assert _C.check_status() == _C.ST_BARRIER_TIMEOUT
+        assert int(target.item()) == 2 and int(mine.item()) == 1 and int(other.item()) == 1
+        # the context is still usable and a complete barrier (both arrivals present) passes
+        other2 = torch.zeros(1, dtype=torch.int32, device="cuda")
+        mine.fill_(3)          # as if the peer had already arrived for the next round
+        _C.barrier_all(mine, [mine.data_ptr(), other2.data_ptr()], 0, target, rank=0)
+        torch.cuda.synchronize()
+        assert _C.check_status() == 0
+    finally:
+        _C.set_barrier_timeout_ms(10000)
+
+
 # ------------------------------------------------------------------ grouped GEMM, all four operand layouts
 def _groups(rows_per_group):
     offs = np.concatenate([[0], np.cumsum(rows_per_group)]).astype(np.int32)
