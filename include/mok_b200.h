@@ -81,6 +81,27 @@ int mokb_schedule(const int32_t* topk_all, int ep_size, int num_local_tokens, in
                   int32_t* peer_rank, int32_t* peer_token_idx, int32_t* num_tokens,
                   int32_t* tokens_per_expert, void* scratch, int32_t* status, void* stream);
 
+/* ---- routing schedule without device allocation.  No counterpart in the reference.
+ * For callers that cannot allocate device memory around the call -- a host framework that
+ * owns the device heap through its own pool, a step loop where cudaMalloc's implicit
+ * synchronisation is unaffordable, a process that commits all its memory at start-up:
+ * same inputs, outputs and result as mokb_schedule, but the work area is a fixed array
+ * inside the library image (4 MiB + 16 KiB, resident on every GPU that loads the library,
+ * until the process exits) instead of caller-provided scratch.  The caller still passes all
+ * inputs and outputs.  The call makes no cudaMalloc / cudaFree and uses no allocating routine.
+ *   - Limit: ep_size * num_local_experts <= MOKB_SCHEDULE_NOALLOC_MAX_EXPERTS; beyond it the
+ *     call fails with MOKB_ERR_INVALID and a message that names the limit.
+ *   - The first call on a device looks up the array's device address (once per device, with
+ *     that device current); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array and find in it what the last call left; the
+ *     entry point clears the part that must start at zero.  Two calls whose kernels overlap
+ *     on the GPU (different streams, or different host threads) race on it: serialise them. */
+#define MOKB_SCHEDULE_NOALLOC_MAX_EXPERTS 1024
+int mokb_schedule_noalloc(const int32_t* topk_all, int ep_size, int num_local_tokens, int topk,
+                          int num_local_experts, int schedule_capacity, int rank,
+                          int32_t* peer_rank, int32_t* peer_token_idx, int32_t* num_tokens,
+                          int32_t* tokens_per_expert, int32_t* status, void* stream);
+
 /* ---- MXFP8 quantiser: replaces `_C.mxfp8_quantize` (csrc/mxfp8.cuh:234-278).
  * x [E, M, N] bf16 (E = 1 for a matrix); outputs may be NULL pairwise:
  * fp8 [E, M, N] + sc [E*M/128, N/128, 32, 16]; fp8_t [E, N, M] + sc_t [E*N/128, M/128, 32, 16]. */

@@ -250,3 +250,105 @@ extern "C" int mokb_schedule(const int32_t* topk_all, int ep_size, int num_local
     note_launch(4);
     return MOKB_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Routing schedule for callers that must not allocate device memory.
+//
+// Some hosts of this library run where cudaMalloc is off limits: inside a
+// framework that owns the whole device heap through its own pool, in a
+// latency-critical step loop where an allocation would serialise the device,
+// or in a process that pre-commits all memory at start-up.  For them the work
+// area of the schedule builder lives in the library image itself: a fixed
+// __device__ array that every GPU loading the library carries until exit.
+// The price is a size limit and shared state (see the header).
+namespace mokb {
+namespace {
+
+constexpr size_t kStaticHeadBytes = 16u << 10;     // cnt[E] + base[E_l + 1] + overflow flag
+constexpr size_t kStaticColcntBytes = 4u << 20;    // colcnt[E][1024 * RC]: E * RC <= 1024
+static __device__ __align__(256) unsigned char g_static_sched_scratch[kStaticHeadBytes + kStaticColcntBytes];
+
+// Device address of the array above, per device.  In host code the array's name is only a
+// handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress,
+// asked for with that device current.
+void* g_static_sched_ptr[64] = {nullptr};
+
+int static_sched_scratch(void** out) {
+    int dev = -1;
+    MOKB_CUDA(cudaGetDevice(&dev));
+    MOKB_REQUIRE(dev >= 0 && dev < 64, "schedule_noalloc: device index %d out of range", dev);
+    if (g_static_sched_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        MOKB_CUDA(cudaGetSymbolAddress(&p, g_static_sched_scratch));
+        MOKB_REQUIRE(p != nullptr, "schedule_noalloc: cudaGetSymbolAddress returned a null address");
+        g_static_sched_ptr[dev] = p;
+    }
+    *out = g_static_sched_ptr[dev];
+    return MOKB_OK;
+}
+
+}  // namespace
+}  // namespace mokb
+
+extern "C" int mokb_schedule_noalloc(const int32_t* topk_all, int ep_size, int num_local_tokens, int topk,
+                                     int num_local_experts, int schedule_capacity, int rank,
+                                     int32_t* peer_rank, int32_t* peer_token_idx, int32_t* num_tokens,
+                                     int32_t* tokens_per_expert, int32_t* status, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    MOKB_REQUIRE(topk_all && peer_rank && peer_token_idx && num_tokens && tokens_per_expert && status,
+                 "schedule_noalloc: null pointer");
+    MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "schedule_noalloc: ep_size %d out of range", ep_size);
+    MOKB_REQUIRE(rank >= 0 && rank < ep_size, "schedule_noalloc: rank %d not in [0, %d)", rank, ep_size);
+    MOKB_REQUIRE(num_local_tokens > 0 && topk > 0 && num_local_experts > 0, "schedule_noalloc: sizes must be positive");
+    MOKB_REQUIRE(schedule_capacity > 0 && schedule_capacity % kPad == 0,
+                 "schedule_noalloc: capacity must be a positive multiple of 256");
+    const long long routes_ll = 1LL * num_local_tokens * topk;
+    MOKB_REQUIRE(routes_ll * ep_size < (1LL << 31), "schedule_noalloc: too many routes");
+    const size_t E = static_cast<size_t>(ep_size) * num_local_experts;
+    MOKB_REQUIRE(E <= MOKB_SCHEDULE_NOALLOC_MAX_EXPERTS,
+                 "schedule_noalloc: ep_size * num_local_experts = %zu exceeds the built-in work area's limit of %d experts; "
+                 "use mokb_schedule with caller-provided scratch", E, MOKB_SCHEDULE_NOALLOC_MAX_EXPERTS);
+    MOKB_REQUIRE(static_cast<size_t>(num_local_experts) * 32 * 4 <= 160 * 1024, "schedule_noalloc: too many local experts");
+
+    void* scratch = nullptr;
+    MOKB_TRY(static_sched_scratch(&scratch));
+
+    SchedParams p;
+    p.topk_all = topk_all;
+    p.R = ep_size; p.routes = static_cast<int>(routes_ll); p.E_l = num_local_experts;
+    p.C = schedule_capacity; p.rank = rank;
+    int cpb;
+    sched_geometry(p.R, p.routes, p.E_l, &p.RC, &p.rows_per_chunk, &cpb);
+    // fewer row chunks per column until colcnt fits the fixed area (the result does not depend on RC)
+    while (p.RC > 1 && E * kThreadsOrder * p.RC * 4 > kStaticColcntBytes) p.RC /= 2;
+    const int P = (p.routes + kThreadsOrder - 1) / kThreadsOrder;
+    p.rows_per_chunk = (P + p.RC - 1) / p.RC;
+    p.V = kThreadsOrder * p.RC;
+    MOKB_REQUIRE(E * p.V * 4 <= kStaticColcntBytes && (E + p.E_l + 2) * 4 <= kStaticHeadBytes,
+                 "schedule_noalloc: problem does not fit the built-in work area");
+    int32_t* s = static_cast<int32_t*>(scratch);
+    p.cnt = s;
+    p.base = s + E;
+    p.overflow = p.base + p.E_l + 1;
+    p.colcnt = reinterpret_cast<int32_t*>(static_cast<char*>(scratch) + kStaticHeadBytes);
+    p.peer_rank = peer_rank; p.peer_token_idx = peer_token_idx;
+    p.num_tokens = num_tokens; p.tokens_per_expert = tokens_per_expert; p.status = status;
+
+    // the area keeps whatever the previous call left: the counters and the overflow flag must start at zero
+    // (colcnt is fully rewritten by the counting pass before anything reads it)
+    MOKB_CUDA(cudaMemsetAsync(scratch, 0, kStaticHeadBytes, stream));
+    MOKB_CUDA(cudaMemsetAsync(peer_rank, 0xFF, static_cast<size_t>(schedule_capacity) * 4, stream));
+    MOKB_CUDA(cudaMemsetAsync(peer_token_idx, 0xFF, static_cast<size_t>(schedule_capacity) * 4, stream));
+
+    const size_t smem = (static_cast<size_t>(p.E_l) * cpb + E + p.E_l) * 4;
+    MOKB_CUDA(cudaFuncSetAttribute(walk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    MOKB_CUDA(cudaFuncSetAttribute(walk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    const dim3 grid(p.V / cpb, p.R);
+    walk_kernel<false><<<grid, cpb, smem, stream>>>(p);
+    finalize_kernel<<<1, 1024, 0, stream>>>(p);
+    scan_kernel<<<static_cast<unsigned>(E), 1024, 0, stream>>>(p);
+    walk_kernel<true><<<grid, cpb, smem, stream>>>(p);
+    MOKB_CUDA(cudaGetLastError());
+    note_launch(4);
+    return MOKB_OK;
+}

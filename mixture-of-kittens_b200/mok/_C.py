@@ -91,6 +91,7 @@ _sig("mokb_all_gather_top_experts", c_int, c_vp, c_u64p, c_int, c_int, c_i64, c_
 _sig("mokb_barrier_all", c_int, c_u64p, c_int, c_int, c_vp, c_vp, c_vp)
 _sig("mokb_schedule_scratch_bytes", c_sz, c_int, c_int)
 _sig("mokb_schedule", c_int, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp)
+_sig("mokb_schedule_noalloc", c_int, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp)
 _sig("mokb_mxfp8_quantize", c_int, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp)
 _sig("mokb_fwd_epilogue", c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_vp)
 _sig("mokb_bwd_epilogue", c_int, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_vp)
@@ -105,7 +106,7 @@ _sig("mokb_swiglu_bwd", c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c
 
 EXPORTED = [
     "mokb_last_error", "mokb_device_arch", "mokb_sm_count", "mokb_struct_sizes", "mokb_set_barrier_timeout_ms", "mokb_launch_count",
-    "mokb_all_gather_top_experts", "mokb_barrier_all", "mokb_schedule_scratch_bytes", "mokb_schedule",
+    "mokb_all_gather_top_experts", "mokb_barrier_all", "mokb_schedule_scratch_bytes", "mokb_schedule", "mokb_schedule_noalloc",
     "mokb_mxfp8_quantize", "mokb_fwd_epilogue", "mokb_bwd_epilogue", "mokb_layer_scratch_bytes",
     "mokb_dispatch_mlp_swiglu_combine_fwd_bf16", "mokb_dispatch_mlp_swiglu_combine_bwd_bf16",
     "mokb_grouped_gemm_bf16", "mokb_dispatch_rows", "mokb_combine_rows", "mokb_swiglu_fwd", "mokb_swiglu_bwd",
@@ -213,6 +214,16 @@ def schedule(topk_all, num_local_experts, schedule_capacity, rank):
                           _p(peer_rank), _p(peer_token_idx), _p(num_tokens), _p(tokens_per_expert),
                           _p(scratch), _p(status_tensor(dev)), _stream()))
     return peer_rank, peer_token_idx, num_tokens, tokens_per_expert
+
+
+def schedule_noalloc(topk_all, num_local_experts, schedule_capacity, rank, peer_rank, peer_token_idx, num_tokens,
+                     tokens_per_expert):
+    """The schedule through the entry point that allocates nothing: the caller hands in all four outputs,
+    and the work area is the library's built-in array (limit: 1024 experts over all ranks)."""
+    ep_size, T, K = topk_all.shape
+    _ck(lib.mokb_schedule_noalloc(_p(topk_all), ep_size, T, K, num_local_experts, schedule_capacity, rank,
+                                  _p(peer_rank), _p(peer_token_idx), _p(num_tokens), _p(tokens_per_expert),
+                                  _p(status_tensor(topk_all.device)), _stream()))
 
 
 def mxfp8_quantize(x_bf16, return_normal, return_transposed):
