@@ -1,15 +1,23 @@
 // Grouped BF16 GEMM for the expert FFN, forward and backward, on the 5th-gen
 // tensor cores: tcgen05.mma with the fp32 accumulator in tensor memory, operands
-// staged in 128B-swizzled shared memory by TMA, and a persistent, warp-specialised
-// CTA per SM.
+// staged in 128B-swizzled shared memory by TMA, and persistent, warp-specialised
+// CTAs.
 //
-//   warp 0      TMA producer   (one elected lane)  : global -> smem ring, 4 stages of 48 KB
-//   warp 1      MMA issuer     (one elected lane)  : 4 x tcgen05.mma (128 x 256 x 16) per stage
-//   warps 2..5  epilogue                           : TMEM -> registers -> bf16 -> global
+//   warp 0      TMA producer   (one lane)  : global -> smem ring
+//   warp 1      MMA issuer     (one lane)  : 4 x tcgen05.mma (K = 16 each) per 64-wide K stage
+//   warps 2..5  epilogue                   : TMEM -> registers -> bf16 -> global
 //
-// The 512 TMEM columns hold two 128x256 fp32 accumulators, so the epilogue of
-// tile i overlaps the main loop of tile i+1 (the reference keeps a single
-// accumulator per CTA, csrc/megakernel/forward.cuh:84).
+// Two tile shapes share the code (template parameter NCTA):
+//   NCTA = 2  a pair of CTAs on neighbouring SMs (cluster of 2, tcgen05 cta_group::2) computes a
+//             256 x 256 tile.  Each CTA stages 128 rows of A and 128 of the 256 B columns
+//             (32 KB per stage, 6 stages), the even CTA issues 256 x 256 x 16 MMAs that read both
+//             CTAs' shared memory, and each CTA holds and drains its own 128 rows of the
+//             accumulator.  Per SM this needs a third less operand traffic than a 128 x 256
+//             tile per CTA, which is what bounds the single-CTA form.  Every CTA loads only its
+//             own half-tiles; barriers are signalled across the pair.
+//   NCTA = 1  one CTA per 128 x 256 tile (48 KB per stage, 4 stages).
+// The 512 TMEM columns hold two accumulators, so the epilogue of tile i overlaps the main loop
+// of tile i+1 (the reference keeps a single accumulator per CTA, csrc/megakernel/forward.cuh:84).
 //
 // One kernel template covers the operand layouts the layer needs
 // (reference: csrc/megakernel/grouped_gemm.cuh:1-381):
@@ -17,24 +25,34 @@
 //   MODE_SWIGLU  gate,up = A * Wg[g]^T, A * Wu[g]^T; hidden = SwiGLU  (one 128+128 column tile)
 //   MODE_NN      D[rows,N] = A[rows,K] * W[g][K,N] (+ A2 * W2[g])    (input gradients)
 //   MODE_WGRAD   D[g][M,N] = A[rows_g,M]^T * B[rows_g,N]             (weight gradients)
-// Rows are grouped in blocks of 128 (expert segments are multiples of 256 rows),
-// so a tile never straddles two experts.
+// Expert segments are multiples of 256 rows, so a tile never straddles two experts.
+#include <stdlib.h>
+#include <string.h>
+
 #include "common.cuh"
 
 namespace mokb {
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2;            // 16 KB
-constexpr int B_BYTES = BN * BK * 2;            // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KB
+constexpr int BN = 256, BK = 64;
+constexpr int A_BYTES = 128 * BK * 2;           // 16 KB: 128 rows (or 2 x 64 columns) of A per CTA
 constexpr int CHUNK_BYTES = 64 * BK * 2;        // one 64-wide MN-major chunk: 8 KB
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int GROUP_M = 8;                      // m-blocks per raster super-group
-constexpr size_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int GROUP_ROWS = 1024;                // rows per raster super-group
 
 enum { MODE_NT = 0, MODE_SWIGLU = 1, MODE_NN = 2, MODE_WGRAD = 3 };
+
+template <int NCTA>
+struct Geo {
+    static constexpr int TILE_M = 128 * NCTA;
+    static constexpr int B_COLS = BN / NCTA;                 // B columns staged by one CTA
+    static constexpr int B_BYTES = B_COLS * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;    // 48 KB / 32 KB
+    static constexpr int STAGES = NCTA == 2 ? 6 : 4;
+    static constexpr int GROUP_M = GROUP_ROWS / TILE_M;
+    static constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
 
 struct KParams {
     int rows_cap;                    // static upper bound of rows
@@ -55,23 +73,26 @@ struct Tile {
     int m_blk, n_blk, group, k_iters, k_row0;
 };
 
-template <int MODE>
+template <int MODE, int NCTA>
 struct Sched {
     int m_blocks, n_blocks, total;
     __device__ Sched(const KParams& p) {
+        constexpr int TM = Geo<NCTA>::TILE_M;
         if (MODE == MODE_WGRAD) {
-            m_blocks = p.M / BM;
+            m_blocks = (p.M + TM - 1) / TM;
             n_blocks = (p.N + BN - 1) / BN;
             total = p.G * m_blocks * n_blocks;
         } else {
             int rows = p.num_rows ? *p.num_rows : p.rows_cap;
             if (rows < 0 || rows > p.rows_cap) rows = 0;
-            m_blocks = rows / BM;
+            m_blocks = rows / TM;
             n_blocks = MODE == MODE_SWIGLU ? p.N / 128 : (p.N + BN - 1) / BN;
             total = m_blocks * n_blocks;
         }
     }
     __device__ Tile get(const KParams& p, int t) const {
+        constexpr int TM = Geo<NCTA>::TILE_M;
+        constexpr int GM = Geo<NCTA>::GROUP_M;
         Tile ti;
         if (MODE == MODE_WGRAD) {
             const int per = m_blocks * n_blocks;
@@ -82,14 +103,14 @@ struct Sched {
             ti.k_row0 = p.group_offsets[ti.group];
             ti.k_iters = (p.group_offsets[ti.group + 1] - ti.k_row0) / BK;
         } else {
-            const int per = GROUP_M * n_blocks;
+            const int per = GM * n_blocks;
             const int sg = t / per;
-            const int first = sg * GROUP_M;
-            const int gsize = min(GROUP_M, m_blocks - first);
+            const int first = sg * GM;
+            const int gsize = min(GM, m_blocks - first);
             const int in = t - sg * per;
             ti.n_blk = in / gsize;
             ti.m_blk = first + (in - ti.n_blk * gsize);
-            ti.group = p.group_of_block ? p.group_of_block[ti.m_blk] : 0;
+            ti.group = p.group_of_block ? p.group_of_block[ti.m_blk * (TM / 128)] : 0;
             ti.k_row0 = 0;
             ti.k_iters = (p.K / BK) * (p.dual ? 2 : 1);
         }
@@ -113,11 +134,20 @@ __device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const uint32_t (
     }
 }
 
-template <int MODE>
+template <int NCTA>
+__device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* t, uint32_t bar, int c0, int c1) {
+    if (NCTA == 2) tma_load_2d_pair(dst, t, bar, c0, c1);
+    else tma_load_2d(dst, t, bar, c0, c1);
+}
+
+template <int MODE, int NCTA>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                     const KParams p) {
+    using G = Geo<NCTA>;
+    constexpr int STAGES = G::STAGES;
+    constexpr int STAGE_BYTES = G::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -133,15 +163,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta = NCTA == 2 ? cluster_ctarank() : 0u;     // 0 = leader of the pair
+    const int tile_id0 = NCTA == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int tile_stride = NCTA == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(full_bar(s), 1);        // leader's: one arrive.expect_tx by the leader's producer + all TMA bytes
+            mbar_init(empty_bar(s), 1);       // one commit arrival per use (sent to both CTAs of a pair)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 128);
+            mbar_init(tempty_bar(a), 4 * NCTA);   // leader's: one arrival per epilogue warp of the pair
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -156,74 +189,88 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
-        tmem_relinquish();
+        if (NCTA == 2) {
+            tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (NCTA == 2) cluster_sync_all();     // the peer's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_slot;
 
-    const Sched<MODE> sched(p);
+    const Sched<MODE, NCTA> sched(p);
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ TMA producer (both CTAs of a pair)
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < sched.total; t += gridDim.x) {
+            const int kh = p.K / BK;
+            for (int t = tile_id0; ok && t < sched.total; t += tile_stride) {
                 const Tile ti = sched.get(p, t);
-                const int kh = p.K / BK;
+                const int row0 = ti.m_blk * G::TILE_M + static_cast<int>(cta) * 128;    // this CTA's rows of A / D
                 for (int it = 0; it < ti.k_iters; ++it) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
-                    const uint32_t fb = full_bar(s);
-                    mbar_expect_tx(fb, STAGE_BYTES);
+                    const uint32_t fb_local = full_bar(s);
+                    const uint32_t fb = NCTA == 2 ? map_to_cta(fb_local, 0) : fb_local;
+                    if (cta == 0) mbar_expect_tx(fb_local, NCTA * STAGE_BYTES);
                     const uint32_t a_dst = smem_base + s * STAGE_BYTES;
                     const uint32_t b_dst = a_dst + A_BYTES;
+                    const int bcol0 = ti.n_blk * BN + static_cast<int>(cta) * G::B_COLS;    // this CTA's B columns
                     if (MODE == MODE_NT) {
-                        tma_load_2d(a_dst, &tmA, fb, it * BK, ti.m_blk * BM);
-                        tma_load_2d(b_dst, &tmB, fb, it * BK, ti.group * p.b_rows_per_group + ti.n_blk * BN);
+                        tma_tile<NCTA>(a_dst, &tmA, fb, it * BK, row0);
+                        tma_tile<NCTA>(b_dst, &tmB, fb, it * BK, ti.group * p.b_rows_per_group + bcol0);
                     } else if (MODE == MODE_SWIGLU) {
-                        tma_load_2d(a_dst, &tmA, fb, it * BK, ti.m_blk * BM);
+                        tma_tile<NCTA>(a_dst, &tmA, fb, it * BK, row0);
                         const int brow = ti.group * p.b_rows_per_group + ti.n_blk * 128;
-                        tma_load_2d(b_dst, &tmB, fb, it * BK, brow);
-                        tma_load_2d(b_dst + B_BYTES / 2, &tmB2, fb, it * BK, brow);
+                        if (NCTA == 2) {      // leader stages the gate columns, its peer the up columns
+                            tma_tile<NCTA>(b_dst, cta == 0 ? &tmB : &tmB2, fb, it * BK, brow);
+                        } else {
+                            tma_tile<NCTA>(b_dst, &tmB, fb, it * BK, brow);
+                            tma_tile<NCTA>(b_dst + G::B_BYTES / 2, &tmB2, fb, it * BK, brow);
+                        }
                     } else if (MODE == MODE_NN) {
                         const bool second = it >= kh;
                         const int kk = (second ? it - kh : it) * BK;
                         const CUtensorMap* ta = second ? &tmA2 : &tmA;
                         const CUtensorMap* tb = second ? &tmB2 : &tmB;
-                        tma_load_2d(a_dst, ta, fb, kk, ti.m_blk * BM);
+                        tma_tile<NCTA>(a_dst, ta, fb, kk, row0);
                         const int brow = ti.group * p.b_rows_per_group + kk;
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) tma_load_2d(b_dst + c * CHUNK_BYTES, tb, fb, ti.n_blk * BN + 64 * c, brow);
+                        for (int c = 0; c < G::B_COLS / 64; ++c) tma_tile<NCTA>(b_dst + c * CHUNK_BYTES, tb, fb, bcol0 + 64 * c, brow);
                     } else {
                         const int krow = ti.k_row0 + it * BK;
 #pragma unroll
-                        for (int c = 0; c < 2; ++c) tma_load_2d(a_dst + c * CHUNK_BYTES, &tmA, fb, ti.m_blk * BM + 64 * c, krow);
+                        for (int c = 0; c < 2; ++c) tma_tile<NCTA>(a_dst + c * CHUNK_BYTES, &tmA, fb, row0 + 64 * c, krow);
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) tma_load_2d(b_dst + c * CHUNK_BYTES, &tmB, fb, ti.n_blk * BN + 64 * c, krow);
+                        for (int c = 0; c < G::B_COLS / 64; ++c) tma_tile<NCTA>(b_dst + c * CHUNK_BYTES, &tmB, fb, bcol0 + 64 * c, krow);
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && cta == 0) {
             constexpr uint32_t a_mn = MODE == MODE_WGRAD ? 1u : 0u;
             constexpr uint32_t b_mn = (MODE == MODE_NN || MODE == MODE_WGRAD) ? 1u : 0u;
-            // instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 256
+            // instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128 per CTA, N = 256
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (a_mn << 15) | (b_mn << 16) |
-                                       (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+                                       (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(G::TILE_M >> 4) << 24);
             constexpr uint32_t a_step = a_mn ? (2048u >> 4) : (32u >> 4);   // descriptor advance per 16 elements of K
             constexpr uint32_t b_step = b_mn ? (2048u >> 4) : (32u >> 4);
+            constexpr uint16_t pair_mask = 0x3;
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
             int local = 0;
-            for (int t = blockIdx.x; ok && t < sched.total; t += gridDim.x, ++local) {
+            for (int t = tile_id0; ok && t < sched.total; t += tile_stride, ++local) {
                 const Tile ti = sched.get(p, t);
                 const int acc = local & 1;
                 const uint32_t acc_ph = (local >> 1) & 1u;
@@ -238,23 +285,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const uint64_t a_desc = a_mn ? make_smem_desc(a_addr, CHUNK_BYTES, 1024) : make_smem_desc(a_addr, 16, 1024);
                     const uint64_t b_desc = b_mn ? make_smem_desc(b_addr, CHUNK_BYTES, 1024) : make_smem_desc(b_addr, 16, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_bf16(d_tmem, a_desc + static_cast<uint64_t>(k * a_step), b_desc + static_cast<uint64_t>(k * b_step),
-                                  idesc, (it | k) != 0 ? 1u : 0u);
-                    umma_commit(empty_bar(s));          // frees the smem stage once these MMAs retire
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = a_desc + static_cast<uint64_t>(k * a_step);
+                        const uint64_t bd = b_desc + static_cast<uint64_t>(k * b_step);
+                        if (NCTA == 2) umma_bf16_pair(d_tmem, ad, bd, idesc, (it | k) != 0 ? 1u : 0u);
+                        else umma_bf16(d_tmem, ad, bd, idesc, (it | k) != 0 ? 1u : 0u);
+                    }
+                    // frees the smem stage (in both CTAs) once these MMAs retire
+                    if (NCTA == 2) umma_commit_pair(empty_bar(s), pair_mask);
+                    else umma_commit(empty_bar(s));
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit(tfull_bar(acc));            // accumulator complete -> epilogue
+                // accumulator complete -> epilogue warps (of both CTAs)
+                if (NCTA == 2) umma_commit_pair(tfull_bar(acc), pair_mask);
+                else umma_commit(tfull_bar(acc));
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------ epilogue (warps 2..5 of every CTA)
         const int quarter = warp & 3;                   // TMEM lanes [32q, 32q+32) belong to warps with id % 4 == q
-        const int row_in_tile = quarter * 32 + lane;
+        const int row_in_cta = quarter * 32 + lane;
         int local = 0;
         bool ok = true;
-        for (int t = blockIdx.x; ok && t < sched.total; t += gridDim.x, ++local) {
+        for (int t = tile_id0; ok && t < sched.total; t += tile_stride, ++local) {
             const Tile ti = sched.get(p, t);
             const int acc = local & 1;
             const uint32_t acc_ph = (local >> 1) & 1u;
@@ -262,8 +316,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
             const bool empty_k = ti.k_iters == 0;
+            const int row_in_tile = static_cast<int>(cta) * 128 + row_in_cta;
             if (MODE == MODE_SWIGLU) {
-                const size_t row = static_cast<size_t>(ti.m_blk) * BM + row_in_tile;
+                const size_t row = static_cast<size_t>(ti.m_blk) * G::TILE_M + row_in_tile;
                 const size_t off = row * p.ldd + static_cast<size_t>(ti.n_blk) * 128;
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
@@ -289,9 +344,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     store_row32(p.D3 + off + c * 32, h);
                 }
             } else {
+                const int tile_row = ti.m_blk * G::TILE_M + row_in_tile;
+                bool row_ok = true;
                 size_t row;
-                if (MODE == MODE_WGRAD) row = static_cast<size_t>(ti.group) * p.M + static_cast<size_t>(ti.m_blk) * BM + row_in_tile;
-                else row = static_cast<size_t>(ti.m_blk) * BM + row_in_tile;
+                if (MODE == MODE_WGRAD) {
+                    row_ok = tile_row < p.M;
+                    row = static_cast<size_t>(ti.group) * p.M + tile_row;
+                } else {
+                    row = static_cast<size_t>(tile_row);
+                }
                 __nv_bfloat16* dst = p.D + row * p.ldd + static_cast<size_t>(ti.n_blk) * BN;
                 const int cols_left = p.N - ti.n_blk * BN;
 #pragma unroll 1
@@ -302,14 +363,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = 0u;
                     } else {
-                        tmem_ld_32x32(t_addr + c * 32, r);
+                        tmem_ld_32x32(t_addr + c * 32, r);     // whole warp, also for rows that are not stored
                         tmem_ld_wait();
                     }
-                    store_row32(dst + c * 32, r);
+                    if (row_ok) store_row32(dst + c * 32, r);
                 }
             }
             tc_fence_before();
-            mbar_arrive(tempty_bar(acc));
+            __syncwarp();
+            if (lane == 0) {
+                if (NCTA == 2) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+                else mbar_arrive(tempty_bar(acc));
+            }
         }
     }
 
@@ -322,23 +387,54 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         while (clock64() - t0 < 2000000ull) __nanosleep(1000);
         __syncthreads();
     }
+    if (NCTA == 2) cluster_sync_all();     // the peer may still read this CTA's smem or signal its barriers until here
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        if (NCTA == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
-template <int MODE>
+template <int MODE, int NCTA>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2, const KParams& p,
            int tiles_upper_bound, cudaStream_t stream) {
-    MOKB_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-    int grid = sm_count();
-    if (tiles_upper_bound < grid) grid = tiles_upper_bound;
-    if (grid < 1) return MOKB_OK;
-    grouped_gemm_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(a, b, a2, b2, p);
-    MOKB_CUDA(cudaGetLastError());
+    constexpr size_t smem = Geo<NCTA>::SMEM_BYTES;
+    MOKB_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<MODE, NCTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int units = sm_count() / NCTA;                       // CTAs, or CTA pairs
+    if (tiles_upper_bound < units) units = tiles_upper_bound;
+    if (units < 1) return MOKB_OK;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(units * NCTA));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = NCTA;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MOKB_CUDA(cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<MODE, NCTA>, a, b, a2, b2, p));
     note_launch();
     return MOKB_OK;
+}
+
+// MOKB_GEMM_CTAS=1 selects the single-CTA tile (for comparison); the default is the CTA pair.
+int ctas_per_tile() {
+    static int v = 0;
+    if (v == 0) {
+        const char* e = getenv("MOKB_GEMM_CTAS");
+        v = (e && e[0] == '1') ? 1 : 2;
+    }
+    return v;
+}
+
+template <int MODE>
+int dispatch_launch(int ncta, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2,
+                    const KParams& p, int tiles, cudaStream_t stream) {
+    return ncta == 2 ? launch<MODE, 2>(a, b, a2, b2, p, tiles, stream) : launch<MODE, 1>(a, b, a2, b2, p, tiles, stream);
 }
 
 }  // namespace
@@ -352,7 +448,11 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     MOKB_REQUIRE(g->mode >= 0 && g->mode <= 3, "grouped_gemm: unknown mode %d", g->mode);
     MOKB_REQUIRE(g->A && g->B && g->D && g->status, "grouped_gemm: null pointer");
     MOKB_REQUIRE(g->G >= 1, "grouped_gemm: G must be >= 1");
-    MOKB_REQUIRE(g->rows_static >= 0 && g->rows_static % BM == 0, "grouped_gemm: rows must be a multiple of 128");
+    MOKB_REQUIRE(g->rows_static >= 0 && g->rows_static % 128 == 0, "grouped_gemm: rows must be a multiple of 128");
+    // row tiles of 256 need row counts in multiples of 256 (true for every tensor of the layer)
+    const int ncta = (ctas_per_tile() == 2 && g->rows_static % 256 == 0) ? 2 : 1;
+    const int TM = 128 * ncta;
+    const uint32_t b_box = static_cast<uint32_t>(BN / ncta);
     KParams p;
     memset(&p, 0, sizeof(p));
     p.rows_cap = g->rows_static;
@@ -372,49 +472,50 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     MOKB_REQUIRE((reinterpret_cast<uintptr_t>(g->D) & 15) == 0, "grouped_gemm: D not 16-byte aligned");
     if (g->rows_static == 0) return MOKB_OK;
     const uint64_t rows = static_cast<uint64_t>(g->rows_static);
+    const int m_tiles = g->rows_static / TM;
     CUtensorMap ta, tb, ta2, tb2;
-    memset(&ta2, 0, sizeof(ta2));
-    memset(&tb2, 0, sizeof(tb2));
     switch (g->mode) {
     case MODE_NT: {
         MOKB_REQUIRE(g->K > 0 && g->K % BK == 0 && g->N > 0 && g->N % BN == 0, "grouped_gemm NT: K %% 64 and N %% 256 must be 0");
-        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->K, rows, 2ull * g->lda, 64, BM));
-        MOKB_TRY(make_tmap_2d(&tb, g->B, 2, g->K, static_cast<uint64_t>(g->G) * g->N, 2ull * g->ldb, 64, BN));
+        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->K, rows, 2ull * g->lda, 64, 128));
+        MOKB_TRY(make_tmap_2d(&tb, g->B, 2, g->K, static_cast<uint64_t>(g->G) * g->N, 2ull * g->ldb, 64, b_box));
         p.b_rows_per_group = g->N;
         ta2 = ta; tb2 = tb;
-        return launch<MODE_NT>(ta, tb, ta2, tb2, p, (g->rows_static / BM) * (g->N / BN), stream);
+        return dispatch_launch<MODE_NT>(ncta, ta, tb, ta2, tb2, p, m_tiles * (g->N / BN), stream);
     }
     case MODE_SWIGLU: {
         MOKB_REQUIRE(g->K > 0 && g->K % BK == 0 && g->N > 0 && g->N % 128 == 0, "grouped_gemm SWIGLU: K %% 64 and N %% 128 must be 0");
         MOKB_REQUIRE(g->B2 && g->D2 && g->D3, "grouped_gemm SWIGLU: B2, D2, D3 required");
-        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->K, rows, 2ull * g->lda, 64, BM));
+        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->K, rows, 2ull * g->lda, 64, 128));
         MOKB_TRY(make_tmap_2d(&tb, g->B, 2, g->K, static_cast<uint64_t>(g->G) * g->N, 2ull * g->ldb, 64, 128));
         MOKB_TRY(make_tmap_2d(&tb2, g->B2, 2, g->K, static_cast<uint64_t>(g->G) * g->N, 2ull * g->ldb, 64, 128));
         p.b_rows_per_group = g->N;
         ta2 = ta;
-        return launch<MODE_SWIGLU>(ta, tb, ta2, tb2, p, (g->rows_static / BM) * (g->N / 128), stream);
+        return dispatch_launch<MODE_SWIGLU>(ncta, ta, tb, ta2, tb2, p, m_tiles * (g->N / 128), stream);
     }
     case MODE_NN: {
         MOKB_REQUIRE(g->K > 0 && g->K % BK == 0 && g->N > 0 && g->N % 64 == 0, "grouped_gemm NN: K %% 64 and N %% 64 must be 0");
         MOKB_REQUIRE((g->A2 == nullptr) == (g->B2 == nullptr), "grouped_gemm NN: A2 and B2 go together");
-        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->K, rows, 2ull * g->lda, 64, BM));
+        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->K, rows, 2ull * g->lda, 64, 128));
         MOKB_TRY(make_tmap_2d(&tb, g->B, 2, g->N, static_cast<uint64_t>(g->G) * g->K, 2ull * g->ldb, 64, 64));
         ta2 = ta; tb2 = tb;
         if (g->A2) {
-            MOKB_TRY(make_tmap_2d(&ta2, g->A2, 2, g->K, rows, 2ull * g->lda, 64, BM));
+            MOKB_TRY(make_tmap_2d(&ta2, g->A2, 2, g->K, rows, 2ull * g->lda, 64, 128));
             MOKB_TRY(make_tmap_2d(&tb2, g->B2, 2, g->N, static_cast<uint64_t>(g->G) * g->K, 2ull * g->ldb, 64, 64));
             p.dual = 1;
         }
         p.b_rows_per_group = g->K;
-        return launch<MODE_NN>(ta, tb, ta2, tb2, p, (g->rows_static / BM) * ((g->N + BN - 1) / BN), stream);
+        return dispatch_launch<MODE_NN>(ncta, ta, tb, ta2, tb2, p, m_tiles * ((g->N + BN - 1) / BN), stream);
     }
     default: {
-        MOKB_REQUIRE(g->M > 0 && g->M % BM == 0 && g->N > 0 && g->N % 64 == 0, "grouped_gemm WGRAD: M %% 128 and N %% 64 must be 0");
+        MOKB_REQUIRE(g->M > 0 && g->M % 128 == 0 && g->N > 0 && g->N % 64 == 0, "grouped_gemm WGRAD: M %% 128 and N %% 64 must be 0");
         MOKB_REQUIRE(g->group_offsets != nullptr, "grouped_gemm WGRAD: group_offsets required");
         MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->M, rows, 2ull * g->lda, 64, 64));
         MOKB_TRY(make_tmap_2d(&tb, g->B, 2, g->N, rows, 2ull * g->ldb, 64, 64));
         ta2 = ta; tb2 = tb;
-        return launch<MODE_WGRAD>(ta, tb, ta2, tb2, p, g->G * (g->M / BM) * ((g->N + BN - 1) / BN), stream);
+        const int wg_ncta = ctas_per_tile();     // the weight-gradient tile is over M and N, not over rows
+        const int tm = 128 * wg_ncta;
+        return dispatch_launch<MODE_WGRAD>(wg_ncta, ta, tb, ta2, tb2, p, g->G * ((g->M + tm - 1) / tm) * ((g->N + BN - 1) / BN), stream);
     }
     }
 }
