@@ -195,7 +195,9 @@ int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_args* args, vo
  * A [rows, M] and B [rows, N]: D[g] [M, N] = A_g^T * B_g (zero if the group is empty). */
 typedef struct {
     int mode;
-    int rows_static;            /* used when num_rows is NULL */
+    int rows_static;            /* row capacity of A and D; the row count when num_rows is NULL */
+    int row_begin, row_end;     /* modes 0-2: only rows [row_begin, min(row_end, rows)) are computed; row_end = 0 means all.
+                                   Both must be multiples of 256. */
     const int32_t* num_rows;    /* device, optional */
     const int32_t* group_of_block;   /* device [rows/128], optional */
     const int32_t* group_offsets;    /* device [G+1] (mode 3) */

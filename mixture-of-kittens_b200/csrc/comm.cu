@@ -69,18 +69,19 @@ __global__ void barrier_kernel(PeerPtrs peers, int R, int rank, int32_t* target,
 template <bool SCALE>
 __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t* __restrict__ peer_rank,
                                 const int32_t* __restrict__ peer_token_idx, const int32_t* __restrict__ num_rows,
-                                int max_rows, int row_divisor, int vec_per_row, uint4* __restrict__ dst,
-                                float* __restrict__ row_scale_out) {
+                                int max_rows, int row_begin, int row_end, int R, int row_divisor, int vec_per_row,
+                                uint4* __restrict__ dst, float* __restrict__ row_scale_out) {
     int rows = num_rows ? *num_rows : max_rows;
     rows = rows < 0 ? 0 : (rows > max_rows ? 0 : rows);
+    rows = min(rows, row_end);
     const int lane = threadIdx.x & 31;
     const int warps_per_block = blockDim.x >> 5;
     const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int nwarps = gridDim.x * warps_per_block;
-    for (int row = warp; row < rows; row += nwarps) {
+    for (int row = row_begin + warp; row < rows; row += nwarps) {
         const int pr = peer_rank[row];
         uint4* out = dst + static_cast<size_t>(row) * vec_per_row;
-        if (pr < 0) {
+        if (pr < 0 || pr >= R) {      // padding row (or a rank outside the pointer list: treated as padding, never dereferenced)
             for (int v = lane; v < vec_per_row; v += 32) out[v] = make_uint4(0, 0, 0, 0);
             if (SCALE && lane == 0 && row_scale_out) row_scale_out[row] = 0.f;
             continue;
@@ -116,17 +117,18 @@ __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t*
 
 __global__ void combine_kernel(const uint4* __restrict__ src, PeerPtrs dst, PeerPtrs val_dst,
                                const int32_t* __restrict__ peer_rank, const int32_t* __restrict__ peer_token_idx,
-                               const int32_t* __restrict__ num_rows, int max_rows, int vec_per_row,
-                               const float* __restrict__ row_values) {
+                               const int32_t* __restrict__ num_rows, int max_rows, int row_begin, int row_end, int R,
+                               int vec_per_row, const float* __restrict__ row_values) {
     int rows = num_rows ? *num_rows : max_rows;
     rows = rows < 0 ? 0 : (rows > max_rows ? 0 : rows);
+    rows = min(rows, row_end);
     const int lane = threadIdx.x & 31;
     const int warps_per_block = blockDim.x >> 5;
     const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int nwarps = gridDim.x * warps_per_block;
-    for (int row = warp; row < rows; row += nwarps) {
+    for (int row = row_begin + warp; row < rows; row += nwarps) {
         const int pr = peer_rank[row];
-        if (pr < 0) continue;
+        if (pr < 0 || pr >= R) continue;
         const int tok = peer_token_idx[row];
         const uint4* in = src + static_cast<size_t>(row) * vec_per_row;
         uint4* out = static_cast<uint4*>(dst.p[pr]) + static_cast<size_t>(tok) * vec_per_row;
@@ -203,45 +205,47 @@ extern "C" int mokb_barrier_all(const uint64_t* barrier_ptrs_host, int ep_size, 
     return MOKB_OK;
 }
 
-extern "C" int mokb_dispatch_rows(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
-                                  const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows,
-                                  int row_divisor, int64_t hidden, void* dst,
-                                  const uint64_t* row_scale_ptrs_host, float* row_scale_out, void* stream) {
+namespace mokb {
+
+int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
+                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
+                       int row_divisor, int64_t hidden, void* dst, const uint64_t* row_scale_ptrs_host,
+                       float* row_scale_out, int blocks, cudaStream_t s) {
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "dispatch_rows: bad ep_size");
     MOKB_REQUIRE(peer_rank && peer_token_idx && dst, "dispatch_rows: null pointer");
     MOKB_REQUIRE(max_rows >= 0 && row_divisor >= 1 && hidden > 0 && hidden % 8 == 0, "dispatch_rows: bad sizes");
+    MOKB_REQUIRE(row_begin >= 0 && row_begin <= row_end, "dispatch_rows: bad row window");
     MOKB_REQUIRE((reinterpret_cast<uintptr_t>(dst) & 15) == 0, "dispatch_rows: dst not 16-byte aligned");
     PeerPtrs src, scale;
     MOKB_TRY(fill_peers(&src, src_ptrs_host, ep_size, "src_ptrs"));
     for (int r = 0; r < kPeerMax; ++r) scale.p[r] = nullptr;
-    if (max_rows == 0) return MOKB_OK;
+    if (max_rows == 0 || row_begin >= max_rows) return MOKB_OK;
     const int threads = 256;
-    const int blocks = sm_count() * 8;
+    if (blocks <= 0) blocks = sm_count() * 8;
     const int vec = static_cast<int>(hidden / 8);
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (row_scale_ptrs_host) {
         for (int r = 0; r < ep_size; ++r) {
             MOKB_REQUIRE(row_scale_ptrs_host[r] != 0, "dispatch_rows: null scale pointer for rank %d", r);
             scale.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(row_scale_ptrs_host[r]));
         }
-        dispatch_kernel<true><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows,
-                                                         row_divisor, vec, static_cast<uint4*>(dst), row_scale_out);
+        dispatch_kernel<true><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
+                                                         row_end, ep_size, row_divisor, vec, static_cast<uint4*>(dst), row_scale_out);
     } else {
-        dispatch_kernel<false><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows,
-                                                          row_divisor, vec, static_cast<uint4*>(dst), nullptr);
+        dispatch_kernel<false><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
+                                                          row_end, ep_size, row_divisor, vec, static_cast<uint4*>(dst), nullptr);
     }
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     return MOKB_OK;
 }
 
-extern "C" int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_size,
-                                 const int32_t* peer_rank, const int32_t* peer_token_idx,
-                                 const int32_t* num_rows, int max_rows, int64_t hidden,
-                                 const float* row_values, const uint64_t* value_ptrs_host, void* stream) {
+int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_size, const int32_t* peer_rank,
+                      const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
+                      int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s) {
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "combine_rows: bad ep_size");
     MOKB_REQUIRE(src && peer_rank && peer_token_idx, "combine_rows: null pointer");
     MOKB_REQUIRE(max_rows >= 0 && hidden > 0 && hidden % 8 == 0, "combine_rows: bad sizes");
+    MOKB_REQUIRE(row_begin >= 0 && row_begin <= row_end, "combine_rows: bad row window");
     MOKB_REQUIRE((row_values == nullptr) == (value_ptrs_host == nullptr), "combine_rows: row_values and value_ptrs go together");
     PeerPtrs dst, val;
     MOKB_TRY(fill_peers(&dst, dst_ptrs_host, ep_size, "dst_ptrs"));
@@ -251,11 +255,29 @@ extern "C" int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host,
             MOKB_REQUIRE(value_ptrs_host[r] != 0, "combine_rows: null value pointer for rank %d", r);
             val.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(value_ptrs_host[r]));
         }
-    if (max_rows == 0) return MOKB_OK;
-    combine_kernel<<<sm_count() * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
-        static_cast<int>(hidden / 8), row_values);
+    if (max_rows == 0 || row_begin >= max_rows) return MOKB_OK;
+    if (blocks <= 0) blocks = sm_count() * 8;
+    combine_kernel<<<blocks, 256, 0, s>>>(static_cast<const uint4*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
+                                          row_begin, row_end, ep_size, static_cast<int>(hidden / 8), row_values);
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     return MOKB_OK;
+}
+
+}  // namespace mokb
+
+extern "C" int mokb_dispatch_rows(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
+                                  const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows,
+                                  int row_divisor, int64_t hidden, void* dst,
+                                  const uint64_t* row_scale_ptrs_host, float* row_scale_out, void* stream) {
+    return dispatch_rows_impl(src_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, 0, max_rows, row_divisor,
+                              hidden, dst, row_scale_ptrs_host, row_scale_out, 0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_size,
+                                 const int32_t* peer_rank, const int32_t* peer_token_idx,
+                                 const int32_t* num_rows, int max_rows, int64_t hidden,
+                                 const float* row_values, const uint64_t* value_ptrs_host, void* stream) {
+    return combine_rows_impl(src, dst_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, 0, max_rows, hidden,
+                             row_values, value_ptrs_host, 0, static_cast<cudaStream_t>(stream));
 }

@@ -39,6 +39,16 @@ void note_launch(int n = 1);   // counts kernels launched by this library (repor
 int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
                  uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
 
+// Row-window forms of dispatch / combine used by the layer to overlap them with the GEMMs:
+// rows [row_begin, min(row_end, *num_rows)) only, on `blocks` CTAs of 256 threads (0 = default).
+int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
+                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
+                       int row_divisor, int64_t hidden, void* dst, const uint64_t* row_scale_ptrs_host,
+                       float* row_scale_out, int blocks, cudaStream_t s);
+int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_size, const int32_t* peer_rank,
+                      const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
+                      int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s);
+
 // ---------------------------------------------------------------- device side
 #ifdef __CUDACC__
 

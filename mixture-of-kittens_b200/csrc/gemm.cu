@@ -56,6 +56,7 @@ struct Geo {
 
 struct KParams {
     int rows_cap;                    // static upper bound of rows
+    int row_begin, row_end;          // row window (multiples of 256); row_end <= rows_cap
     const int32_t* num_rows;         // device, optional
     const int32_t* group_of_block;   // device [rows/128], optional
     const int32_t* group_offsets;    // device [G+1], MODE_WGRAD
@@ -75,8 +76,9 @@ struct Tile {
 
 template <int MODE, int NCTA>
 struct Sched {
-    int m_blocks, n_blocks, total;
+    int m_blocks, n_blocks, total, m_first;
     __device__ Sched(const KParams& p) {
+        m_first = 0;
         constexpr int TM = Geo<NCTA>::TILE_M;
         if (MODE == MODE_WGRAD) {
             m_blocks = (p.M + TM - 1) / TM;
@@ -85,7 +87,9 @@ struct Sched {
         } else {
             int rows = p.num_rows ? *p.num_rows : p.rows_cap;
             if (rows < 0 || rows > p.rows_cap) rows = 0;
-            m_blocks = rows / TM;
+            const int hi = min(rows, p.row_end), lo = min(p.row_begin, hi);
+            m_first = lo / TM;
+            m_blocks = (hi - lo) / TM;
             n_blocks = MODE == MODE_SWIGLU ? p.N / 128 : (p.N + BN - 1) / BN;
             total = m_blocks * n_blocks;
         }
@@ -109,7 +113,7 @@ struct Sched {
             const int gsize = min(GM, m_blocks - first);
             const int in = t - sg * per;
             ti.n_blk = in / gsize;
-            ti.m_blk = first + (in - ti.n_blk * gsize);
+            ti.m_blk = m_first + first + (in - ti.n_blk * gsize);
             ti.group = p.group_of_block ? p.group_of_block[ti.m_blk * (TM / 128)] : 0;
             ti.k_row0 = 0;
             ti.k_iters = (p.K / BK) * (p.dual ? 2 : 1);
@@ -456,6 +460,10 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     KParams p;
     memset(&p, 0, sizeof(p));
     p.rows_cap = g->rows_static;
+    p.row_begin = g->row_begin;
+    p.row_end = g->row_end > 0 ? g->row_end : g->rows_static;
+    MOKB_REQUIRE(p.row_begin >= 0 && p.row_begin % 256 == 0 && p.row_end % (128 * ncta) == 0 && p.row_begin <= p.row_end && p.row_end <= g->rows_static,
+                 "grouped_gemm: bad row window [%d, %d) of %d", g->row_begin, g->row_end, g->rows_static);
     p.num_rows = g->num_rows;
     p.group_of_block = g->group_of_block;
     p.group_offsets = g->group_offsets;
@@ -472,7 +480,7 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     MOKB_REQUIRE((reinterpret_cast<uintptr_t>(g->D) & 15) == 0, "grouped_gemm: D not 16-byte aligned");
     if (g->rows_static == 0) return MOKB_OK;
     const uint64_t rows = static_cast<uint64_t>(g->rows_static);
-    const int m_tiles = g->rows_static / TM;
+    const int m_tiles = (p.row_end - p.row_begin + TM - 1) / TM;
     CUtensorMap ta, tb, ta2, tb2;
     switch (g->mode) {
     case MODE_NT: {

@@ -1,8 +1,24 @@
-// The fused MoE layer, forward and backward (BF16): the stream-ordered sequence
-// of dispatch, grouped GEMMs, SwiGLU and combine that replaces the reference's
-// persistent kernels (csrc/megakernel/forward.cuh:1-291, backward.cuh:1-443).
+// The fused MoE layer, forward and backward (BF16): the sequence of dispatch,
+// grouped GEMMs, SwiGLU and combine that replaces the reference's persistent
+// kernels (csrc/megakernel/forward.cuh:1-291, backward.cuh:1-443).
+//
 // Nothing here synchronises the host: the number of routed rows is read on the
-// device by every kernel (forward.cuh:20 does the same).
+// device by every kernel (forward.cuh:20 does the same).  Communication overlaps
+// computation the way the reference's communication CTAs do, but with stream
+// ordering instead of in-kernel counters: dispatch and combine run on two side
+// streams of this library, in row windows of `minibatch_size` rows, on
+// `num_comm_sms` SMs' worth of threads, and are tied to the GEMM launches on the
+// caller's stream by events (fork after the prologue, join before returning):
+//
+//   forward   side 1: dispatch(c0) dispatch(c1) ...
+//             caller: prologue | shared gate/up, shared down | gate/up(c0) down(c0) gate/up(c1) down(c1) ...
+//             side 2:                                                   combine(c0)          combine(c1) ...
+//   backward  side 1: scaled dispatch of d_y
+//             caller: prologue | shared backward (6 launches) | routed dgrads | routed wgrads
+//             side 2:                                                          combine of d_x + router grads
+//
+// No kernel waits on another kernel; MOKB_OVERLAP=0 puts everything on the caller's stream.
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -101,9 +117,59 @@ int check_common(const A* a, const char* who) {
     MOKB_REQUIRE(a->num_local_experts > 0 && a->topk > 0 && a->topk <= 255, "%s: bad expert/top-k counts", who);
     MOKB_REQUIRE(a->schedule_capacity > 0 && a->schedule_capacity % 256 == 0, "%s: schedule_capacity must be a positive multiple of 256", who);
     MOKB_REQUIRE(a->macrobatch_size > 0 && a->macrobatch_size % 256 == 0, "%s: macrobatch_size must be a positive multiple of 256", who);
+    MOKB_REQUIRE(a->minibatch_size > 0 && a->minibatch_size % 256 == 0, "%s: minibatch_size must be a positive multiple of 256", who);
+    MOKB_REQUIRE(a->num_comm_sms > 0, "%s: num_comm_sms must be positive", who);
     MOKB_REQUIRE(a->peer_rank && a->peer_token_idx && a->num_tokens && a->tokens_per_expert, "%s: null schedule pointer", who);
     MOKB_REQUIRE(a->scratch && a->status, "%s: scratch and status are required", who);
     return MOKB_OK;
+}
+
+// ---- side streams and events, one set per device, created on first use
+constexpr int kMaxChunks = 32;
+
+struct Async {
+    bool ready = false;
+    cudaStream_t s1 = nullptr, s2 = nullptr;
+    cudaEvent_t fork = nullptr, join1 = nullptr, join2 = nullptr;
+    cudaEvent_t ev_in[kMaxChunks] = {nullptr};    // dispatch of chunk c finished
+    cudaEvent_t ev_out[kMaxChunks] = {nullptr};   // rows of chunk c are ready to be combined
+};
+Async g_async[64];
+
+int get_async(Async** out) {
+    int dev = -1;
+    MOKB_CUDA(cudaGetDevice(&dev));
+    MOKB_REQUIRE(dev >= 0 && dev < 64, "layer: device index %d out of range", dev);
+    Async& a = g_async[dev];
+    if (!a.ready) {
+        MOKB_CUDA(cudaStreamCreateWithFlags(&a.s1, cudaStreamNonBlocking));
+        MOKB_CUDA(cudaStreamCreateWithFlags(&a.s2, cudaStreamNonBlocking));
+        cudaEvent_t* single[3] = {&a.fork, &a.join1, &a.join2};
+        for (auto e : single) MOKB_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+        for (int c = 0; c < kMaxChunks; ++c) {
+            MOKB_CUDA(cudaEventCreateWithFlags(&a.ev_in[c], cudaEventDisableTiming));
+            MOKB_CUDA(cudaEventCreateWithFlags(&a.ev_out[c], cudaEventDisableTiming));
+        }
+        a.ready = true;
+    }
+    *out = &a;
+    return MOKB_OK;
+}
+
+bool overlap_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("MOKB_OVERLAP");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// rows per communication/compute window: minibatch_size, coarsened so that at most kMaxChunks windows cover MB
+int chunk_rows_for(int MB, int minibatch) {
+    int rows = minibatch;
+    if ((MB + rows - 1) / rows > kMaxChunks) rows = static_cast<int>(align256((MB + kMaxChunks - 1) / kMaxChunks));
+    return rows;
 }
 
 }  // namespace
@@ -123,46 +189,76 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_arg
     MOKB_REQUIRE(a->x_ptrs_host && a->w_shared_gate && a->w_shared_up && a->w_routed_gate && a->w_routed_up, "fwd_bf16: null input");
     MOKB_REQUIRE(a->x_routed && a->gate_shared && a->up_shared && a->hidden_shared && a->gate_routed && a->up_routed && a->hidden_routed,
                  "fwd_bf16: null output");
-    if (!a->skip_down_combine)
+    const bool with_down = !a->skip_down_combine;
+    if (with_down)
         MOKB_REQUIRE(a->combine_ptrs_host && a->w_shared_down && a->w_routed_down && a->y_shared && a->y_routed, "fwd_bf16: null down/combine pointer");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
     const Scratch s = carve(a->scratch, E_l, MB);
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, s, a->status, stream));
+    const bool overlap = overlap_enabled();
+    Async* as = nullptr;
+    if (overlap) MOKB_TRY(get_async(&as));
+    cudaStream_t s_in = overlap ? as->s1 : stream, s_out = overlap ? as->s2 : stream;
+    const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
+    const int chunk = chunk_rows_for(MB, a->minibatch_size);
+    const int nchunks = (MB + chunk - 1) / chunk;
 
-    // dispatch: pull every scheduled row from its home rank
-    MOKB_TRY(mokb_dispatch_rows(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, a->topk, H,
-                                a->x_routed, nullptr, nullptr, stream));
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, s, a->status, stream));
+    if (overlap) {
+        MOKB_CUDA(cudaEventRecord(as->fork, stream));
+        MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
+        if (with_down) MOKB_CUDA(cudaStreamWaitEvent(s_out, as->fork, 0));
+    }
+    // dispatch: pull every scheduled row from its home rank, window by window
+    for (int c = 0; c < nchunks; ++c) {
+        const int r0 = c * chunk, r1 = r0 + chunk < MB ? r0 + chunk : MB;
+        MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, r0, r1, a->topk, H,
+                                    a->x_routed, nullptr, nullptr, comm_blocks, s_in));
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+    }
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
 
-    // shared expert: gate/up + SwiGLU in one pass, then down
+    // shared expert: gate/up + SwiGLU in one pass, then down (independent of the dispatch)
     mokb_gemm_args g = gemm_base(a->status);
     g.mode = 1; g.rows_static = T; g.N = I; g.K = H;
     g.A = x_local; g.lda = H; g.B = a->w_shared_gate; g.B2 = a->w_shared_up; g.ldb = H;
     g.D = a->gate_shared; g.D2 = a->up_shared; g.D3 = a->hidden_shared; g.ldd = I;
     g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
     MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    if (!a->skip_down_combine) {
+    if (with_down) {
         g = gemm_base(a->status);
         g.mode = 0; g.rows_static = T; g.N = H; g.K = I;
         g.A = a->hidden_shared; g.lda = I; g.B = a->w_shared_down; g.ldb = I; g.D = a->y_shared; g.ldd = H;
         MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
     }
 
-    // routed experts
-    g = gemm_base(a->status);
-    g.mode = 1; g.rows_static = MB; g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
-    g.A = a->x_routed; g.lda = H; g.B = a->w_routed_gate; g.B2 = a->w_routed_up; g.ldb = H;
-    g.D = a->gate_routed; g.D2 = a->up_routed; g.D3 = a->hidden_routed; g.ldd = I;
-    g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    if (!a->skip_down_combine) {
+    // routed experts, window by window behind the dispatch
+    for (int c = 0; c < nchunks; ++c) {
+        const int r0 = c * chunk, r1 = r0 + chunk < MB ? r0 + chunk : MB;
+        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
         g = gemm_base(a->status);
-        g.mode = 0; g.rows_static = MB; g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = H; g.K = I;
+        g.mode = 1; g.rows_static = MB; g.row_begin = r0; g.row_end = r1;
+        g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
+        g.A = a->x_routed; g.lda = H; g.B = a->w_routed_gate; g.B2 = a->w_routed_up; g.ldb = H;
+        g.D = a->gate_routed; g.D2 = a->up_routed; g.D3 = a->hidden_routed; g.ldd = I;
+        g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
+        MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+        if (!with_down) continue;
+        g = gemm_base(a->status);
+        g.mode = 0; g.rows_static = MB; g.row_begin = r0; g.row_end = r1;
+        g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = H; g.K = I;
         g.A = a->hidden_routed; g.lda = I; g.B = a->w_routed_down; g.ldb = I; g.D = a->y_routed; g.ldd = H;
         MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-        // combine: push every row back to slot t*K+k of its home rank
-        MOKB_TRY(mokb_combine_rows(a->y_routed, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, H,
-                                   nullptr, nullptr, stream));
+        // combine: push the window's rows back to slot t*K+k of their home ranks
+        if (overlap) {
+            MOKB_CUDA(cudaEventRecord(as->ev_out[c], stream));
+            MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[c], 0));
+        }
+        MOKB_TRY(combine_rows_impl(a->y_routed, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, r0, r1,
+                                   H, nullptr, nullptr, comm_blocks, s_out));
+    }
+    if (overlap && with_down) {
+        MOKB_CUDA(cudaEventRecord(as->join2, s_out));
+        MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
     }
     return MOKB_OK;
 }
@@ -180,13 +276,23 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
                  a->d_w_shared_up && a->d_w_routed_up && a->d_w_shared_down && a->d_w_routed_down, "bwd_bf16: null output");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
     const Scratch s = carve(a->scratch, E_l, MB);
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, s, a->status, stream));
+    const bool overlap = overlap_enabled();
+    Async* as = nullptr;
+    if (overlap) MOKB_TRY(get_async(&as));
+    cudaStream_t s_in = overlap ? as->s1 : stream, s_out = overlap ? as->s2 : stream;
+    const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
     const int lim = a->has_swiglu_limit;
     const float limv = a->swiglu_limit;
 
-    // reverse combine: pull d_y rows, scaled by the route's router weight
-    MOKB_TRY(mokb_dispatch_rows(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, a->topk, H,
-                                a->d_y_routed, a->router_weight_ptrs_host, s.w_row, stream));
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, s, a->status, stream));
+    if (overlap) {
+        MOKB_CUDA(cudaEventRecord(as->fork, stream));
+        MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
+    }
+    // reverse combine: pull d_y rows, scaled by the route's router weight (overlaps the shared expert's backward)
+    MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB, a->topk, H,
+                                a->d_y_routed, a->router_weight_ptrs_host, s.w_row, comm_blocks, s_in));
+    if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
     const void* d_y_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->d_y_ptrs_host[a->ep_rank]));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
 
@@ -213,6 +319,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
     MOKB_TRY(wgrad(a->d_up_shared, I, x_local, H, a->d_w_shared_up, 1, T, s.shared_offsets));
 
     // ---- routed experts
+    if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
     g = gemm_base(a->status);
     g.mode = 2; g.rows_static = MB; g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
     g.A = a->d_y_routed; g.lda = H; g.B = a->w_routed_down; g.ldb = I; g.D = a->d_hidden_routed; g.ldd = I;
@@ -224,11 +331,17 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
     g.A = a->d_gate_routed; g.B = a->w_routed_gate; g.A2 = a->d_up_routed; g.B2 = a->w_routed_up; g.lda = I; g.ldb = H;
     g.D = a->d_x_routed; g.ldd = H;
     MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    // reverse dispatch: push d_x rows and the per-route router-weight gradient home
-    MOKB_TRY(mokb_combine_rows(a->d_x_routed, a->d_x_routed_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, H,
-                               s.d_w_row, a->d_router_weight_ptrs_host, stream));
+    // reverse dispatch: push d_x rows and the per-route router-weight gradient home (overlaps the weight gradients)
+    if (overlap) {
+        MOKB_CUDA(cudaEventRecord(as->ev_out[0], stream));
+        MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[0], 0));
+    }
+    MOKB_TRY(combine_rows_impl(a->d_x_routed, a->d_x_routed_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB,
+                               H, s.d_w_row, a->d_router_weight_ptrs_host, comm_blocks, s_out));
+    if (overlap) MOKB_CUDA(cudaEventRecord(as->join2, s_out));
     MOKB_TRY(wgrad(a->d_y_routed, H, a->hidden_routed, I, a->d_w_routed_down, E_l, MB, s.expert_offsets));
     MOKB_TRY(wgrad(a->d_gate_routed, I, a->x_routed, H, a->d_w_routed_gate, E_l, MB, s.expert_offsets));
     MOKB_TRY(wgrad(a->d_up_routed, I, a->x_routed, H, a->d_w_routed_up, E_l, MB, s.expert_offsets));
+    if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
     return MOKB_OK;
 }

@@ -261,6 +261,24 @@ def test_gemm_nt(mods, rows_per_group, N, K):
     assert torch.all(D[rows:] == 3.0)
 
 
+def test_gemm_row_window_touches_only_its_rows(mods):
+    _C, ops = mods
+    rows_per_group, N, K = [512, 256, 768], 256, 128
+    offs, gob, rows = _groups(rows_per_group)
+    g = torch.Generator().manual_seed(15)
+    A = torch.randn(rows, K, generator=g).to(torch.bfloat16).cuda()
+    W = (torch.randn(3, N, K, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    full = torch.empty(rows, N, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm(0, A, W, full, group_of_block=gob, G=3, N=N, K=K)
+    n = torch.tensor([1280], dtype=torch.int32, device="cuda")      # fewer rows than the last window asks for
+    part = torch.full((rows, N), 9.0, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm(0, A, W, part, num_rows=n, group_of_block=gob, G=3, N=N, K=K, row_begin=256, row_end=768)
+    _C.grouped_gemm(0, A, W, part, num_rows=n, group_of_block=gob, G=3, N=N, K=K, row_begin=1024, row_end=1536)
+    assert _C.check_status() == 0
+    assert torch.equal(part[256:768], full[256:768]) and torch.equal(part[1024:1280], full[1024:1280])
+    assert torch.all(part[:256] == 9.0) and torch.all(part[768:1024] == 9.0) and torch.all(part[1280:] == 9.0)
+
+
 @pytest.mark.parametrize("limit", [None, 1.0])
 def test_gemm_swiglu(mods, limit):
     _C, ops = mods
