@@ -183,6 +183,85 @@ size_t mokb_layer_scratch_bytes(int schedule_capacity, int num_local_experts, in
 int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_args* args, void* stream);
 int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_args* args, void* stream);
 
+/* ---- the fused layer in MXFP8: replace `_C.dispatch_mlp_swiglu_combine_{fwd,bwd}_mxfp8` and
+ * `_C.recompute_forward_context_mxfp8` (csrc/megakernel/entrypoints.cuh:11-96, 169-332; host launchers
+ * forward.cuh:296-428, backward.cuh:448-679).  Routed experts run in block-scaled E4M3, the shared expert
+ * in BF16.  E4M3 tensors are passed as byte pointers; every `*_sc` is a packed scale tensor
+ * [rows/128, cols/128, 32, 16] for the tensor it follows.  "work" buffers are caller-allocated and need
+ * no initialisation; their contents after the call are unspecified. */
+typedef struct {
+    int ep_size, ep_rank;
+    int num_local_tokens, hidden, intermediate, num_local_experts, topk;
+    int schedule_capacity, macrobatch_size, minibatch_size, num_comm_sms;
+    int has_swiglu_limit;
+    float swiglu_limit;
+    const int32_t* peer_rank;
+    const int32_t* peer_token_idx;
+    const int32_t* num_tokens;
+    const int32_t* tokens_per_expert;
+    const uint64_t* x_ptrs_host;
+    const uint64_t* combine_ptrs_host;
+    const void *w_shared_gate, *w_shared_up, *w_shared_down;                  /* bf16 */
+    const void *w_routed_gate, *w_routed_gate_sc;                             /* [E_l, I, H] quantised along H */
+    const void *w_routed_up, *w_routed_up_sc;
+    const void *w_routed_down, *w_routed_down_sc;                             /* [E_l, H, I] quantised along I */
+    /* outputs (ops.py:265-278 of the reference) */
+    void *x_fp8_t, *x_sc_t;                                                   /* [H, MB]: x_routed^T quantised along tokens */
+    void *gate_shared, *up_shared, *hidden_shared;                            /* [T, I] bf16 */
+    void *gate_fp8, *gate_sc, *up_fp8, *up_sc;                                /* [MB, I] */
+    void *hidden_fp8_t, *hidden_sc_t;                                         /* [I, MB] */
+    void *y_shared, *y_routed;                                                /* [T, H], [MB, H] bf16 */
+    /* work */
+    void *x_routed;                                                           /* [MB, H] bf16 */
+    void *x_fp8, *x_sc;                                                       /* [MB, H] */
+    void *gate_bf16, *up_bf16;                                                /* [MB, I] bf16 */
+    void *hidden_fp8, *hidden_sc;                                             /* [MB, I] */
+    void* scratch;                                                            /* mokb_layer_scratch_bytes() */
+    int32_t* status;
+    int skip_down_combine;                                                    /* 1 = recompute_forward_context */
+} mokb_fwd_mxfp8_args;
+
+typedef struct {
+    int ep_size, ep_rank;
+    int num_local_tokens, hidden, intermediate, num_local_experts, topk;
+    int schedule_capacity, macrobatch_size, minibatch_size, num_comm_sms;
+    int has_swiglu_limit;
+    float swiglu_limit;
+    const int32_t* peer_rank;
+    const int32_t* peer_token_idx;
+    const int32_t* num_tokens;
+    const int32_t* tokens_per_expert;
+    const uint64_t* d_y_ptrs_host;
+    const uint64_t* d_x_routed_ptrs_host;
+    const uint64_t* router_weight_ptrs_host;
+    const uint64_t* d_router_weight_ptrs_host;
+    const uint64_t* x_ptrs_host;
+    const void *w_shared_gate, *w_shared_up, *w_shared_down;                  /* bf16 */
+    const void *w_routed_gate_t, *w_routed_gate_t_sc;                         /* [E_l, H, I] = W_gate^T quantised along I */
+    const void *w_routed_up_t, *w_routed_up_t_sc;
+    const void *w_routed_down_t, *w_routed_down_t_sc;                         /* [E_l, I, H] = W_down^T quantised along H */
+    /* saved forward context */
+    const void *x_fp8_t, *x_sc_t, *gate_shared, *gate_fp8, *gate_sc, *up_shared, *up_fp8, *up_sc;
+    const void *hidden_shared, *hidden_fp8_t, *hidden_sc_t;
+    /* outputs (ops.py:903-921 of the reference) */
+    void *d_x_shared, *d_x_routed;                                            /* [T, H], [MB, H] bf16 */
+    void *d_gate_shared, *d_gate_fp8, *d_gate_sc;                             /* [T, I] bf16; [MB, I] */
+    void *d_up_shared, *d_up_fp8, *d_up_sc;
+    void *d_hidden_shared, *d_hidden_routed;                                  /* [T, I], [MB, I] bf16 */
+    void *d_y_fp8, *d_y_sc;                                                   /* [MB, H] */
+    void *d_w_shared_gate, *d_w_routed_gate, *d_w_shared_up, *d_w_routed_up, *d_w_shared_down, *d_w_routed_down;   /* bf16 */
+    /* work */
+    void *d_y_routed;                                                         /* [MB, H] bf16 */
+    void *d_y_fp8_t, *d_y_sc_t;                                               /* [H, MB] */
+    void *d_gate_fp8_t, *d_gate_sc_t, *d_up_fp8_t, *d_up_sc_t;                /* [I, MB] */
+    void *partials;                                                           /* [MB, I/128] f32 */
+    void* scratch;
+    int32_t* status;
+} mokb_bwd_mxfp8_args;
+
+int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_args* args, void* stream);
+int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_args* args, void* stream);
+
 /* ---- building blocks, exported for tests and micro-benchmarks.  They are the
  * kernels the two layer calls above are made of. */
 
@@ -211,6 +290,27 @@ typedef struct {
     int32_t* status;
 } mokb_gemm_args;
 int mokb_grouped_gemm_bf16(const mokb_gemm_args* args, void* stream);
+
+/* Grouped MXFP8 GEMM (E4M3 data + one E8M0 scale per 32 elements of K, scales in the packed
+ * [rows/128, K/128, 32, 16] layout the quantiser emits), fp32 accumulation, bf16 output.  Both operands
+ * have the contraction axis contiguous (csrc/megakernel/grouped_gemm.cuh:183-237 of the reference).
+ *   mode 0: D[rows,N] = A[rows,K] * B[g][N,K]^T, plus A2 * B2[g]^T into the same tile when A2 is given
+ *   mode 1: D = A * B[g]^T and D2 = A * B2[g]^T in one pass (gate and up), N columns each
+ *   mode 2: D[g][M,N] = A[M, cols_g] * B[N, cols_g]^T with cols_g = [off[g], off[g+1]) of the
+ *           rows_static token columns of A [M, rows_static] and B [N, rows_static] (weight gradients) */
+typedef struct {
+    int mode;
+    int rows_static, row_begin, row_end;     /* as in mokb_gemm_args; multiples of 256 */
+    const int32_t* num_rows;
+    const int32_t* group_of_block;
+    const int32_t* group_offsets;
+    int G, M, N, K;
+    const void *A, *A_sc, *B, *B_sc, *A2, *A2_sc, *B2, *B2_sc;
+    void *D, *D2;
+    int ldd;
+    int32_t* status;
+} mokb_gemm_fp8_args;
+int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* args, void* stream);
 
 /* Row gather from peers (dispatch, csrc/megakernel/dispatch_combine.cuh:1-150):
  * dst[i] = src_rank(peer_rank[i])[peer_token_idx[i] / row_divisor] for i < *num_rows;

@@ -49,6 +49,18 @@ int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                       int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s);
 
+// MXFP8 codec launchers (quantize.cu); `num_rows` (device, optional) bounds the rows that are processed.
+int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int32_t* num_rows,
+                  void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, cudaStream_t stream);
+int swiglu_fwd_quant_impl(const void* gate, const void* up, int64_t rows_cap, int64_t I, const int32_t* num_rows,
+                          int has_limit, float limit, void* gate_q, void* gate_sc, void* up_q, void* up_sc,
+                          void* hid_q, void* hid_sc, void* hid_qt, void* hid_sct, cudaStream_t stream);
+int swiglu_bwd_quant_impl(const void* gate_q, const void* gate_sc, const void* up_q, const void* up_sc, const void* d_hidden,
+                          int64_t rows_cap, int64_t I, const int32_t* num_rows, int has_limit, float limit,
+                          const float* row_scale, void* dg_q, void* dg_sc, void* dg_qt, void* dg_sct,
+                          void* du_q, void* du_sc, void* du_qt, void* du_sct, float* partials, float* row_grad,
+                          cudaStream_t stream);
+
 // ---------------------------------------------------------------- device side
 #ifdef __CUDACC__
 
@@ -219,6 +231,32 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc,
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
         "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// Block-scaled E4M3 MMA over the pair; scale bytes are picked by the a_sf_id / b_sf_id fields of `idesc`.
+__device__ __forceinline__ void umma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+// smem -> TMEM copy of one 32 x 16-byte scale tile in both CTAs of the pair (each from its own smem),
+// replicated to the four 32-lane quarters.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t smem_desc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// Shared-memory descriptor of an un-swizzled K-major tile whose rows are 16 bytes wide (a scale tile):
+// 8-row groups 128 B apart.
+__device__ __forceinline__ uint64_t make_smem_desc_plain16(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);
+    d |= static_cast<uint64_t>(1) << 16;           // LBO: one 16-byte unit (the tile is a single unit wide)
+    d |= static_cast<uint64_t>(128 >> 4) << 32;    // SBO: 128 B between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;
+}
+
 // arrive on the barrier at this offset in every CTA of `cta_mask` once the MMAs issued so far retire
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"

@@ -1,0 +1,429 @@
+// Grouped MXFP8 GEMM for the routed experts: E4M3 operands with one E8M0 scale per 32
+// elements of the contraction axis, multiplied by tcgen05.mma kind::mxf8f6f4.block_scale
+// with fp32 accumulation in tensor memory and bf16 output
+// (reference: csrc/megakernel/grouped_gemm.cuh:183-237, the MXFP8 branches).
+//
+// Every MXFP8 product of the layer is "A * B^T with the contraction axis contiguous in both
+// operands": the backward pass gets pre-transposed, pre-quantised weights and token-axis
+// quantised activations (csrc/megakernel/backward.cuh:335-403).  So there is one operand layout
+// and three ways of walking it:
+//   FMODE_NT     D[rows,N] = A[rows,K] * W[g][N,K]^T (+ A2 * W2[g]^T)   down, both input gradients
+//   FMODE_DUALB  D = A * Wg[g]^T, D2 = A * Wu[g]^T, one 128+128 column tile  gate and up
+//   FMODE_WGRAD  D[g][M,N] = A[M, cols_g] * B[N, cols_g]^T                weight gradients
+//
+// A CTA pair (cluster of 2, cta_group::2) computes a 256 x 256 tile; K advances 128 bytes per
+// stage (4 MMAs of K = 32).  Per stage each CTA stages 16 KB of A, 16 KB of B and three
+// 512-byte scale tiles (its 128 rows of A, all 256 columns of B: every CTA fetches both B scale
+// tiles itself).  The MMA lane copies the scale tiles into tensor memory with tcgen05.cp
+// before the stage's MMAs; the instruction descriptor's scale ids select the byte of the K block.
+//
+// Tensor memory: block scaling needs columns for the scales, so two 256-column accumulators do
+// not fit in the 512 columns.  There is one accumulator; the epilogue drains it into registers
+// as packed bf16 (about as long as one K stage), releases it, and only then writes global
+// memory, so the stores still overlap the next tile's main loop.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace mokb {
+namespace {
+
+constexpr int BN = 256, BKB = 128;                 // tile columns; K bytes (= elements) per stage
+constexpr int TILE_M = 256;
+constexpr int A_BYTES = 128 * BKB;                 // 16 KB per CTA
+constexpr int B_BYTES = 128 * BKB;                 // 16 KB per CTA
+constexpr int DATA_BYTES = A_BYTES + B_BYTES;
+constexpr int SF_TILE = 512;                       // one 32 x 16-byte scale tile
+constexpr int SF_BYTES = 3 * SF_TILE;              // SFA | SFB(cols 0..127) | SFB(cols 128..255)
+constexpr int STAGES = 6;
+constexpr int STAGE_TX = DATA_BYTES + SF_BYTES;    // bytes one CTA lands per stage
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SF_COL0 = 256;                       // scale columns start after the accumulator
+constexpr int SF_SET_COLS = 16;                    // SFA 4 + SFB 8, padded
+constexpr int GROUP_M = 4;
+constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * (DATA_BYTES + SF_BYTES) + 1024 + 256;
+
+enum { FMODE_NT = 0, FMODE_DUALB = 1, FMODE_WGRAD = 2 };
+
+struct FParams {
+    int rows_cap, row_begin, row_end;
+    const int32_t* num_rows;
+    const int32_t* group_of_block;
+    const int32_t* group_offsets;
+    int G, M, N, K;
+    int b_rows_per_group;
+    int dual;
+    int a_ktiles, b_ktiles;          // scale tiles per row block of A / B (= contraction extent / 128)
+    __nv_bfloat16 *D, *D2;
+    int ldd;
+    int32_t* status;
+};
+
+struct Tile {
+    int m_blk, n_blk, group, k_iters, k_tile0;
+};
+
+template <int MODE>
+struct Sched {
+    int m_blocks, n_blocks, total, m_first;
+    __device__ Sched(const FParams& p) {
+        m_first = 0;
+        if (MODE == FMODE_WGRAD) {
+            m_blocks = (p.M + TILE_M - 1) / TILE_M;
+            n_blocks = (p.N + BN - 1) / BN;
+            total = p.G * m_blocks * n_blocks;
+        } else {
+            int rows = p.num_rows ? *p.num_rows : p.rows_cap;
+            if (rows < 0 || rows > p.rows_cap) rows = 0;
+            const int hi = min(rows, p.row_end), lo = min(p.row_begin, hi);
+            m_first = lo / TILE_M;
+            m_blocks = (hi - lo) / TILE_M;
+            n_blocks = MODE == FMODE_DUALB ? p.N / 128 : (p.N + BN - 1) / BN;
+            total = m_blocks * n_blocks;
+        }
+    }
+    __device__ Tile get(const FParams& p, int t) const {
+        Tile ti;
+        if (MODE == FMODE_WGRAD) {
+            const int per = m_blocks * n_blocks;
+            ti.group = t / per;
+            const int rem = t - ti.group * per;
+            ti.n_blk = rem / m_blocks;
+            ti.m_blk = rem - ti.n_blk * m_blocks;
+            const int c0 = p.group_offsets[ti.group];
+            ti.k_tile0 = c0 / BKB;
+            ti.k_iters = (p.group_offsets[ti.group + 1] - c0) / BKB;
+        } else {
+            const int per = GROUP_M * n_blocks;
+            const int sg = t / per;
+            const int first = sg * GROUP_M;
+            const int gsize = min(GROUP_M, m_blocks - first);
+            const int in = t - sg * per;
+            ti.n_blk = in / gsize;
+            ti.m_blk = m_first + first + (in - ti.n_blk * gsize);
+            ti.group = p.group_of_block ? p.group_of_block[ti.m_blk * 2] : 0;
+            ti.k_tile0 = 0;
+            ti.k_iters = (p.K / BKB) * (p.dual ? 2 : 1);
+        }
+        return ti;
+    }
+};
+
+__device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+struct Maps {        // by-value kernel argument
+    CUtensorMap A, B, A2, B2;          // E4M3 data, 128-byte swizzle, boxes of 128 x 128
+    CUtensorMap SA, SB, SA2, SB2;      // scale tiles: rows of 128 u32
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t sf_base = smem_base + STAGES * DATA_BYTES;
+    const uint32_t bars = sf_base + STAGES * SF_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t tfull_bar = bars + 8u * (2 * STAGES);
+    const uint32_t tempty_bar = bars + 8u * (2 * STAGES + 1);
+    uint8_t* bar_gen = smem_gen + STAGES * (DATA_BYTES + SF_BYTES);
+    volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * STAGES + 2));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * (2 * STAGES + 2) + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta = cluster_ctarank();
+    const int tile_id0 = static_cast<int>(blockIdx.x >> 1);
+    const int tile_stride = static_cast<int>(gridDim.x >> 1);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tfull_bar, 1);
+        mbar_init(tempty_bar, 8);             // one arrival per epilogue warp of the pair
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tm.A); tma_prefetch_desc(&tm.B); tma_prefetch_desc(&tm.SA); tma_prefetch_desc(&tm.SB);
+        if (MODE == FMODE_DUALB || p.dual) { tma_prefetch_desc(&tm.B2); tma_prefetch_desc(&tm.SB2); }
+        if (p.dual) { tma_prefetch_desc(&tm.A2); tma_prefetch_desc(&tm.SA2); }
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_slot;
+
+    const Sched<MODE> sched(p);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            const int kh = p.K / BKB;
+            for (int t = tile_id0; ok && t < sched.total; t += tile_stride) {
+                const Tile ti = sched.get(p, t);
+                const int row0 = ti.m_blk * TILE_M + static_cast<int>(cta) * 128;     // this CTA's rows of A (and of D)
+                for (int it = 0; it < ti.k_iters; ++it) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
+                    const uint32_t fb_local = full_bar(s);
+                    const uint32_t fb = map_to_cta(fb_local, 0);
+                    if (cta == 0) mbar_expect_tx(fb_local, 2 * STAGE_TX);
+                    const uint32_t a_dst = smem_base + s * DATA_BYTES;
+                    const uint32_t b_dst = a_dst + A_BYTES;
+                    const uint32_t sfa_dst = sf_base + s * SF_BYTES;
+                    if (MODE == FMODE_WGRAD) {
+                        const int kt = ti.k_tile0 + it;
+                        const int brow = ti.n_blk * BN;
+                        tma_load_2d_pair(a_dst, &tm.A, fb, kt * BKB, row0);
+                        tma_load_2d_pair(b_dst, &tm.B, fb, kt * BKB, brow + static_cast<int>(cta) * 128);
+                        tma_load_2d_pair(sfa_dst, &tm.SA, fb, 0, (row0 / 128) * p.a_ktiles + kt);
+                        tma_load_2d_pair(sfa_dst + SF_TILE, &tm.SB, fb, 0, (brow / 128) * p.b_ktiles + kt);
+                        tma_load_2d_pair(sfa_dst + 2 * SF_TILE, &tm.SB, fb, 0, (brow / 128 + 1) * p.b_ktiles + kt);
+                    } else {
+                        const bool second = it >= kh;
+                        const int kt = second ? it - kh : it;
+                        const CUtensorMap* ta = second ? &tm.A2 : &tm.A;
+                        const CUtensorMap* tsa = second ? &tm.SA2 : &tm.SA;
+                        tma_load_2d_pair(a_dst, ta, fb, kt * BKB, row0);
+                        tma_load_2d_pair(sfa_dst, tsa, fb, 0, (row0 / 128) * p.a_ktiles + kt);
+                        if (MODE == FMODE_DUALB) {
+                            const int brow = ti.group * p.b_rows_per_group + ti.n_blk * 128;
+                            tma_load_2d_pair(b_dst, cta == 0 ? &tm.B : &tm.B2, fb, kt * BKB, brow);
+                            tma_load_2d_pair(sfa_dst + SF_TILE, &tm.SB, fb, 0, (brow / 128) * p.b_ktiles + kt);
+                            tma_load_2d_pair(sfa_dst + 2 * SF_TILE, &tm.SB2, fb, 0, (brow / 128) * p.b_ktiles + kt);
+                        } else {
+                            const CUtensorMap* tb = second ? &tm.B2 : &tm.B;
+                            const CUtensorMap* tsb = second ? &tm.SB2 : &tm.SB;
+                            const int brow = ti.group * p.b_rows_per_group + ti.n_blk * BN;
+                            tma_load_2d_pair(b_dst, tb, fb, kt * BKB, brow + static_cast<int>(cta) * 128);
+                            tma_load_2d_pair(sfa_dst + SF_TILE, tsb, fb, 0, (brow / 128) * p.b_ktiles + kt);
+                            tma_load_2d_pair(sfa_dst + 2 * SF_TILE, tsb, fb, 0, (brow / 128 + 1) * p.b_ktiles + kt);
+                        }
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA)
+        if (lane == 0 && cta == 0) {
+            // block-scaled instruction descriptor: E4M3 x E4M3, E8M0 scales, M = 256 over the pair, N = 256
+            constexpr uint32_t idesc0 = (static_cast<uint32_t>(BN >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(TILE_M >> 4) << 24);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            int local = 0;
+            for (int t = tile_id0; ok && t < sched.total; t += tile_stride, ++local) {
+                const Tile ti = sched.get(p, t);
+                if (!mbar_wait(tempty_bar, (local & 1) ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base;
+                for (int it = 0; it < ti.k_iters; ++it) {
+                    if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * DATA_BYTES;
+                    const uint32_t b_addr = a_addr + A_BYTES;
+                    const uint32_t sf_addr = sf_base + s * SF_BYTES;
+                    const uint32_t sf_cols = tmem_base + SF_COL0 + (s & 1) * SF_SET_COLS;
+                    tmem_cp_32x128b_warpx4_pair(sf_cols, make_smem_desc_plain16(sf_addr));
+                    tmem_cp_32x128b_warpx4_pair(sf_cols + 4, make_smem_desc_plain16(sf_addr + SF_TILE));
+                    tmem_cp_32x128b_warpx4_pair(sf_cols + 8, make_smem_desc_plain16(sf_addr + 2 * SF_TILE));
+                    const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
+                    const uint64_t b_desc = make_smem_desc(b_addr, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t idesc = idesc0 | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29);
+                        umma_mxf8_pair(d_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc,
+                                       sf_cols, sf_cols + 4, (it | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_pair(empty_bar(s), 0x3);
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit_pair(tfull_bar, 0x3);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;
+        const int row_in_tile = static_cast<int>(cta) * 128 + quarter * 32 + lane;
+        int local = 0;
+        bool ok = true;
+        for (int t = tile_id0; ok && t < sched.total; t += tile_stride, ++local) {
+            const Tile ti = sched.get(p, t);
+            if (!mbar_wait(tfull_bar, local & 1, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            const bool empty_k = ti.k_iters == 0;
+            // drain the accumulator into registers as packed bf16, then hand it back to the MMA lane
+            uint32_t packed[BN / 2];
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(t_addr + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    packed[c * 16 + i] = empty_k ? 0u : pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
+
+            const int tile_row = ti.m_blk * TILE_M + row_in_tile;
+            if (MODE == FMODE_DUALB) {
+                const size_t off = static_cast<size_t>(tile_row) * p.ldd + static_cast<size_t>(ti.n_blk) * 128;
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                    st_global_v4(p.D + off + 8 * q, packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                    st_global_v4(p.D2 + off + 8 * q, packed[64 + 4 * q], packed[64 + 4 * q + 1], packed[64 + 4 * q + 2], packed[64 + 4 * q + 3]);
+                }
+            } else {
+                bool row_ok = true;
+                size_t row = static_cast<size_t>(tile_row);
+                if (MODE == FMODE_WGRAD) {
+                    row_ok = tile_row < p.M;
+                    row += static_cast<size_t>(ti.group) * p.M;
+                }
+                __nv_bfloat16* dst = p.D + row * p.ldd + static_cast<size_t>(ti.n_blk) * BN;
+                const int cols_left = p.N - ti.n_blk * BN;
+                if (row_ok) {
+#pragma unroll
+                    for (int q = 0; q < 32; ++q)
+                        if (q * 8 < cols_left)
+                            st_global_v4(dst + 8 * q, packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const unsigned long long t0 = clock64();
+        while (clock64() - t0 < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int MODE>
+int launch(const Maps& m, const FParams& p, int tiles_upper_bound, cudaStream_t stream) {
+    MOKB_CUDA(cudaFuncSetAttribute(grouped_gemm_mxfp8_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    int pairs = sm_count() / 2;
+    if (tiles_upper_bound < pairs) pairs = tiles_upper_bound;
+    if (pairs < 1) return MOKB_OK;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(pairs * 2));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MOKB_CUDA(cudaLaunchKernelEx(&cfg, grouped_gemm_mxfp8_kernel<MODE>, m, p));
+    note_launch();
+    return MOKB_OK;
+}
+
+int data_map(CUtensorMap* out, const void* base, uint64_t k, uint64_t rows) {
+    return make_tmap_2d(out, base, 1, k, rows, k, 128, 128);
+}
+int scale_map(CUtensorMap* out, const void* base, uint64_t tiles) {
+    return make_tmap_2d(out, base, 4, 128, tiles, 512, 128, 1);
+}
+
+}  // namespace
+}  // namespace mokb
+
+using namespace mokb;
+
+extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    MOKB_REQUIRE(g != nullptr, "grouped_gemm_mxfp8: null args");
+    MOKB_REQUIRE(g->mode >= 0 && g->mode <= 2, "grouped_gemm_mxfp8: unknown mode %d", g->mode);
+    MOKB_REQUIRE(g->A && g->A_sc && g->B && g->B_sc && g->D && g->status, "grouped_gemm_mxfp8: null pointer");
+    MOKB_REQUIRE(g->G >= 1 && g->ldd % 8 == 0, "grouped_gemm_mxfp8: bad G or ldd");
+    MOKB_REQUIRE(g->rows_static > 0 && g->rows_static % 256 == 0, "grouped_gemm_mxfp8: rows must be a positive multiple of 256");
+    FParams p;
+    memset(&p, 0, sizeof(p));
+    p.rows_cap = g->rows_static;
+    p.row_begin = g->row_begin;
+    p.row_end = g->row_end > 0 ? g->row_end : g->rows_static;
+    MOKB_REQUIRE(p.row_begin >= 0 && p.row_begin % 256 == 0 && p.row_end % 256 == 0 && p.row_begin <= p.row_end && p.row_end <= g->rows_static,
+                 "grouped_gemm_mxfp8: bad row window");
+    p.num_rows = g->num_rows;
+    p.group_of_block = g->group_of_block;
+    p.group_offsets = g->group_offsets;
+    p.G = g->G; p.M = g->M; p.N = g->N; p.K = g->K;
+    p.D = static_cast<__nv_bfloat16*>(g->D);
+    p.D2 = static_cast<__nv_bfloat16*>(g->D2);
+    p.ldd = g->ldd;
+    p.status = g->status;
+    Maps m;
+    memset(&m, 0, sizeof(m));
+    const uint64_t rows = static_cast<uint64_t>(g->rows_static);
+    const int m_tiles = (p.row_end - p.row_begin) / TILE_M;
+    if (g->mode == FMODE_WGRAD) {
+        // A [M, rows], B [N, rows]: the contraction runs over the token axis, one window per group
+        MOKB_REQUIRE(g->M > 0 && g->M % 128 == 0 && g->N > 0 && g->N % 128 == 0, "grouped_gemm_mxfp8 WGRAD: M and N must be multiples of 128");
+        MOKB_REQUIRE(g->group_offsets != nullptr, "grouped_gemm_mxfp8 WGRAD: group_offsets required");
+        MOKB_TRY(data_map(&m.A, g->A, rows, g->M));
+        MOKB_TRY(data_map(&m.B, g->B, rows, g->N));
+        MOKB_TRY(scale_map(&m.SA, g->A_sc, static_cast<uint64_t>(g->M / 128) * (rows / 128)));
+        MOKB_TRY(scale_map(&m.SB, g->B_sc, static_cast<uint64_t>(g->N / 128) * (rows / 128)));
+        m.A2 = m.A; m.B2 = m.B; m.SA2 = m.SA; m.SB2 = m.SB;
+        p.a_ktiles = p.b_ktiles = static_cast<int>(rows / 128);
+        return launch<FMODE_WGRAD>(m, p, g->G * ((g->M + TILE_M - 1) / TILE_M) * ((g->N + BN - 1) / BN), stream);
+    }
+    MOKB_REQUIRE(g->K > 0 && g->K % 128 == 0 && g->N > 0 && g->N % 128 == 0, "grouped_gemm_mxfp8: K and N must be multiples of 128");
+    const uint64_t brows = static_cast<uint64_t>(g->G) * g->N;
+    MOKB_TRY(data_map(&m.A, g->A, g->K, rows));
+    MOKB_TRY(data_map(&m.B, g->B, g->K, brows));
+    MOKB_TRY(scale_map(&m.SA, g->A_sc, (rows / 128) * (g->K / 128)));
+    MOKB_TRY(scale_map(&m.SB, g->B_sc, (brows / 128) * (g->K / 128)));
+    m.A2 = m.A; m.B2 = m.B; m.SA2 = m.SA; m.SB2 = m.SB;
+    p.a_ktiles = p.b_ktiles = g->K / 128;
+    p.b_rows_per_group = g->N;
+    if (g->mode == FMODE_DUALB) {
+        MOKB_REQUIRE(g->B2 && g->B2_sc && g->D2, "grouped_gemm_mxfp8 DUALB: B2, B2_sc and D2 required");
+        MOKB_TRY(data_map(&m.B2, g->B2, g->K, brows));
+        MOKB_TRY(scale_map(&m.SB2, g->B2_sc, (brows / 128) * (g->K / 128)));
+        return launch<FMODE_DUALB>(m, p, m_tiles * (g->N / 128), stream);
+    }
+    if (g->A2) {
+        MOKB_REQUIRE(g->A2_sc && g->B2 && g->B2_sc, "grouped_gemm_mxfp8: the second operand pair needs data and scales");
+        MOKB_TRY(data_map(&m.A2, g->A2, g->K, rows));
+        MOKB_TRY(data_map(&m.B2, g->B2, g->K, brows));
+        MOKB_TRY(scale_map(&m.SA2, g->A2_sc, (rows / 128) * (g->K / 128)));
+        MOKB_TRY(scale_map(&m.SB2, g->B2_sc, (brows / 128) * (g->K / 128)));
+        p.dual = 1;
+    }
+    return launch<FMODE_NT>(m, p, m_tiles * ((g->N + BN - 1) / BN), stream);
+}

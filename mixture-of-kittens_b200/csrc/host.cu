@@ -63,15 +63,19 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t in
     }
     MOKB_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor base %p is not 16-byte aligned", base);
     MOKB_REQUIRE(row_stride_bytes % 16 == 0, "row stride %llu B is not a multiple of 16", (unsigned long long)row_stride_bytes);
-    MOKB_REQUIRE(box_inner * elem_bytes == 128, "swizzled box must be 128 B wide");
-    MOKB_REQUIRE(box_outer >= 1 && box_outer <= 256, "box height %u out of range", box_outer);
+    // elem_bytes 2 = bf16 and 1 = u8, 128-byte swizzle; elem_bytes 4 = u32 rows copied as they are (scale tiles)
+    const bool plain = elem_bytes == 4;
+    MOKB_REQUIRE(plain || box_inner * elem_bytes == 128, "swizzled box must be 128 B wide");
+    MOKB_REQUIRE(box_inner <= 256 && box_outer >= 1 && box_outer <= 256, "box %ux%u out of range", box_inner, box_outer);
     cuuint64_t dims[2] = {inner, outer};
     cuuint64_t strides[1] = {row_stride_bytes};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
-    CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                             : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    plain ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu outer=%llu stride=%llu box=%ux%u)", (int)r,
                   (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)row_stride_bytes, box_inner, box_outer);

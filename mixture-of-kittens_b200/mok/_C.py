@@ -74,6 +74,13 @@ class GemmArgs(ctypes.Structure):
                 ("swiglu_limit", c_f32), ("status", c_vp)]
 
 
+class GemmFp8Args(ctypes.Structure):
+    _fields_ = [("mode", c_int), ("rows_static", c_int), ("row_begin", c_int), ("row_end", c_int), ("num_rows", c_vp),
+                ("group_of_block", c_vp), ("group_offsets", c_vp), ("G", c_int), ("M", c_int), ("N", c_int), ("K", c_int),
+                ("A", c_vp), ("A_sc", c_vp), ("B", c_vp), ("B_sc", c_vp), ("A2", c_vp), ("A2_sc", c_vp), ("B2", c_vp),
+                ("B2_sc", c_vp), ("D", c_vp), ("D2", c_vp), ("ldd", c_int), ("status", c_vp)]
+
+
 def _sig(name, restype, *argtypes):
     fn = getattr(lib, name)
     fn.restype = restype
@@ -99,6 +106,7 @@ _sig("mokb_layer_scratch_bytes", c_sz, c_int, c_int, c_int)
 _sig("mokb_dispatch_mlp_swiglu_combine_fwd_bf16", c_int, ctypes.POINTER(FwdArgs), c_vp)
 _sig("mokb_dispatch_mlp_swiglu_combine_bwd_bf16", c_int, ctypes.POINTER(BwdArgs), c_vp)
 _sig("mokb_grouped_gemm_bf16", c_int, ctypes.POINTER(GemmArgs), c_vp)
+_sig("mokb_grouped_gemm_mxfp8", c_int, ctypes.POINTER(GemmFp8Args), c_vp)
 _sig("mokb_dispatch_rows", c_int, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_i64, c_vp, c_u64p, c_vp, c_vp)
 _sig("mokb_combine_rows", c_int, c_vp, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_vp, c_u64p, c_vp)
 _sig("mokb_swiglu_fwd", c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_f32, c_vp)
@@ -109,7 +117,7 @@ EXPORTED = [
     "mokb_all_gather_top_experts", "mokb_barrier_all", "mokb_schedule_scratch_bytes", "mokb_schedule", "mokb_schedule_noalloc",
     "mokb_mxfp8_quantize", "mokb_fwd_epilogue", "mokb_bwd_epilogue", "mokb_layer_scratch_bytes",
     "mokb_dispatch_mlp_swiglu_combine_fwd_bf16", "mokb_dispatch_mlp_swiglu_combine_bwd_bf16",
-    "mokb_grouped_gemm_bf16", "mokb_dispatch_rows", "mokb_combine_rows", "mokb_swiglu_fwd", "mokb_swiglu_bwd",
+    "mokb_grouped_gemm_bf16", "mokb_grouped_gemm_mxfp8", "mokb_dispatch_rows", "mokb_combine_rows", "mokb_swiglu_fwd", "mokb_swiglu_bwd",
 ]
 
 
@@ -405,6 +413,22 @@ def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None
     g.swiglu_limit = 0.0 if swiglu_limit is None else float(swiglu_limit)
     g.status = _p(status_tensor(A.device))
     _ck(lib.mokb_grouped_gemm_bf16(ctypes.byref(g), _stream()))
+
+
+def grouped_gemm_mxfp8(mode, A, A_sc, B, B_sc, D, *, rows=None, num_rows=None, group_of_block=None, group_offsets=None,
+                       G=1, M=0, N=0, K=0, A2=None, A2_sc=None, B2=None, B2_sc=None, D2=None, ldd=None, row_begin=0, row_end=0):
+    g = GemmFp8Args()
+    g.mode = mode
+    g.rows_static = (A.shape[0] if mode != 2 else A.shape[1]) if rows is None else rows
+    g.row_begin, g.row_end = row_begin, row_end
+    g.num_rows, g.group_of_block, g.group_offsets = _p(num_rows), _p(group_of_block), _p(group_offsets)
+    g.G, g.M, g.N, g.K = G, M, N, K
+    g.A, g.A_sc, g.B, g.B_sc = _p(A), _p(A_sc), _p(B), _p(B_sc)
+    g.A2, g.A2_sc, g.B2, g.B2_sc = _p(A2), _p(A2_sc), _p(B2), _p(B2_sc)
+    g.D, g.D2 = _p(D), _p(D2)
+    g.ldd = D.shape[-1] if ldd is None else ldd
+    g.status = _p(status_tensor(A.device))
+    _ck(lib.mokb_grouped_gemm_mxfp8(ctypes.byref(g), _stream()))
 
 
 def dispatch_rows(src_ptrs, peer_rank, peer_token_idx, num_rows, max_rows, row_divisor, hidden, dst,

@@ -1,0 +1,104 @@
+"""GPU parity of the block-scaled MXFP8 grouped GEMM against fp32 matmuls of the de-quantised
+operands (products of E4M3 values and power-of-two scales are exact in fp32, so only the
+summation order and the final bf16 rounding differ)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mok_oracle as O
+from tests.gpu_common import GEMM_TOL, assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def quant(x):
+    """bf16 [.., R, C] -> (fp8 cuda, packed scales cuda, de-quantised fp32 cpu), blocks along the last axis."""
+    q, s, _, _ = O.mxfp8_quantize(x, True, False)
+    deq = O.dequantize(q.reshape(-1, x.shape[-1]), s).reshape(x.shape)
+    return q.cuda(), s.cuda(), deq
+
+
+def groups(rows_per_group):
+    offs = np.concatenate([[0], np.cumsum(rows_per_group)]).astype(np.int32)
+    gob = np.concatenate([np.full(n // 128, g, np.int32) for g, n in enumerate(rows_per_group)] or [np.zeros(0, np.int32)])
+    return torch.from_numpy(offs).cuda(), torch.from_numpy(gob).cuda(), int(offs[-1])
+
+
+@pytest.mark.parametrize("dual", [False, True])
+@pytest.mark.parametrize("rows_per_group,N,K", [([256], 256, 128), ([512, 0, 256], 384, 512), ([256, 768], 256, 1024)])
+def test_mxfp8_gemm_nt(rows_per_group, N, K, dual):
+    from mok import _C
+    offs, gob, rows = groups(rows_per_group)
+    G_ = len(rows_per_group)
+    g = torch.Generator().manual_seed(31)
+    A = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    W = (torch.randn(G_, N, K, generator=g) * 0.1).to(torch.bfloat16)
+    Aq, As, Ad = quant(A)
+    Wq, Ws, Wd = quant(W)
+    extra = {}
+    if dual:
+        A2 = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+        W2 = (torch.randn(G_, N, K, generator=g) * 0.1).to(torch.bfloat16)
+        A2q, A2s, A2d = quant(A2)
+        W2q, W2s, W2d = quant(W2)
+        extra = dict(A2=A2q, A2_sc=A2s, B2=W2q, B2_sc=W2s)
+    D = torch.full((rows, N), 3.0, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm_mxfp8(0, Aq, As, Wq, Ws, D, group_of_block=gob, G=G_, N=N, K=K, **extra)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0
+    o = offs.cpu().numpy()
+    for gi in range(G_):
+        s, e = int(o[gi]), int(o[gi + 1])
+        if s == e:
+            continue
+        ref = Ad[s:e] @ Wd[gi].T
+        if dual:
+            ref = ref + A2d[s:e] @ W2d[gi].T
+        assert_close(f"group {gi}", ref.to(torch.bfloat16), D[s:e], GEMM_TOL)
+
+
+def test_mxfp8_gemm_dual_b():
+    from mok import _C
+    rows_per_group, N, K = [512, 256], 384, 256
+    offs, gob, rows = groups(rows_per_group)
+    g = torch.Generator().manual_seed(32)
+    A = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    Wg = (torch.randn(2, N, K, generator=g) * 0.1).to(torch.bfloat16)
+    Wu = (torch.randn(2, N, K, generator=g) * 0.1).to(torch.bfloat16)
+    Aq, As, Ad = quant(A)
+    Gq, Gs, Gd = quant(Wg)
+    Uq, Us, Ud = quant(Wu)
+    D = torch.empty(rows, N, dtype=torch.bfloat16, device="cuda")
+    D2 = torch.empty(rows, N, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm_mxfp8(1, Aq, As, Gq, Gs, D, group_of_block=gob, G=2, N=N, K=K, B2=Uq, B2_sc=Us, D2=D2)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0
+    o = offs.cpu().numpy()
+    for gi in range(2):
+        s, e = int(o[gi]), int(o[gi + 1])
+        assert_close("gate", (Ad[s:e] @ Gd[gi].T).to(torch.bfloat16), D[s:e], GEMM_TOL)
+        assert_close("up", (Ad[s:e] @ Ud[gi].T).to(torch.bfloat16), D2[s:e], GEMM_TOL)
+
+
+@pytest.mark.parametrize("cols_per_group,M,N", [([256], 128, 256), ([512, 0, 256], 256, 384), ([256, 1024], 384, 512)])
+def test_mxfp8_gemm_wgrad(cols_per_group, M, N):
+    from mok import _C
+    offs, gob, cols = groups(cols_per_group)
+    G_ = len(cols_per_group)
+    g = torch.Generator().manual_seed(33)
+    A = torch.randn(M, cols, generator=g).to(torch.bfloat16)       # token axis contiguous, quantised along it
+    B = torch.randn(N, cols, generator=g).to(torch.bfloat16)
+    Aq, As, Ad = quant(A)
+    Bq, Bs, Bd = quant(B)
+    D = torch.full((G_, M, N), 5.0, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm_mxfp8(2, Aq, As, Bq, Bs, D, group_offsets=offs, G=G_, M=M, N=N)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0
+    o = offs.cpu().numpy()
+    for gi in range(G_):
+        s, e = int(o[gi]), int(o[gi + 1])
+        if e == s:
+            assert torch.all(D[gi] == 0)
+            continue
+        ref = (Ad[:, s:e] @ Bd[:, s:e].T).to(torch.bfloat16)
+        assert_close(f"wgrad {gi}", ref, D[gi], (GEMM_TOL[0] * 8, GEMM_TOL[1]))
