@@ -261,6 +261,8 @@ typedef struct {
 
 int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_args* args, void* stream);
 int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_args* args, void* stream);
+/* sizeof() of {mokb_fwd_mxfp8_args, mokb_bwd_mxfp8_args}. */
+int mokb_struct_sizes_mxfp8(int* out, int n);
 
 /* ---- building blocks, exported for tests and micro-benchmarks.  They are the
  * kernels the two layer calls above are made of. */

@@ -415,3 +415,10 @@ def bwd_epilogue(d_x_shared: torch.Tensor, d_x_routed_buffer: torch.Tensor) -> t
 
 
 _fake_impls.register()
+
+# the MXFP8 layer operators live in their own module; `mok.ops` is the one public namespace
+from .ops_mxfp8 import (  # noqa: E402,F401
+    dispatch_mlp_swiglu_combine_bwd_mxfp8,
+    dispatch_mlp_swiglu_combine_fwd_mxfp8,
+    recompute_forward_context_mxfp8,
+)
