@@ -173,6 +173,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-mxfp8", action="store_true", help="skip the MXFP8 leg (reported under the key \"mxfp8\")")
     ap.add_argument("--kernel-only", action="store_true", help="time only the dominant GEMM (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if not args.kernel_only else args.warmup
@@ -319,6 +320,38 @@ def main():
                 "peak_source": f"{peak_kind} cuBLAS bf16 burst", "traffic": traffic,
                 "launch_ms": kern["ms"], "flops_per_launch": kern["flops_per_launch"]}
 
+    # ---- the same step with the routed experts in MXFP8 (weights pre-quantised outside the step, as the reference does)
+    mx = None
+    if not args.no_mxfp8:
+        from mok import ops
+        qg, qu, qd = (ops.mxfp8_quantize(w_, True, True) for w_ in (wrg, wru, wrd))
+
+        def step_mx(mark=False):
+            sched = F.build_schedule(ws, cfg, te_d, num_local_experts=E_l)
+            out, ctx = F.forward(cfg, ws, sched, x_d, rw_d, wsg, wsu, wsd, (qg[0], qg[1]), (qu[0], qu[1]), (qd[0], qd[1]))
+            if mark:
+                marks["mid"].record()
+            return F.backward(cfg, ws, sched, ctx, gy_d, x_d, rw_d, wsg, wsu, wsd, qg, qu, (qd[2], qd[3]))
+        for _ in range(args.warmup):
+            step_mx()
+        torch.cuda.synchronize()
+        mx_ms = timed(step_mx, args.steps) / args.steps
+        mx_f, mx_b = [], []
+        for _ in range(2):
+            torch.cuda.synchronize()
+            ev[0].record()
+            step_mx(mark=True)
+            ev[2].record()
+            torch.cuda.synchronize()
+            mx_f.append(ev[0].elapsed_time(ev[1]))
+            mx_b.append(ev[1].elapsed_time(ev[2]))
+        assert _C.check_status() == 0, "device status word set during the MXFP8 steps"
+        mx = {"value": T * world / (mx_ms / 1000.0), "unit": "tokens/s", "ms_per_step": mx_ms,
+              "tflops_per_gpu": layer_flops(T, K, H, I) / (mx_ms / 1000.0) / 1e12,
+              "fwd_ms": statistics.median(mx_f), "bwd_ms": statistics.median(mx_b),
+              "note": "routed experts in block-scaled E4M3 (tcgen05 mxf8f6f4), shared expert BF16; inputs resident in HBM"}
+        del qg, qu, qd
+
     if rank == 0:
         tokens = T * world
         flops = layer_flops(T, K, H, I)
@@ -336,6 +369,8 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clock_summary,
         }
+        if mx is not None:
+            line["mxfp8"] = mx
         if world == 1 and not args.no_cpu_baseline:
             Ts, Es, dt = cpu_oracle_sample(H, I, K)
             line["cpu_baseline"] = {

@@ -61,6 +61,25 @@ def main():
             checks[name] = [mx, rel, good]
             ok &= good
         report["checks"][f"case{case}"] = checks
+        if case == 0:
+            # the same layer with the routed experts in MXFP8, against the oracle's MXFP8 dataflow
+            from mok import ops
+            refq = O.layer_forward_backward(ranks, swiglu_limit=limit, schedule_capacity_factor=factor, mxfp8=True)[rank]
+            qg, qu, qd = (ops.mxfp8_quantize(w, True, True) for w in (inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down))
+            sched = F.build_schedule(ws, cfg, inp.top_experts, num_local_experts=E_l)
+            out, ctx = F.forward(cfg, ws, sched, inp.x, inp.router_weights, inp.w_shared_gate, inp.w_shared_up,
+                                 inp.w_shared_down, (qg[0], qg[1]), (qu[0], qu[1]), (qd[0], qd[1]), limit)
+            grads = F.backward(cfg, ws, sched, ctx, inp.grad_output, inp.x, inp.router_weights, inp.w_shared_gate,
+                               inp.w_shared_up, inp.w_shared_down, qg, qu, (qd[2], qd[3]), limit)
+            torch.cuda.synchronize()
+            mchecks = {"status": _C.check_status()}
+            ok &= mchecks["status"] == 0
+            for name, got in zip(names, (out, *grads)):
+                mx, rel = O.error_stats(refq[name], got.cpu())
+                good = bool(np.isfinite(mx) and mx <= 1.0 and rel <= 0.03)
+                mchecks[name] = [mx, rel, good]
+                ok &= good
+            report["checks"]["case0_mxfp8"] = mchecks
     report["ok"] = bool(ok)
     out_dir = os.environ.get("MOKB_TEST_OUT", "/tmp")
     with open(os.path.join(out_dir, f"multirank_rank{rank}.json"), "w") as f:
