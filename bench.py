@@ -45,6 +45,7 @@ WORKLOADS = {
     "c1": (1024, 1024, 512, 8, 2, 256, 0.5, "router"),
     "c4": (16384, 4096, 1536, 128, 8, 8192, 1.0, "zipf"),
     "c5": (16384, 5120, 1408, 64, 6, 8192, 0.5, "gaussian"),
+    "c2r": (16384, 7168, 2048, 32, 8, 8192, 0.5, "gaussian"),    # one rank's share of c2 at EP=8 (32 experts), without the NVLink part
     "small": (4096, 2048, 1024, 32, 4, 2048, 0.5, "gaussian"),   # for profiler captures: a few GB on the device
 }
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"

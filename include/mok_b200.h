@@ -289,6 +289,7 @@ typedef struct {
     int ldd;
     int has_swiglu_limit;
     float swiglu_limit;
+    int accumulate;             /* mode 3: D[g] += result (read, add in fp32, round to bf16); empty groups are left alone */
     int32_t* status;
 } mokb_gemm_args;
 int mokb_grouped_gemm_bf16(const mokb_gemm_args* args, void* stream);

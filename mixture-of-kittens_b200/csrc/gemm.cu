@@ -67,6 +67,7 @@ struct KParams {
     int ldd;
     int has_limit;
     float limit;
+    int accumulate;                  // MODE_WGRAD: add to the stored bf16 result instead of overwriting it
     int32_t* status;
 };
 
@@ -86,7 +87,7 @@ struct Sched {
             total = p.G * m_blocks * n_blocks;
         } else {
             int rows = p.num_rows ? *p.num_rows : p.rows_cap;
-            if (rows < 0 || rows > p.rows_cap) rows = 0;
+            if (rows < 0) rows = 0;                 // the row window below never exceeds the tensors (row_end <= rows_cap)
             const int hi = min(rows, p.row_end), lo = min(p.row_begin, hi);
             m_first = lo / TM;
             m_blocks = (hi - lo) / TM;
@@ -364,11 +365,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (c * 32 >= cols_left) break;
                     uint32_t r[32];
                     if (empty_k) {
+                        if (MODE == MODE_WGRAD && p.accumulate) break;      // nothing to add: leave the stored gradient
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = 0u;
                     } else {
                         tmem_ld_32x32(t_addr + c * 32, r);     // whole warp, also for rows that are not stored
                         tmem_ld_wait();
+                    }
+                    if (MODE == MODE_WGRAD && p.accumulate && row_ok) {
+                        const uint4* old = reinterpret_cast<const uint4*>(dst + c * 32);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 o = old[q];
+                            const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 f = unpack_bf16(ow[j]);
+                                r[8 * q + 2 * j] = __float_as_uint(__uint_as_float(r[8 * q + 2 * j]) + f.x);
+                                r[8 * q + 2 * j + 1] = __float_as_uint(__uint_as_float(r[8 * q + 2 * j + 1]) + f.y);
+                            }
+                        }
                     }
                     if (row_ok) store_row32(dst + c * 32, r);
                 }
@@ -472,6 +488,7 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     p.D2 = static_cast<__nv_bfloat16*>(g->D2);
     p.D3 = static_cast<__nv_bfloat16*>(g->D3);
     p.ldd = g->ldd;
+    p.accumulate = g->accumulate;
     p.has_limit = g->has_swiglu_limit;
     p.limit = g->swiglu_limit;
     p.status = g->status;

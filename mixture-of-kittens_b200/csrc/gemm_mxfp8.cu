@@ -75,7 +75,7 @@ struct Sched {
             total = p.G * m_blocks * n_blocks;
         } else {
             int rows = p.num_rows ? *p.num_rows : p.rows_cap;
-            if (rows < 0 || rows > p.rows_cap) rows = 0;
+            if (rows < 0) rows = 0;                 // the row window below never exceeds the tensors (row_end <= rows_cap)
             const int hi = min(rows, p.row_end), lo = min(p.row_begin, hi);
             m_first = lo / TILE_M;
             m_blocks = (hi - lo) / TILE_M;

@@ -17,124 +17,21 @@
 //             caller: prologue | shared backward (6 launches) | routed dgrads | routed wgrads
 //             side 2:                                                          combine of d_x + router grads
 //
+// Macrobatches (csrc/megakernel/types.cuh:86-106, forward.cuh:89-131, backward.cuh:286-329 of the
+// reference): the routed buffers hold `macrobatch_size` rows; when the schedule has more, the rows
+// are processed MB at a time.  The forward walks the macrobatches from the last to the first, so
+// that macrobatch 0's intermediates are what stays saved; the backward consumes the saved context
+// for macrobatch 0, and for every later one replays dispatch + gate/up + SwiGLU first.  Weight
+// gradients of later macrobatches are added to the stored bf16 gradient in macrobatch order, which
+// keeps results bit-reproducible.  How many macrobatches are non-empty is only known on the
+// device: all ceil(capacity / MB) are enqueued and the empty ones find no rows.
+//
 // No kernel waits on another kernel; MOKB_OVERLAP=0 puts everything on the caller's stream.
-#include <stdlib.h>
-#include <string.h>
-
-#include "common.cuh"
+#include "layer_common.cuh"
 
 namespace mokb {
-namespace {
 
-struct Scratch {
-    int32_t* expert_offsets;   // [E_l + 1] row offset of each expert segment
-    int32_t* shared_offsets;   // [2] = {0, T}: the shared expert as a one-group problem
-    int32_t* n_rows;           // [1] validated number of routed rows (0 if it does not fit)
-    int32_t* group_of_block;   // [MB / 128]
-    float* w_row;              // [MB] router weight of each routed row (backward)
-    float* d_w_row;            // [MB] router-weight gradient of each routed row (backward)
-};
-
-size_t align256(size_t x) { return (x + 255) / 256 * 256; }
-
-Scratch carve(void* base, int E_l, int MB) {
-    char* p = static_cast<char*>(base);
-    Scratch s;
-    s.expert_offsets = reinterpret_cast<int32_t*>(p); p += align256((E_l + 1) * 4);
-    s.shared_offsets = reinterpret_cast<int32_t*>(p); p += 256;
-    s.n_rows = reinterpret_cast<int32_t*>(p); p += 256;
-    s.group_of_block = reinterpret_cast<int32_t*>(p); p += align256(static_cast<size_t>(MB / 128) * 4);
-    s.w_row = reinterpret_cast<float*>(p); p += align256(static_cast<size_t>(MB) * 4);
-    s.d_w_row = reinterpret_cast<float*>(p);
-    return s;
-}
-
-// One CTA: segment offsets from tokens_per_expert, row-block -> expert table,
-// and the capacity checks that the reference turns into a trap.
-__global__ void prologue_kernel(const int32_t* __restrict__ tokens_per_expert, const int32_t* __restrict__ num_tokens,
-                                int E_l, int capacity, int MB, int T, Scratch s, int32_t* status) {
-    __shared__ int32_t offs[2049];
-    __shared__ int32_t ok_s;
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int e = 0; e < E_l; ++e) {
-            offs[e] = run;
-            run += tokens_per_expert[e];
-        }
-        offs[E_l] = run;
-        const int n = *num_tokens;
-        int ok = 1;
-        if (n != run || n < 0 || n > capacity) { ok = 0; atomicCAS(status, MOKB_ST_OK, MOKB_ST_SCHEDULE_OVERFLOW); }
-        else if (n > MB) { ok = 0; atomicCAS(status, MOKB_ST_OK, MOKB_ST_MACROBATCH_OVERFLOW); }
-        ok_s = ok;
-        *s.n_rows = ok ? n : 0;
-        s.shared_offsets[0] = 0;
-        s.shared_offsets[1] = T;
-    }
-    __syncthreads();
-    const int ok = ok_s;
-    for (int e = threadIdx.x; e <= E_l; e += blockDim.x) s.expert_offsets[e] = ok ? offs[e] : 0;
-    const int nblocks = ok ? offs[E_l] / 128 : 0;
-    for (int b = threadIdx.x; b < MB / 128; b += blockDim.x) {
-        int g = -1;
-        if (b < nblocks) {
-            const int row = b * 128;
-            int lo = 0, hi = E_l;          // last e with offs[e] <= row
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (offs[mid] <= row) lo = mid; else hi = mid;
-            }
-            g = lo;
-        }
-        s.group_of_block[b] = g;
-    }
-}
-
-int run_prologue(const int32_t* tpe, const int32_t* num_tokens, int E_l, int C, int MB, int T, const Scratch& s,
-                 int32_t* status, cudaStream_t stream) {
-    MOKB_REQUIRE(E_l <= 2048, "layer: at most 2048 local experts");
-    prologue_kernel<<<1, 256, 0, stream>>>(tpe, num_tokens, E_l, C, MB, T, s, status);
-    MOKB_CUDA(cudaGetLastError());
-    note_launch();
-    return MOKB_OK;
-}
-
-mokb_gemm_args gemm_base(int32_t* status) {
-    mokb_gemm_args g;
-    memset(&g, 0, sizeof(g));
-    g.G = 1;
-    g.status = status;
-    return g;
-}
-
-template <class A>
-int check_common(const A* a, const char* who) {
-    MOKB_REQUIRE(a != nullptr, "%s: null args", who);
-    MOKB_REQUIRE(a->ep_size >= 1 && a->ep_size <= MOKB_MAX_EP && a->ep_rank >= 0 && a->ep_rank < a->ep_size, "%s: bad ep_size/ep_rank", who);
-    MOKB_REQUIRE(a->num_local_tokens > 0 && a->num_local_tokens % 256 == 0, "%s: num_local_tokens must be a positive multiple of 256", who);
-    MOKB_REQUIRE(a->hidden > 0 && a->hidden % 256 == 0, "%s: hidden must be a positive multiple of 256", who);
-    MOKB_REQUIRE(a->intermediate > 0 && a->intermediate % 128 == 0, "%s: intermediate must be a positive multiple of 128", who);
-    MOKB_REQUIRE(a->num_local_experts > 0 && a->topk > 0 && a->topk <= 255, "%s: bad expert/top-k counts", who);
-    MOKB_REQUIRE(a->schedule_capacity > 0 && a->schedule_capacity % 256 == 0, "%s: schedule_capacity must be a positive multiple of 256", who);
-    MOKB_REQUIRE(a->macrobatch_size > 0 && a->macrobatch_size % 256 == 0, "%s: macrobatch_size must be a positive multiple of 256", who);
-    MOKB_REQUIRE(a->minibatch_size > 0 && a->minibatch_size % 256 == 0, "%s: minibatch_size must be a positive multiple of 256", who);
-    MOKB_REQUIRE(a->num_comm_sms > 0, "%s: num_comm_sms must be positive", who);
-    MOKB_REQUIRE(a->peer_rank && a->peer_token_idx && a->num_tokens && a->tokens_per_expert, "%s: null schedule pointer", who);
-    MOKB_REQUIRE(a->scratch && a->status, "%s: scratch and status are required", who);
-    return MOKB_OK;
-}
-
-// ---- side streams and events, one set per device, created on first use
-constexpr int kMaxChunks = 32;
-
-struct Async {
-    bool ready = false;
-    cudaStream_t s1 = nullptr, s2 = nullptr;
-    cudaEvent_t fork = nullptr, join1 = nullptr, join2 = nullptr;
-    cudaEvent_t ev_in[kMaxChunks] = {nullptr};    // dispatch of chunk c finished
-    cudaEvent_t ev_out[kMaxChunks] = {nullptr};   // rows of chunk c are ready to be combined
-};
-Async g_async[64];
+static Async g_async[64];
 
 int get_async(Async** out) {
     int dev = -1;
@@ -165,22 +62,12 @@ bool overlap_enabled() {
     return v == 1;
 }
 
-// rows per communication/compute window: minibatch_size, coarsened so that at most kMaxChunks windows cover MB
-int chunk_rows_for(int MB, int minibatch) {
-    int rows = minibatch;
-    if ((MB + rows - 1) / rows > kMaxChunks) rows = static_cast<int>(align256((MB + kMaxChunks - 1) / kMaxChunks));
-    return rows;
-}
-
-}  // namespace
 }  // namespace mokb
 
 using namespace mokb;
 
 extern "C" size_t mokb_layer_scratch_bytes(int schedule_capacity, int num_local_experts, int macrobatch_size) {
-    (void)schedule_capacity;
-    return align256((num_local_experts + 1) * 4) + 512 + align256(static_cast<size_t>(macrobatch_size / 128) * 4) +
-           2 * align256(static_cast<size_t>(macrobatch_size) * 4);
+    return scratch_bytes(schedule_capacity, num_local_experts, macrobatch_size);
 }
 
 extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_args* a, void* stream_) {
@@ -193,72 +80,91 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_arg
     if (with_down)
         MOKB_REQUIRE(a->combine_ptrs_host && a->w_shared_down && a->w_routed_down && a->y_shared && a->y_routed, "fwd_bf16: null down/combine pointer");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
-    const Scratch s = carve(a->scratch, E_l, MB);
+    const int C = a->schedule_capacity;
+    const Scratch s = carve(a->scratch, C, E_l, MB);
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
     cudaStream_t s_in = overlap ? as->s1 : stream, s_out = overlap ? as->s2 : stream;
     const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
-    const int chunk = chunk_rows_for(MB, a->minibatch_size);
-    const int nchunks = (MB + chunk - 1) / chunk;
+    // recompute only rebuilds macrobatch 0 (the saved context); the forward walks all of them, last first
+    const int n_macro = with_down ? macrobatches(C, MB) : 1;
 
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, s, a->status, stream));
-    if (overlap) {
-        MOKB_CUDA(cudaEventRecord(as->fork, stream));
-        MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
-        if (with_down) MOKB_CUDA(cudaStreamWaitEvent(s_out, as->fork, 0));
-    }
-    // dispatch: pull every scheduled row from its home rank, window by window
-    for (int c = 0; c < nchunks; ++c) {
-        const int r0 = c * chunk, r1 = r0 + chunk < MB ? r0 + chunk : MB;
-        MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, r0, r1, a->topk, H,
-                                    a->x_routed, nullptr, nullptr, comm_blocks, s_in));
-        if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
-    }
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, false, s, a->status, stream));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
+    bool shared_done = false;
 
-    // shared expert: gate/up + SwiGLU in one pass, then down (independent of the dispatch)
-    mokb_gemm_args g = gemm_base(a->status);
-    g.mode = 1; g.rows_static = T; g.N = I; g.K = H;
-    g.A = x_local; g.lda = H; g.B = a->w_shared_gate; g.B2 = a->w_shared_up; g.ldb = H;
-    g.D = a->gate_shared; g.D2 = a->up_shared; g.D3 = a->hidden_shared; g.ldd = I;
-    g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    if (with_down) {
-        g = gemm_base(a->status);
-        g.mode = 0; g.rows_static = T; g.N = H; g.K = I;
-        g.A = a->hidden_shared; g.lda = I; g.B = a->w_shared_down; g.ldb = I; g.D = a->y_shared; g.ldd = H;
-        MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    }
+    for (int mi = 0; mi < n_macro; ++mi) {
+        const int m = n_macro - 1 - mi;
+        const int lo = m * MB, hi = (lo + MB < C) ? lo + MB : C;
+        // only macrobatch 0 (the one that is always populated) is cut into overlap windows
+        const int chunk = m == 0 ? chunk_rows_for(MB, a->minibatch_size) : MB;
+        const int nchunks = (hi - lo + chunk - 1) / chunk;
+        void* x_routed = rebase(a->x_routed, lo, 2ull * H);
+        void* gate_r = rebase(a->gate_routed, lo, 2ull * I);
+        void* up_r = rebase(a->up_routed, lo, 2ull * I);
+        void* hidden_r = rebase(a->hidden_routed, lo, 2ull * I);
+        void* y_r = with_down ? rebase(a->y_routed, lo, 2ull * H) : nullptr;
 
-    // routed experts, window by window behind the dispatch
-    for (int c = 0; c < nchunks; ++c) {
-        const int r0 = c * chunk, r1 = r0 + chunk < MB ? r0 + chunk : MB;
-        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
-        g = gemm_base(a->status);
-        g.mode = 1; g.rows_static = MB; g.row_begin = r0; g.row_end = r1;
-        g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
-        g.A = a->x_routed; g.lda = H; g.B = a->w_routed_gate; g.B2 = a->w_routed_up; g.ldb = H;
-        g.D = a->gate_routed; g.D2 = a->up_routed; g.D3 = a->hidden_routed; g.ldd = I;
-        g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
-        MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-        if (!with_down) continue;
-        g = gemm_base(a->status);
-        g.mode = 0; g.rows_static = MB; g.row_begin = r0; g.row_end = r1;
-        g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = H; g.K = I;
-        g.A = a->hidden_routed; g.lda = I; g.B = a->w_routed_down; g.ldb = I; g.D = a->y_routed; g.ldd = H;
-        MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-        // combine: push the window's rows back to slot t*K+k of their home ranks
-        if (overlap) {
-            MOKB_CUDA(cudaEventRecord(as->ev_out[c], stream));
-            MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[c], 0));
+        if (overlap) {     // everything enqueued so far (previous macrobatch included) precedes this one's side work
+            MOKB_CUDA(cudaEventRecord(as->fork, stream));
+            MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
+            if (with_down) MOKB_CUDA(cudaStreamWaitEvent(s_out, as->fork, 0));
         }
-        MOKB_TRY(combine_rows_impl(a->y_routed, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, r0, r1,
-                                   H, nullptr, nullptr, comm_blocks, s_out));
-    }
-    if (overlap && with_down) {
-        MOKB_CUDA(cudaEventRecord(as->join2, s_out));
-        MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
+        // dispatch: pull every scheduled row from its home rank, window by window
+        for (int c = 0; c < nchunks; ++c) {
+            const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
+            MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
+                                        x_routed, nullptr, nullptr, comm_blocks, s_in));
+            if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+        }
+
+        if (!shared_done) {
+            // shared expert: gate/up + SwiGLU in one pass, then down (independent of the dispatch)
+            shared_done = true;
+            mokb_gemm_args g = gemm_base(a->status);
+            g.mode = 1; g.rows_static = T; g.N = I; g.K = H;
+            g.A = x_local; g.lda = H; g.B = a->w_shared_gate; g.B2 = a->w_shared_up; g.ldb = H;
+            g.D = a->gate_shared; g.D2 = a->up_shared; g.D3 = a->hidden_shared; g.ldd = I;
+            g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
+            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+            if (with_down) {
+                g = gemm_base(a->status);
+                g.mode = 0; g.rows_static = T; g.N = H; g.K = I;
+                g.A = a->hidden_shared; g.lda = I; g.B = a->w_shared_down; g.ldb = I; g.D = a->y_shared; g.ldd = H;
+                MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+            }
+        }
+
+        // routed experts, window by window behind the dispatch
+        for (int c = 0; c < nchunks; ++c) {
+            const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
+            if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
+            mokb_gemm_args g = gemm_base(a->status);
+            g.mode = 1; g.rows_static = hi; g.row_begin = r0; g.row_end = r1;
+            g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
+            g.A = x_routed; g.lda = H; g.B = a->w_routed_gate; g.B2 = a->w_routed_up; g.ldb = H;
+            g.D = gate_r; g.D2 = up_r; g.D3 = hidden_r; g.ldd = I;
+            g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
+            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+            if (!with_down) continue;
+            g = gemm_base(a->status);
+            g.mode = 0; g.rows_static = hi; g.row_begin = r0; g.row_end = r1;
+            g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = H; g.K = I;
+            g.A = hidden_r; g.lda = I; g.B = a->w_routed_down; g.ldb = I; g.D = y_r; g.ldd = H;
+            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+            // combine: push the window's rows back to slot t*K+k of their home ranks
+            if (overlap) {
+                MOKB_CUDA(cudaEventRecord(as->ev_out[c], stream));
+                MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[c], 0));
+            }
+            MOKB_TRY(combine_rows_impl(y_r, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1,
+                                       H, nullptr, nullptr, comm_blocks, s_out));
+        }
+        if (overlap && with_down) {    // the next macrobatch overwrites y_routed: the combine must be done with it
+            MOKB_CUDA(cudaEventRecord(as->join2, s_out));
+            MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
+        }
     }
     return MOKB_OK;
 }
@@ -275,7 +181,8 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
                  a->d_hidden_shared && a->d_hidden_routed && a->d_y_routed && a->d_w_shared_gate && a->d_w_routed_gate &&
                  a->d_w_shared_up && a->d_w_routed_up && a->d_w_shared_down && a->d_w_routed_down, "bwd_bf16: null output");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
-    const Scratch s = carve(a->scratch, E_l, MB);
+    const int C = a->schedule_capacity;
+    const Scratch s = carve(a->scratch, C, E_l, MB);
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
@@ -283,251 +190,102 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
     const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
     const int lim = a->has_swiglu_limit;
     const float limv = a->swiglu_limit;
+    const int n_macro = macrobatches(C, MB);
 
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, s, a->status, stream));
-    if (overlap) {
-        MOKB_CUDA(cudaEventRecord(as->fork, stream));
-        MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
-    }
-    // reverse combine: pull d_y rows, scaled by the route's router weight (overlaps the shared expert's backward)
-    MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB, a->topk, H,
-                                a->d_y_routed, a->router_weight_ptrs_host, s.w_row, comm_blocks, s_in));
-    if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, false, s, a->status, stream));
     const void* d_y_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->d_y_ptrs_host[a->ep_rank]));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
-
-    // ---- shared expert
-    mokb_gemm_args g = gemm_base(a->status);
-    g.mode = 2; g.rows_static = T; g.N = I; g.K = H;
-    g.A = d_y_local; g.lda = H; g.B = a->w_shared_down; g.ldb = I; g.D = a->d_hidden_shared; g.ldd = I;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    MOKB_TRY(mokb_swiglu_bwd(a->gate_shared, a->up_shared, a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, nullptr,
-                             nullptr, T, I, lim, limv, stream));
-    g = gemm_base(a->status);
-    g.mode = 2; g.rows_static = T; g.N = H; g.K = I;
-    g.A = a->d_gate_shared; g.B = a->w_shared_gate; g.A2 = a->d_up_shared; g.B2 = a->w_shared_up; g.lda = I; g.ldb = H;
-    g.D = a->d_x_shared; g.ldd = H;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    auto wgrad = [&](const void* A, int M, const void* B, int N, void* D, int G, int rows, const int32_t* offs) -> int {
+    auto wgrad = [&](const void* A, int M, const void* B, int N, void* D, int G, int rows, const int32_t* offs, int accumulate) -> int {
         mokb_gemm_args w = gemm_base(a->status);
-        w.mode = 3; w.rows_static = rows; w.G = G; w.M = M; w.N = N; w.group_offsets = offs;
+        w.mode = 3; w.rows_static = rows; w.G = G; w.M = M; w.N = N; w.group_offsets = offs; w.accumulate = accumulate;
         w.A = A; w.lda = M; w.B = B; w.ldb = N; w.D = D; w.ldd = N;
         return mokb_grouped_gemm_bf16(&w, stream);
     };
-    MOKB_TRY(wgrad(d_y_local, H, a->hidden_shared, I, a->d_w_shared_down, 1, T, s.shared_offsets));
-    MOKB_TRY(wgrad(a->d_gate_shared, I, x_local, H, a->d_w_shared_gate, 1, T, s.shared_offsets));
-    MOKB_TRY(wgrad(a->d_up_shared, I, x_local, H, a->d_w_shared_up, 1, T, s.shared_offsets));
 
-    // ---- routed experts
-    if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
-    g = gemm_base(a->status);
-    g.mode = 2; g.rows_static = MB; g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
-    g.A = a->d_y_routed; g.lda = H; g.B = a->w_routed_down; g.ldb = I; g.D = a->d_hidden_routed; g.ldd = I;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    MOKB_TRY(mokb_swiglu_bwd(a->gate_routed, a->up_routed, a->d_hidden_routed, a->d_gate_routed, a->d_up_routed, s.w_row, s.d_w_row,
-                             s.n_rows, MB, I, lim, limv, stream));
-    g = gemm_base(a->status);
-    g.mode = 2; g.rows_static = MB; g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = H; g.K = I;
-    g.A = a->d_gate_routed; g.B = a->w_routed_gate; g.A2 = a->d_up_routed; g.B2 = a->w_routed_up; g.lda = I; g.ldb = H;
-    g.D = a->d_x_routed; g.ldd = H;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    // reverse dispatch: push d_x rows and the per-route router-weight gradient home (overlaps the weight gradients)
-    if (overlap) {
-        MOKB_CUDA(cudaEventRecord(as->ev_out[0], stream));
-        MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[0], 0));
-    }
-    MOKB_TRY(combine_rows_impl(a->d_x_routed, a->d_x_routed_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB,
-                               H, s.d_w_row, a->d_router_weight_ptrs_host, comm_blocks, s_out));
-    if (overlap) MOKB_CUDA(cudaEventRecord(as->join2, s_out));
-    MOKB_TRY(wgrad(a->d_y_routed, H, a->hidden_routed, I, a->d_w_routed_down, E_l, MB, s.expert_offsets));
-    MOKB_TRY(wgrad(a->d_gate_routed, I, a->x_routed, H, a->d_w_routed_gate, E_l, MB, s.expert_offsets));
-    MOKB_TRY(wgrad(a->d_up_routed, I, a->x_routed, H, a->d_w_routed_up, E_l, MB, s.expert_offsets));
-    if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
-    return MOKB_OK;
-}
+    for (int m = 0; m < n_macro; ++m) {
+        const int lo = m * MB, hi = (lo + MB < C) ? lo + MB : C;
+        // the saved context and the routed work buffers, addressed by schedule row
+        void* x_routed = rebase(const_cast<void*>(a->x_routed), lo, 2ull * H);
+        void* gate_r = rebase(const_cast<void*>(a->gate_routed), lo, 2ull * I);
+        void* up_r = rebase(const_cast<void*>(a->up_routed), lo, 2ull * I);
+        void* hidden_r = rebase(const_cast<void*>(a->hidden_routed), lo, 2ull * I);
+        void* d_y_r = rebase(a->d_y_routed, lo, 2ull * H);
+        void* d_hidden_r = rebase(a->d_hidden_routed, lo, 2ull * I);
+        void* d_gate_r = rebase(a->d_gate_routed, lo, 2ull * I);
+        void* d_up_r = rebase(a->d_up_routed, lo, 2ull * I);
+        void* d_x_r = rebase(a->d_x_routed, lo, 2ull * H);
+        float* w_row = rebase(s.w_row, lo, 4);
+        float* d_w_row = rebase(s.d_w_row, lo, 4);
 
-// ============================================================================
-// MXFP8: routed experts in block-scaled E4M3, shared expert in BF16
-// (reference: csrc/megakernel/forward.cuh:296-428, backward.cuh:448-679).
-//
-// Dataflow (quantisation points as in the reference):
-//   forward   dispatch x -> quantise x row-wise (GEMM operand) and token-wise (saved for wgrad)
-//             gate, up = x_q * Wg_q^T, x_q * Wu_q^T (bf16) -> SwiGLU -> quantise gate, up (saved),
-//             hidden row-wise (GEMM operand) and token-wise (saved) -> y = hidden_q * Wd_q^T -> combine
-//   backward  pull d_y * w -> quantise both ways -> d_hidden = d_y_q * WdT_q^T
-//             -> de-quantise saved gate/up, SwiGLU backward, router-gradient partials, quantise d_gate, d_up
-//             both ways -> d_x = d_gate_q * WgT_q^T + d_up_q * WuT_q^T -> combine;
-//             weight gradients contract the token-wise quantised tensors over each expert's rows.
-// Dispatch / combine overlap the shared expert's BF16 GEMMs and the weight gradients on the side streams.
-namespace mokb {
-namespace {
+        if (overlap) {     // the previous macrobatch's weight gradients still read the buffers the dispatches below overwrite
+            MOKB_CUDA(cudaEventRecord(as->fork, stream));
+            MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
+        }
+        // replay (later macrobatches only): pull x again; the saved context holds macrobatch 0
+        if (m > 0)
+            MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
+                                        x_routed, nullptr, nullptr, comm_blocks, s_in));
+        // reverse combine: pull d_y rows, scaled by the route's router weight
+        MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
+                                    d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in));
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
 
-mokb_gemm_fp8_args fp8_base(int32_t* status) {
-    mokb_gemm_fp8_args g;
-    memset(&g, 0, sizeof(g));
-    g.G = 1;
-    g.status = status;
-    return g;
-}
+        if (m == 0) {
+            // ---- shared expert (overlaps the dispatch above)
+            mokb_gemm_args g = gemm_base(a->status);
+            g.mode = 2; g.rows_static = T; g.N = I; g.K = H;
+            g.A = d_y_local; g.lda = H; g.B = a->w_shared_down; g.ldb = I; g.D = a->d_hidden_shared; g.ldd = I;
+            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+            MOKB_TRY(mokb_swiglu_bwd(a->gate_shared, a->up_shared, a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, nullptr,
+                                     nullptr, T, I, lim, limv, stream));
+            g = gemm_base(a->status);
+            g.mode = 2; g.rows_static = T; g.N = H; g.K = I;
+            g.A = a->d_gate_shared; g.B = a->w_shared_gate; g.A2 = a->d_up_shared; g.B2 = a->w_shared_up; g.lda = I; g.ldb = H;
+            g.D = a->d_x_shared; g.ldd = H;
+            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+            MOKB_TRY(wgrad(d_y_local, H, a->hidden_shared, I, a->d_w_shared_down, 1, T, s.shared_offsets, 0));
+            MOKB_TRY(wgrad(a->d_gate_shared, I, x_local, H, a->d_w_shared_gate, 1, T, s.shared_offsets, 0));
+            MOKB_TRY(wgrad(a->d_up_shared, I, x_local, H, a->d_w_shared_up, 1, T, s.shared_offsets, 0));
+        }
 
-}  // namespace
-}  // namespace mokb
-
-extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_args* a, void* stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    MOKB_TRY(check_common(a, "fwd_mxfp8"));
-    MOKB_REQUIRE(a->intermediate % 128 == 0 && a->hidden % 128 == 0, "fwd_mxfp8: hidden and intermediate must be multiples of 128");
-    MOKB_REQUIRE(a->x_ptrs_host && a->w_shared_gate && a->w_shared_up && a->w_routed_gate && a->w_routed_gate_sc && a->w_routed_up &&
-                 a->w_routed_up_sc, "fwd_mxfp8: null input");
-    MOKB_REQUIRE(a->x_fp8_t && a->x_sc_t && a->gate_shared && a->up_shared && a->hidden_shared && a->gate_fp8 && a->gate_sc &&
-                 a->up_fp8 && a->up_sc && a->hidden_fp8_t && a->hidden_sc_t, "fwd_mxfp8: null output");
-    MOKB_REQUIRE(a->x_routed && a->x_fp8 && a->x_sc && a->gate_bf16 && a->up_bf16 && a->hidden_fp8 && a->hidden_sc, "fwd_mxfp8: null work buffer");
-    const bool with_down = !a->skip_down_combine;
-    if (with_down)
-        MOKB_REQUIRE(a->combine_ptrs_host && a->w_shared_down && a->w_routed_down && a->w_routed_down_sc && a->y_shared && a->y_routed,
-                     "fwd_mxfp8: null down/combine pointer");
-    const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
-    const Scratch s = carve(a->scratch, E_l, MB);
-    const bool overlap = overlap_enabled();
-    Async* as = nullptr;
-    if (overlap) MOKB_TRY(get_async(&as));
-    cudaStream_t s_in = overlap ? as->s1 : stream;
-    const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
-
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, s, a->status, stream));
-    if (overlap) {
-        MOKB_CUDA(cudaEventRecord(as->fork, stream));
-        MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
-    }
-    // dispatch + quantise (row-wise for the GEMM, token-wise for the weight gradients) on the side stream
-    MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB, a->topk, H,
-                                a->x_routed, nullptr, nullptr, comm_blocks, s_in));
-    MOKB_TRY(quantize_impl(a->x_routed, 1, MB, H, s.n_rows, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, s_in));
-    if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
-    const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
-
-    // shared expert (BF16)
-    mokb_gemm_args g = gemm_base(a->status);
-    g.mode = 1; g.rows_static = T; g.N = I; g.K = H;
-    g.A = x_local; g.lda = H; g.B = a->w_shared_gate; g.B2 = a->w_shared_up; g.ldb = H;
-    g.D = a->gate_shared; g.D2 = a->up_shared; g.D3 = a->hidden_shared; g.ldd = I;
-    g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    if (with_down) {
+        // ---- routed experts of this macrobatch
+        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
+        mokb_gemm_args g;
+        if (m > 0) {       // replay gate/up + SwiGLU into the context buffers
+            g = gemm_base(a->status);
+            g.mode = 1; g.rows_static = hi; g.row_begin = lo; g.row_end = hi;
+            g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
+            g.A = x_routed; g.lda = H; g.B = a->w_routed_gate; g.B2 = a->w_routed_up; g.ldb = H;
+            g.D = gate_r; g.D2 = up_r; g.D3 = hidden_r; g.ldd = I;
+            g.has_swiglu_limit = lim; g.swiglu_limit = limv;
+            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+        }
         g = gemm_base(a->status);
-        g.mode = 0; g.rows_static = T; g.N = H; g.K = I;
-        g.A = a->hidden_shared; g.lda = I; g.B = a->w_shared_down; g.ldb = I; g.D = a->y_shared; g.ldd = H;
+        g.mode = 2; g.rows_static = hi; g.row_begin = lo; g.row_end = hi;
+        g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
+        g.A = d_y_r; g.lda = H; g.B = a->w_routed_down; g.ldb = I; g.D = d_hidden_r; g.ldd = I;
         MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+        MOKB_TRY(mokb_swiglu_bwd(a->gate_routed, a->up_routed, a->d_hidden_routed, a->d_gate_routed, a->d_up_routed, s.w_row, s.d_w_row,
+                                 s.mb_rows + m, MB, I, lim, limv, stream));
+        g = gemm_base(a->status);
+        g.mode = 2; g.rows_static = hi; g.row_begin = lo; g.row_end = hi;
+        g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = H; g.K = I;
+        g.A = d_gate_r; g.B = a->w_routed_gate; g.A2 = d_up_r; g.B2 = a->w_routed_up; g.lda = I; g.ldb = H;
+        g.D = d_x_r; g.ldd = H;
+        MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+        // reverse dispatch: push d_x rows and the per-route router-weight gradient home (overlaps the weight gradients)
+        if (overlap) {
+            MOKB_CUDA(cudaEventRecord(as->ev_out[0], stream));
+            MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[0], 0));
+        }
+        MOKB_TRY(combine_rows_impl(d_x_r, a->d_x_routed_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi,
+                                   H, d_w_row, a->d_router_weight_ptrs_host, comm_blocks, s_out));
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->join2, s_out));
+        const int32_t* offs = s.mb_offsets + static_cast<size_t>(m) * (E_l + 1);
+        MOKB_TRY(wgrad(d_y_r, H, hidden_r, I, a->d_w_routed_down, E_l, hi, offs, m > 0));
+        MOKB_TRY(wgrad(d_gate_r, I, x_routed, H, a->d_w_routed_gate, E_l, hi, offs, m > 0));
+        MOKB_TRY(wgrad(d_up_r, I, x_routed, H, a->d_w_routed_up, E_l, hi, offs, m > 0));
+        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
     }
-
-    // routed experts (MXFP8)
-    if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
-    mokb_gemm_fp8_args f = fp8_base(a->status);
-    f.mode = 1; f.rows_static = MB; f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
-    f.A = a->x_fp8; f.A_sc = a->x_sc; f.B = a->w_routed_gate; f.B_sc = a->w_routed_gate_sc; f.B2 = a->w_routed_up; f.B2_sc = a->w_routed_up_sc;
-    f.D = a->gate_bf16; f.D2 = a->up_bf16; f.ldd = I;
-    MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-    MOKB_TRY(swiglu_fwd_quant_impl(a->gate_bf16, a->up_bf16, MB, I, s.n_rows, a->has_swiglu_limit, a->swiglu_limit, a->gate_fp8, a->gate_sc,
-                                   a->up_fp8, a->up_sc, a->hidden_fp8, a->hidden_sc, a->hidden_fp8_t, a->hidden_sc_t, stream));
-    if (with_down) {
-        f = fp8_base(a->status);
-        f.mode = 0; f.rows_static = MB; f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = H; f.K = I;
-        f.A = a->hidden_fp8; f.A_sc = a->hidden_sc; f.B = a->w_routed_down; f.B_sc = a->w_routed_down_sc; f.D = a->y_routed; f.ldd = H;
-        MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-        MOKB_TRY(combine_rows_impl(a->y_routed, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB, H,
-                                   nullptr, nullptr, 0, stream));
-    }
-    return MOKB_OK;
-}
-
-extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_args* a, void* stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    MOKB_TRY(check_common(a, "bwd_mxfp8"));
-    MOKB_REQUIRE(a->d_y_ptrs_host && a->d_x_routed_ptrs_host && a->router_weight_ptrs_host && a->d_router_weight_ptrs_host && a->x_ptrs_host,
-                 "bwd_mxfp8: null pointer list");
-    MOKB_REQUIRE(a->w_shared_gate && a->w_shared_up && a->w_shared_down && a->w_routed_gate_t && a->w_routed_gate_t_sc && a->w_routed_up_t &&
-                 a->w_routed_up_t_sc && a->w_routed_down_t && a->w_routed_down_t_sc, "bwd_mxfp8: null weight");
-    MOKB_REQUIRE(a->x_fp8_t && a->x_sc_t && a->gate_shared && a->gate_fp8 && a->gate_sc && a->up_shared && a->up_fp8 && a->up_sc &&
-                 a->hidden_shared && a->hidden_fp8_t && a->hidden_sc_t, "bwd_mxfp8: null forward context");
-    MOKB_REQUIRE(a->d_x_shared && a->d_x_routed && a->d_gate_shared && a->d_gate_fp8 && a->d_gate_sc && a->d_up_shared && a->d_up_fp8 &&
-                 a->d_up_sc && a->d_hidden_shared && a->d_hidden_routed && a->d_y_fp8 && a->d_y_sc && a->d_w_shared_gate &&
-                 a->d_w_routed_gate && a->d_w_shared_up && a->d_w_routed_up && a->d_w_shared_down && a->d_w_routed_down, "bwd_mxfp8: null output");
-    MOKB_REQUIRE(a->d_y_routed && a->d_y_fp8_t && a->d_y_sc_t && a->d_gate_fp8_t && a->d_gate_sc_t && a->d_up_fp8_t && a->d_up_sc_t && a->partials,
-                 "bwd_mxfp8: null work buffer");
-    const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
-    const Scratch s = carve(a->scratch, E_l, MB);
-    const bool overlap = overlap_enabled();
-    Async* as = nullptr;
-    if (overlap) MOKB_TRY(get_async(&as));
-    cudaStream_t s_in = overlap ? as->s1 : stream, s_out = overlap ? as->s2 : stream;
-    const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
-    const int lim = a->has_swiglu_limit;
-    const float limv = a->swiglu_limit;
-
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, s, a->status, stream));
-    if (overlap) {
-        MOKB_CUDA(cudaEventRecord(as->fork, stream));
-        MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
-    }
-    MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB, a->topk, H,
-                                a->d_y_routed, a->router_weight_ptrs_host, s.w_row, comm_blocks, s_in));
-    MOKB_TRY(quantize_impl(a->d_y_routed, 1, MB, H, s.n_rows, a->d_y_fp8, a->d_y_sc, a->d_y_fp8_t, a->d_y_sc_t, s_in));
-    if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
-    const void* d_y_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->d_y_ptrs_host[a->ep_rank]));
-    const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
-
-    // ---- shared expert (BF16)
-    mokb_gemm_args g = gemm_base(a->status);
-    g.mode = 2; g.rows_static = T; g.N = I; g.K = H;
-    g.A = d_y_local; g.lda = H; g.B = a->w_shared_down; g.ldb = I; g.D = a->d_hidden_shared; g.ldd = I;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    MOKB_TRY(mokb_swiglu_bwd(a->gate_shared, a->up_shared, a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, nullptr,
-                             nullptr, T, I, lim, limv, stream));
-    g = gemm_base(a->status);
-    g.mode = 2; g.rows_static = T; g.N = H; g.K = I;
-    g.A = a->d_gate_shared; g.B = a->w_shared_gate; g.A2 = a->d_up_shared; g.B2 = a->w_shared_up; g.lda = I; g.ldb = H;
-    g.D = a->d_x_shared; g.ldd = H;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    auto wgrad_bf16 = [&](const void* A, int M, const void* B, int N, void* D) -> int {
-        mokb_gemm_args w = gemm_base(a->status);
-        w.mode = 3; w.rows_static = T; w.G = 1; w.M = M; w.N = N; w.group_offsets = s.shared_offsets;
-        w.A = A; w.lda = M; w.B = B; w.ldb = N; w.D = D; w.ldd = N;
-        return mokb_grouped_gemm_bf16(&w, stream);
-    };
-    MOKB_TRY(wgrad_bf16(d_y_local, H, a->hidden_shared, I, a->d_w_shared_down));
-    MOKB_TRY(wgrad_bf16(a->d_gate_shared, I, x_local, H, a->d_w_shared_gate));
-    MOKB_TRY(wgrad_bf16(a->d_up_shared, I, x_local, H, a->d_w_shared_up));
-
-    // ---- routed experts (MXFP8)
-    if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
-    mokb_gemm_fp8_args f = fp8_base(a->status);
-    f.mode = 0; f.rows_static = MB; f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
-    f.A = a->d_y_fp8; f.A_sc = a->d_y_sc; f.B = a->w_routed_down_t; f.B_sc = a->w_routed_down_t_sc; f.D = a->d_hidden_routed; f.ldd = I;
-    MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-    MOKB_TRY(swiglu_bwd_quant_impl(a->gate_fp8, a->gate_sc, a->up_fp8, a->up_sc, a->d_hidden_routed, MB, I, s.n_rows, lim, limv, s.w_row,
-                                   a->d_gate_fp8, a->d_gate_sc, a->d_gate_fp8_t, a->d_gate_sc_t, a->d_up_fp8, a->d_up_sc, a->d_up_fp8_t,
-                                   a->d_up_sc_t, static_cast<float*>(a->partials), s.d_w_row, stream));
-    f = fp8_base(a->status);
-    f.mode = 0; f.rows_static = MB; f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = H; f.K = I;
-    f.A = a->d_gate_fp8; f.A_sc = a->d_gate_sc; f.B = a->w_routed_gate_t; f.B_sc = a->w_routed_gate_t_sc;
-    f.A2 = a->d_up_fp8; f.A2_sc = a->d_up_sc; f.B2 = a->w_routed_up_t; f.B2_sc = a->w_routed_up_t_sc; f.D = a->d_x_routed; f.ldd = H;
-    MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-    if (overlap) {
-        MOKB_CUDA(cudaEventRecord(as->ev_out[0], stream));
-        MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[0], 0));
-    }
-    MOKB_TRY(combine_rows_impl(a->d_x_routed, a->d_x_routed_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB,
-                               H, s.d_w_row, a->d_router_weight_ptrs_host, comm_blocks, s_out));
-    if (overlap) MOKB_CUDA(cudaEventRecord(as->join2, s_out));
-    auto wgrad_fp8 = [&](const void* A, const void* A_sc, int M, const void* B, const void* B_sc, int N, void* D) -> int {
-        mokb_gemm_fp8_args w = fp8_base(a->status);
-        w.mode = 2; w.rows_static = MB; w.G = E_l; w.M = M; w.N = N; w.group_offsets = s.expert_offsets;
-        w.A = A; w.A_sc = A_sc; w.B = B; w.B_sc = B_sc; w.D = D; w.ldd = N;
-        return mokb_grouped_gemm_mxfp8(&w, stream);
-    };
-    MOKB_TRY(wgrad_fp8(a->d_y_fp8_t, a->d_y_sc_t, H, a->hidden_fp8_t, a->hidden_sc_t, I, a->d_w_routed_down));
-    MOKB_TRY(wgrad_fp8(a->d_gate_fp8_t, a->d_gate_sc_t, I, a->x_fp8_t, a->x_sc_t, H, a->d_w_routed_gate));
-    MOKB_TRY(wgrad_fp8(a->d_up_fp8_t, a->d_up_sc_t, I, a->x_fp8_t, a->x_sc_t, H, a->d_w_routed_up));
-    if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
     return MOKB_OK;
 }

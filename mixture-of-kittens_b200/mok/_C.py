@@ -71,7 +71,7 @@ class GemmArgs(ctypes.Structure):
                 ("group_offsets", c_vp), ("G", c_int), ("M", c_int), ("N", c_int), ("K", c_int),
                 ("A", c_vp), ("B", c_vp), ("A2", c_vp), ("B2", c_vp), ("lda", c_int), ("ldb", c_int),
                 ("D", c_vp), ("D2", c_vp), ("D3", c_vp), ("ldd", c_int), ("has_swiglu_limit", c_int),
-                ("swiglu_limit", c_f32), ("status", c_vp)]
+                ("swiglu_limit", c_f32), ("accumulate", c_int), ("status", c_vp)]
 
 
 class GemmFp8Args(ctypes.Structure):
@@ -397,9 +397,10 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(d_y_buffer, d_y_buffer_ptrs, d_x_routed
 # ----------------------------------------------------------------------------
 def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None, group_offsets=None, G=1,
                  M=0, N=0, K=0, A2=None, B2=None, D2=None, D3=None, lda=None, ldb=None, ldd=None, swiglu_limit=None,
-                 row_begin=0, row_end=0):
+                 row_begin=0, row_end=0, accumulate=False):
     g = GemmArgs()
     g.mode = mode
+    g.accumulate = 1 if accumulate else 0
     g.row_begin, g.row_end = row_begin, row_end
     g.rows_static = A.shape[0] if rows is None else rows
     g.num_rows, g.group_of_block, g.group_offsets = _p(num_rows), _p(group_of_block), _p(group_offsets)

@@ -31,6 +31,9 @@ def run_layer(inp_cpu, E_l, *, limit=None, MB=None, mb=256, recompute=False, mul
     sched = F.build_schedule(ws, cfg, inp.top_experts, num_local_experts=E_l)
     out, ctx = F.forward(cfg, ws, sched, inp.x, inp.router_weights, inp.w_shared_gate, inp.w_shared_up,
                          inp.w_shared_down, inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down, limit)
+    # the backward replays later macrobatches into the context buffers (as the reference does): keep what the forward saved
+    import types
+    saved = types.SimpleNamespace(**{k: getattr(ctx, k).clone() for k in CTX_KEYS})
     ctx2 = None
     if recompute:
         ctx2 = F.recompute_forward_context(cfg, ws, sched, inp.x, inp.w_shared_gate, inp.w_shared_up,
@@ -39,7 +42,7 @@ def run_layer(inp_cpu, E_l, *, limit=None, MB=None, mb=256, recompute=False, mul
                        inp.w_shared_up, inp.w_shared_down, inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down, limit)
     torch.cuda.synchronize()
     assert _C.check_status() == 0
-    return sched, out, ctx, ctx2, grads, ws
+    return sched, out, saved, ctx2, grads, ws
 
 
 @pytest.mark.parametrize("shape", [
@@ -106,15 +109,39 @@ def test_recompute_is_bit_identical_and_runs_are_deterministic():
         assert torch.equal(a, b)
 
 
-def test_macrobatch_too_small_is_reported_not_fatal():
-    from mok import _C, functional as F
+@pytest.mark.parametrize("MB,mb", [(512, 256), (768, 256), (1024, 512)])
+def test_several_macrobatches_with_replay_match_the_single_macrobatch_result(MB, mb):
+    # capacity 2048 rows, ~1300-1500 of them used: 2-3 populated macrobatches and at least one empty one
+    ranks = O.make_inputs(R=1, T=512, H=256, I=256, E=4, K=2, seed=3, routing="gaussian")
+    ref = O.layer_forward_backward(ranks)[0]
+    N = int(ref["num_tokens"][0])
+    assert N > MB
+    sched, out, ctx, ctx2, grads, ws = run_layer(ranks[0], 4, MB=MB, mb=mb, recompute=True)
+    # the saved context is macrobatch 0, and recompute rebuilds exactly that
+    assert torch.equal(ctx.x_routed.cpu(), ref["x_routed"][:MB])
+    assert_close("gate_routed", ref["gate_routed"][:MB], ctx.gate_routed, (0.13, 4e-3))
+    for k in CTX_KEYS:
+        assert torch.equal(getattr(ctx, k), getattr(ctx2, k)), k
+    assert_close("combine_buffer", ref["combine_buffer"], ws.combine_buffer, (0.13, 4e-3))
+    assert_close("output", ref["output"], out, (0.13, 4e-3))
+    for k, got in zip(GRAD_KEYS, grads):
+        assert_close(k, ref[k], got, O.BF16_TOLERANCE)
+        assert O.error_stats(ref[k], got.cpu())[1] < 8e-3, k
+    # bit-reproducible across runs as well
+    _, out_b, _, _, grads_b, _ = run_layer(ranks[0], 4, MB=MB, mb=mb)
+    assert torch.equal(out, out_b) and all(torch.equal(a, b) for a, b in zip(grads, grads_b))
+
+
+def test_mxfp8_macrobatch_too_small_is_reported_not_fatal():
+    # the MXFP8 layer handles one macrobatch; more rows than that are reported through the status word
+    from mok import _C, functional as F, ops
     ranks = O.make_inputs(R=1, T=512, H=256, I=256, E=4, K=2, seed=3, routing="gaussian")
     group = init_single_rank_group()
     inp = to_dev(ranks[0])
     cfg = F.MoKConfig(minibatch_size=256, macrobatch_size=512)
     ws = F.get_workspace(cfg, group, device=torch.device("cuda", 0), num_local_tokens=512, hidden_size=256, topk=2)
     sched = F.build_schedule(ws, cfg, inp.top_experts, num_local_experts=4)
-    F.forward(cfg, ws, sched, inp.x, inp.router_weights, inp.w_shared_gate, inp.w_shared_up, inp.w_shared_down,
-              inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down)
+    q = [ops.mxfp8_quantize(w, True, False)[:2] for w in (inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down)]
+    F.forward(cfg, ws, sched, inp.x, inp.router_weights, inp.w_shared_gate, inp.w_shared_up, inp.w_shared_down, *q)
     torch.cuda.synchronize()
     assert _C.check_status() == _C.ST_MACROBATCH_OVERFLOW
