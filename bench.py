@@ -173,6 +173,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--minibatch", type=int, default=0, help="override the workload's minibatch_size (overlap window)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-mxfp8", action="store_true", help="skip the MXFP8 leg (reported under the key \"mxfp8\")")
     ap.add_argument("--kernel-only", action="store_true", help="time only the dominant GEMM (profiler captures)")
@@ -198,6 +199,8 @@ def main():
     group = dist.group.WORLD
 
     T, H, I, E, K, mb, mult, routing = WORKLOADS[args.workload]
+    if args.minibatch:
+        mb = args.minibatch
     assert E % world == 0
     E_l = E // world
     MB = int(math.ceil((T * K + E_l * 256) / mb) * mb)
@@ -321,6 +324,26 @@ def main():
                 "peak_source": f"{peak_kind} cuBLAS bf16 burst", "traffic": traffic,
                 "launch_ms": kern["ms"], "flops_per_launch": kern["flops_per_launch"]}
 
+    # ---- the communication phases alone: dispatch (row pull) and combine (row push) over all scheduled rows,
+    # every rank at once, CUDA events, max over ranks.  Bytes over NVLink = rows whose home is another rank.
+    comm = None
+    if world > 1:
+        n_rows = int(sched.num_tokens.item())
+        remote = int(((sched.peer_rank >= 0) & (sched.peer_rank != rank)).sum().item())
+        buf = torch.empty(MB, H, dtype=torch.bfloat16, device=device)
+        comm = {"remote_rows": remote, "rows": n_rows, "nvlink_peak_gbs_per_direction": 900.0, "measured_peer_copy_gbs": 770.0}
+        for name, fn in (
+            ("dispatch", lambda: _C.dispatch_rows(ws.x_buffer_ptrs, sched.peer_rank, sched.peer_token_idx, sched.num_tokens,
+                                                  MB, K, H, buf)),
+            ("combine", lambda: _C.combine_rows(buf, ws.combine_buffer_ptrs, sched.peer_rank, sched.peer_token_idx,
+                                                sched.num_tokens, MB, H)),
+        ):
+            fn()
+            ms = timed(fn, 5) / 5
+            comm[name] = {"ms": ms, "nvlink_gbs": remote * H * 2 / (ms / 1000.0) / 1e9,
+                          "frac_of_900": remote * H * 2 / (ms / 1000.0) / 1e9 / 900.0}
+        del buf
+
     # ---- the same step with the routed experts in MXFP8 (weights pre-quantised outside the step, as the reference does)
     mx = None
     if not args.no_mxfp8:
@@ -372,6 +395,8 @@ def main():
         }
         if mx is not None:
             line["mxfp8"] = mx
+        if comm is not None:
+            line["comm"] = comm
         if world == 1 and not args.no_cpu_baseline:
             Ts, Es, dt = cpu_oracle_sample(H, I, K)
             line["cpu_baseline"] = {
