@@ -77,7 +77,40 @@ class ClockSampler:
         self.proc = None
         self.lines: list[str] = []
 
+    def _nvml_loop(self):
+        # NVML from a thread: no process start-up, so even a 200 ms timed region gets samples
+        import pynvml
+        h = self._nvml_handle
+        bits = {"hw_slowdown": pynvml.nvmlClocksEventReasonHwSlowdown,
+                "hw_thermal_slowdown": pynvml.nvmlClocksEventReasonHwThermalSlowdown,
+                "sw_thermal_slowdown": pynvml.nvmlClocksEventReasonSwThermalSlowdown,
+                "sw_power_cap": pynvml.nvmlClocksEventReasonSwPowerCap}
+        while not self._stop.is_set():
+            try:
+                sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+                pw = pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0
+                r = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                flags = ["Active" if r & bits[n] else "Not Active" for n in
+                         ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")]
+                self.lines.append(", ".join([str(sm), str(mx), f"{pw:.1f}", *flags]))
+            except Exception:
+                break
+            self._stop.wait(0.02)
+
     def __enter__(self):
+        self._stop = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[self.index]) if visible and visible.split(",")[self.index].isdigit() else self.index
+            self._nvml_handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            pass
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
@@ -93,6 +126,7 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def __exit__(self, *exc):
+        self._stop.set()
         if self.proc is not None:
             self.proc.terminate()
             try:

@@ -14,7 +14,9 @@ using namespace mokb;
 //             -> de-quantise saved gate/up, SwiGLU backward, router-gradient partials, quantise d_gate, d_up
 //             both ways -> d_x = d_gate_q * WgT_q^T + d_up_q * WuT_q^T -> combine;
 //             weight gradients contract the token-wise quantised tensors over each expert's rows.
-// Dispatch / combine overlap the shared expert's BF16 GEMMs and the weight gradients on the side streams.
+// The forward is cut into row windows (minibatch_size rows each): dispatch + quantise of window c+1 and the
+// combine of window c-1 run on the side streams while the GEMMs of window c run on the caller's stream.
+// In the backward, dispatch / combine overlap the shared expert's BF16 GEMMs and the weight gradients.
 namespace mokb {
 namespace {
 
@@ -47,19 +49,26 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
-    cudaStream_t s_in = overlap ? as->s1 : stream;
+    cudaStream_t s_in = overlap ? as->s1 : stream, s_out = overlap ? as->s2 : stream;
     const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
+    // overlap windows: rows [r0, r1) flow dispatch+quantise (side stream 1) -> GEMMs (caller's stream) -> combine (side stream 2)
+    const int chunk = chunk_rows_for(MB, a->minibatch_size);
+    const int nchunks = (MB + chunk - 1) / chunk;
 
     MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, true, s, a->status, stream));
     if (overlap) {
         MOKB_CUDA(cudaEventRecord(as->fork, stream));
         MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
+        if (with_down) MOKB_CUDA(cudaStreamWaitEvent(s_out, as->fork, 0));
     }
-    // dispatch + quantise (row-wise for the GEMM, token-wise for the weight gradients) on the side stream
-    MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB, a->topk, H,
-                                a->x_routed, nullptr, nullptr, comm_blocks, s_in));
-    MOKB_TRY(quantize_impl(a->x_routed, 1, MB, H, s.n_rows, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, s_in));
-    if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
+    // dispatch + quantise (row-wise for the GEMM, token-wise for the weight gradients), window by window
+    for (int c = 0; c < nchunks; ++c) {
+        const int r0 = c * chunk, r1 = r0 + chunk < MB ? r0 + chunk : MB;
+        MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, r0, r1, a->topk, H,
+                                    a->x_routed, nullptr, nullptr, comm_blocks, s_in));
+        MOKB_TRY(quantize_impl(a->x_routed, 1, MB, H, s.n_rows, r0, r1, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, s_in));
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+    }
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
 
     // shared expert (BF16)
@@ -76,22 +85,34 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
         MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
     }
 
-    // routed experts (MXFP8)
-    if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
-    mokb_gemm_fp8_args f = fp8_base(a->status);
-    f.mode = 1; f.rows_static = MB; f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
-    f.A = a->x_fp8; f.A_sc = a->x_sc; f.B = a->w_routed_gate; f.B_sc = a->w_routed_gate_sc; f.B2 = a->w_routed_up; f.B2_sc = a->w_routed_up_sc;
-    f.D = a->gate_bf16; f.D2 = a->up_bf16; f.ldd = I;
-    MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-    MOKB_TRY(swiglu_fwd_quant_impl(a->gate_bf16, a->up_bf16, MB, I, s.n_rows, a->has_swiglu_limit, a->swiglu_limit, a->gate_fp8, a->gate_sc,
-                                   a->up_fp8, a->up_sc, a->hidden_fp8, a->hidden_sc, a->hidden_fp8_t, a->hidden_sc_t, stream));
-    if (with_down) {
+    // routed experts (MXFP8), window by window behind the dispatch
+    for (int c = 0; c < nchunks; ++c) {
+        const int r0 = c * chunk, r1 = r0 + chunk < MB ? r0 + chunk : MB;
+        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
+        mokb_gemm_fp8_args f = fp8_base(a->status);
+        f.mode = 1; f.rows_static = MB; f.row_begin = r0; f.row_end = r1;
+        f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
+        f.A = a->x_fp8; f.A_sc = a->x_sc; f.B = a->w_routed_gate; f.B_sc = a->w_routed_gate_sc; f.B2 = a->w_routed_up; f.B2_sc = a->w_routed_up_sc;
+        f.D = a->gate_bf16; f.D2 = a->up_bf16; f.ldd = I;
+        MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
+        MOKB_TRY(swiglu_fwd_quant_impl(a->gate_bf16, a->up_bf16, MB, I, s.n_rows, r0, r1, a->has_swiglu_limit, a->swiglu_limit, a->gate_fp8,
+                                       a->gate_sc, a->up_fp8, a->up_sc, a->hidden_fp8, a->hidden_sc, a->hidden_fp8_t, a->hidden_sc_t, stream));
+        if (!with_down) continue;
         f = fp8_base(a->status);
-        f.mode = 0; f.rows_static = MB; f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = H; f.K = I;
+        f.mode = 0; f.rows_static = MB; f.row_begin = r0; f.row_end = r1;
+        f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = H; f.K = I;
         f.A = a->hidden_fp8; f.A_sc = a->hidden_sc; f.B = a->w_routed_down; f.B_sc = a->w_routed_down_sc; f.D = a->y_routed; f.ldd = H;
         MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-        MOKB_TRY(combine_rows_impl(a->y_routed, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB, H,
-                                   nullptr, nullptr, 0, stream));
+        if (overlap) {
+            MOKB_CUDA(cudaEventRecord(as->ev_out[c], stream));
+            MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[c], 0));
+        }
+        MOKB_TRY(combine_rows_impl(a->y_routed, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, r0, r1, H,
+                                   nullptr, nullptr, comm_blocks, s_out));
+    }
+    if (overlap && with_down) {
+        MOKB_CUDA(cudaEventRecord(as->join2, s_out));
+        MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
     }
     return MOKB_OK;
 }
@@ -127,7 +148,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
     }
     MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB, a->topk, H,
                                 a->d_y_routed, a->router_weight_ptrs_host, s.w_row, comm_blocks, s_in));
-    MOKB_TRY(quantize_impl(a->d_y_routed, 1, MB, H, s.n_rows, a->d_y_fp8, a->d_y_sc, a->d_y_fp8_t, a->d_y_sc_t, s_in));
+    MOKB_TRY(quantize_impl(a->d_y_routed, 1, MB, H, s.n_rows, 0, MB, a->d_y_fp8, a->d_y_sc, a->d_y_fp8_t, a->d_y_sc_t, s_in));
     if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
     const void* d_y_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->d_y_ptrs_host[a->ep_rank]));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
@@ -160,7 +181,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
     f.mode = 0; f.rows_static = MB; f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
     f.A = a->d_y_fp8; f.A_sc = a->d_y_sc; f.B = a->w_routed_down_t; f.B_sc = a->w_routed_down_t_sc; f.D = a->d_hidden_routed; f.ldd = I;
     MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-    MOKB_TRY(swiglu_bwd_quant_impl(a->gate_fp8, a->gate_sc, a->up_fp8, a->up_sc, a->d_hidden_routed, MB, I, s.n_rows, lim, limv, s.w_row,
+    MOKB_TRY(swiglu_bwd_quant_impl(a->gate_fp8, a->gate_sc, a->up_fp8, a->up_sc, a->d_hidden_routed, MB, I, s.n_rows, 0, MB, lim, limv, s.w_row,
                                    a->d_gate_fp8, a->d_gate_sc, a->d_gate_fp8_t, a->d_gate_sc_t, a->d_up_fp8, a->d_up_sc, a->d_up_fp8_t,
                                    a->d_up_sc_t, static_cast<float*>(a->partials), s.d_w_row, stream));
     f = fp8_base(a->status);

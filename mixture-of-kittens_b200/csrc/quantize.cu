@@ -99,15 +99,27 @@ __device__ __forceinline__ int live_rows(const int32_t* num_rows, int64_t cap) {
     return (n < 0 || n > cap) ? 0 : n;
 }
 
+// rows [begin, min(end, *num_rows)) of a tensor with `cap` rows; the grid's y index counts 128-row tiles from `begin`
+struct RowWindow {
+    const int32_t* num_rows;
+    int begin, end;
+};
+__device__ __forceinline__ bool tile_in_window(const RowWindow& w, int64_t cap, int64_t* r0) {
+    *r0 = static_cast<int64_t>(blockIdx.y) * TILE + w.begin;
+    const int live = min(live_rows(w.num_rows, cap), w.end);
+    return *r0 < live;
+}
+
 // grid (N/128, M/128, E), 256 threads.
 __global__ void __launch_bounds__(256) quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64_t N,
-                                                       const int32_t* __restrict__ num_rows,
+                                                       RowWindow win,
                                                        uint8_t* __restrict__ q, uint8_t* __restrict__ sc,
                                                        uint8_t* __restrict__ qt, uint8_t* __restrict__ sct) {
     __shared__ __nv_bfloat16 tile[TILE_ELEMS];
     const int64_t e = blockIdx.z;
-    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * TILE, c0 = static_cast<int64_t>(blockIdx.x) * TILE;
-    if (r0 >= live_rows(num_rows, M)) return;
+    const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
+    int64_t r0;
+    if (!tile_in_window(win, M, &r0)) return;
     load_tile_bf16(tile, x + (e * M + r0) * N + c0, N);
     __syncthreads();
     if (q) quantize_tile_rows(tile, q, sc, e * M, r0, c0, N);
@@ -123,13 +135,14 @@ struct Clamp {
 // grid (I/128, rows_cap/128), 256 threads, 3 staged tiles.
 __global__ void __launch_bounds__(256) swiglu_fwd_quant_kernel(
     const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up, int64_t rows_cap, int64_t I,
-    const int32_t* __restrict__ num_rows, Clamp c,
+    RowWindow win, Clamp c,
     uint8_t* gate_q, uint8_t* gate_sc, uint8_t* up_q, uint8_t* up_sc,
     uint8_t* hid_q, uint8_t* hid_sc, uint8_t* hid_qt, uint8_t* hid_sct) {
     extern __shared__ __nv_bfloat16 sm[];
     __nv_bfloat16 *tg = sm, *tu = sm + TILE_ELEMS, *th = sm + 2 * TILE_ELEMS;
-    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * TILE, c0 = static_cast<int64_t>(blockIdx.x) * TILE;
-    if (r0 >= live_rows(num_rows, rows_cap)) return;
+    const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
+    int64_t r0;
+    if (!tile_in_window(win, rows_cap, &r0)) return;
     load_tile_bf16(tg, gate + r0 * I + c0, I);
     load_tile_bf16(tu, up + r0 * I + c0, I);
     __syncthreads();
@@ -155,14 +168,15 @@ __global__ void __launch_bounds__(256) swiglu_fwd_quant_kernel(
 __global__ void __launch_bounds__(256) swiglu_bwd_quant_kernel(
     const uint8_t* __restrict__ gate_q, const uint8_t* __restrict__ gate_sc, const uint8_t* __restrict__ up_q,
     const uint8_t* __restrict__ up_sc, const __nv_bfloat16* __restrict__ d_hidden, int64_t rows_cap, int64_t I,
-    const int32_t* __restrict__ num_rows, Clamp c, const float* __restrict__ row_scale,
+    RowWindow win, Clamp c, const float* __restrict__ row_scale,
     uint8_t* dg_q, uint8_t* dg_sc, uint8_t* dg_qt, uint8_t* dg_sct,
     uint8_t* du_q, uint8_t* du_sc, uint8_t* du_qt, uint8_t* du_sct, float* __restrict__ partials) {
     extern __shared__ __nv_bfloat16 sm[];
     __nv_bfloat16 *tdh = sm, *tdg = sm + TILE_ELEMS, *tdu = sm + 2 * TILE_ELEMS;
     __shared__ float row_part[TILE][2];
-    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * TILE, c0 = static_cast<int64_t>(blockIdx.x) * TILE;
-    if (r0 >= live_rows(num_rows, rows_cap)) return;
+    const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
+    int64_t r0;
+    if (!tile_in_window(win, rows_cap, &r0)) return;
     load_tile_bf16(tdh, d_hidden + r0 * I + c0, I);
     __syncthreads();
     // two threads per row, 64 columns each (two scale blocks of 32)
@@ -208,10 +222,10 @@ __global__ void __launch_bounds__(256) swiglu_bwd_quant_kernel(
 }
 
 // row_grad[row] = sum over the column blocks of partials[row, :], in block order (fixed, reproducible)
-__global__ void row_sum_kernel(const float* __restrict__ partials, int nblk, const int32_t* __restrict__ num_rows,
-                               int64_t rows_cap, float* __restrict__ out) {
-    const int rows = live_rows(num_rows, rows_cap);
-    for (int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; row < rows;
+__global__ void row_sum_kernel(const float* __restrict__ partials, int nblk, RowWindow win, int64_t rows_cap,
+                               float* __restrict__ out) {
+    const int rows = min(live_rows(win.num_rows, rows_cap), win.end);
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x + win.begin; row < rows;
          row += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         float s = 0.0f;
         for (int b = 0; b < nblk; ++b) s += partials[row * nblk + b];
@@ -221,16 +235,20 @@ __global__ void row_sum_kernel(const float* __restrict__ partials, int nblk, con
 
 }  // namespace
 
-int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int32_t* num_rows,
+int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int32_t* num_rows, int row_begin, int row_end,
                   void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, cudaStream_t stream) {
+    if (row_end <= 0) row_end = static_cast<int>(M);
+    MOKB_REQUIRE(row_begin >= 0 && row_begin % 128 == 0 && row_end % 128 == 0 && row_begin <= row_end && row_end <= M,
+                 "mxfp8_quantize: bad row window");
+    if (row_begin == row_end) return MOKB_OK;
     MOKB_REQUIRE(x_bf16 != nullptr, "mxfp8_quantize: null input");
     MOKB_REQUIRE(E > 0 && M > 0 && N > 0 && M % 128 == 0 && N % 128 == 0, "mxfp8_quantize: M and N must be positive multiples of 128");
     MOKB_REQUIRE((x_fp8 == nullptr) == (x_sc == nullptr) && (x_fp8_t == nullptr) == (x_sc_t == nullptr),
                  "mxfp8_quantize: data and scale outputs go together");
     MOKB_REQUIRE(x_fp8 || x_fp8_t, "mxfp8_quantize: at least one quantised layout must be requested");
     MOKB_REQUIRE(E <= 65535 && M / 128 <= 65535, "mxfp8_quantize: tensor too large for one launch");
-    const dim3 grid(static_cast<unsigned>(N / 128), static_cast<unsigned>(M / 128), static_cast<unsigned>(E));
-    quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), M, N, num_rows,
+    const dim3 grid(static_cast<unsigned>(N / 128), static_cast<unsigned>((row_end - row_begin) / 128), static_cast<unsigned>(E));
+    quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), M, N, RowWindow{num_rows, row_begin, row_end},
                                               static_cast<uint8_t*>(x_fp8), static_cast<uint8_t*>(x_sc),
                                               static_cast<uint8_t*>(x_fp8_t), static_cast<uint8_t*>(x_sc_t));
     MOKB_CUDA(cudaGetLastError());
@@ -239,15 +257,20 @@ int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int
 }
 
 int swiglu_fwd_quant_impl(const void* gate, const void* up, int64_t rows_cap, int64_t I, const int32_t* num_rows,
-                          int has_limit, float limit, void* gate_q, void* gate_sc, void* up_q, void* up_sc,
+                          int row_begin, int row_end, int has_limit, float limit, void* gate_q, void* gate_sc, void* up_q, void* up_sc,
                           void* hid_q, void* hid_sc, void* hid_qt, void* hid_sct, cudaStream_t stream) {
     MOKB_REQUIRE(gate && up && gate_q && gate_sc && up_q && up_sc && hid_q && hid_sc && hid_qt && hid_sct, "swiglu_fwd_quant: null pointer");
     MOKB_REQUIRE(rows_cap > 0 && rows_cap % 128 == 0 && I > 0 && I % 128 == 0 && rows_cap / 128 <= 65535, "swiglu_fwd_quant: bad sizes");
     const size_t smem = 3 * TILE_ELEMS * sizeof(__nv_bfloat16);
     MOKB_CUDA(cudaFuncSetAttribute(swiglu_fwd_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const dim3 grid(static_cast<unsigned>(I / 128), static_cast<unsigned>(rows_cap / 128));
+    if (row_end <= 0) row_end = static_cast<int>(rows_cap);
+    MOKB_REQUIRE(row_begin >= 0 && row_begin % 128 == 0 && row_end % 128 == 0 && row_begin <= row_end && row_end <= rows_cap,
+                 "swiglu_fwd_quant: bad row window");
+    if (row_begin == row_end) return MOKB_OK;
+    const dim3 grid(static_cast<unsigned>(I / 128), static_cast<unsigned>((row_end - row_begin) / 128));
     swiglu_fwd_quant_kernel<<<grid, 256, smem, stream>>>(
-        static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), rows_cap, I, num_rows, Clamp{has_limit, limit},
+        static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), rows_cap, I, RowWindow{num_rows, row_begin, row_end},
+        Clamp{has_limit, limit},
         static_cast<uint8_t*>(gate_q), static_cast<uint8_t*>(gate_sc), static_cast<uint8_t*>(up_q), static_cast<uint8_t*>(up_sc),
         static_cast<uint8_t*>(hid_q), static_cast<uint8_t*>(hid_sc), static_cast<uint8_t*>(hid_qt), static_cast<uint8_t*>(hid_sct));
     MOKB_CUDA(cudaGetLastError());
@@ -256,7 +279,7 @@ int swiglu_fwd_quant_impl(const void* gate, const void* up, int64_t rows_cap, in
 }
 
 int swiglu_bwd_quant_impl(const void* gate_q, const void* gate_sc, const void* up_q, const void* up_sc, const void* d_hidden,
-                          int64_t rows_cap, int64_t I, const int32_t* num_rows, int has_limit, float limit,
+                          int64_t rows_cap, int64_t I, const int32_t* num_rows, int row_begin, int row_end, int has_limit, float limit,
                           const float* row_scale, void* dg_q, void* dg_sc, void* dg_qt, void* dg_sct,
                           void* du_q, void* du_sc, void* du_qt, void* du_sct, float* partials, float* row_grad,
                           cudaStream_t stream) {
@@ -266,16 +289,22 @@ int swiglu_bwd_quant_impl(const void* gate_q, const void* gate_sc, const void* u
     MOKB_REQUIRE(rows_cap > 0 && rows_cap % 128 == 0 && I > 0 && I % 128 == 0 && rows_cap / 128 <= 65535, "swiglu_bwd_quant: bad sizes");
     const size_t smem = 3 * TILE_ELEMS * sizeof(__nv_bfloat16);
     MOKB_CUDA(cudaFuncSetAttribute(swiglu_bwd_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const dim3 grid(static_cast<unsigned>(I / 128), static_cast<unsigned>(rows_cap / 128));
+    if (row_end <= 0) row_end = static_cast<int>(rows_cap);
+    MOKB_REQUIRE(row_begin >= 0 && row_begin % 128 == 0 && row_end % 128 == 0 && row_begin <= row_end && row_end <= rows_cap,
+                 "swiglu_bwd_quant: bad row window");
+    if (row_begin == row_end) return MOKB_OK;
+    const RowWindow win{num_rows, row_begin, row_end};
+    const dim3 grid(static_cast<unsigned>(I / 128), static_cast<unsigned>((row_end - row_begin) / 128));
     swiglu_bwd_quant_kernel<<<grid, 256, smem, stream>>>(
         static_cast<const uint8_t*>(gate_q), static_cast<const uint8_t*>(gate_sc), static_cast<const uint8_t*>(up_q),
-        static_cast<const uint8_t*>(up_sc), static_cast<const __nv_bfloat16*>(d_hidden), rows_cap, I, num_rows, Clamp{has_limit, limit},
+        static_cast<const uint8_t*>(up_sc), static_cast<const __nv_bfloat16*>(d_hidden), rows_cap, I, win, Clamp{has_limit, limit},
         row_scale, static_cast<uint8_t*>(dg_q), static_cast<uint8_t*>(dg_sc), static_cast<uint8_t*>(dg_qt), static_cast<uint8_t*>(dg_sct),
         static_cast<uint8_t*>(du_q), static_cast<uint8_t*>(du_sc), static_cast<uint8_t*>(du_qt), static_cast<uint8_t*>(du_sct), partials);
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     if (row_grad) {
-        row_sum_kernel<<<sm_count() * 4, 256, 0, stream>>>(partials, static_cast<int>(I / 128), num_rows, rows_cap, row_grad);
+        const int blocks = min(sm_count() * 4, (row_end - row_begin + 255) / 256);
+        row_sum_kernel<<<blocks, 256, 0, stream>>>(partials, static_cast<int>(I / 128), win, rows_cap, row_grad);
         MOKB_CUDA(cudaGetLastError());
         note_launch();
     }
@@ -288,5 +317,5 @@ using namespace mokb;
 
 extern "C" int mokb_mxfp8_quantize(const void* x_bf16, int64_t E, int64_t M, int64_t N,
                                    void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, void* stream) {
-    return quantize_impl(x_bf16, E, M, N, nullptr, x_fp8, x_sc, x_fp8_t, x_sc_t, static_cast<cudaStream_t>(stream));
+    return quantize_impl(x_bf16, E, M, N, nullptr, 0, 0, x_fp8, x_sc, x_fp8_t, x_sc_t, static_cast<cudaStream_t>(stream));
 }

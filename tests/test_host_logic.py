@@ -126,3 +126,47 @@ def test_oracle_multi_rank_layer_is_consistent_with_single_rank_math():
         one = O.RankInputs(**{**ranks[r].__dict__, "w_routed_gate": allW[0], "w_routed_up": allW[1], "w_routed_down": allW[2]})
         single = O.layer_forward_backward([one], with_backward=False)[0]
         assert torch.equal(single["output"], outs[r]["output"])
+
+
+def test_whole_layer_traces_under_fake_tensors():
+    """Every operator of forward + backward (BF16 and MXFP8) has a meta kernel with the reference's output
+    shapes, so the layer can be traced without a device (what torch.compile(fullgraph=True) needs)."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from mok import ops  # noqa: F401
+    T, H, I, E_l, K, MB, C = 512, 256, 384, 4, 2, 1024, 2048
+    with FakeTensorMode():
+        dev = "cuda"
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        x = torch.empty(T, H, **bf)
+        comb = torch.empty(T * K, H, **bf)
+        wsg, wsu, wsd = torch.empty(I, H, **bf), torch.empty(I, H, **bf), torch.empty(H, I, **bf)
+        wrg, wru, wrd = torch.empty(E_l, I, H, **bf), torch.empty(E_l, I, H, **bf), torch.empty(E_l, H, I, **bf)
+        sched = (torch.empty(C, **i32), torch.empty(C, **i32), torch.empty(1, **i32), torch.empty(E_l, **i32))
+        f = torch.ops.mok.dispatch_mlp_swiglu_combine_fwd_bf16(x, [16], comb, [16], wsg, wrg, wsu, wru, wsd, wrd, *sched,
+                                                              K, None, 40, MB, 256)
+        assert [tuple(t.shape) for t in f] == [(MB, H), (T, I), (MB, I), (T, I), (MB, I), (T, I), (MB, I), (T, H), (MB, H)]
+        rw = torch.empty(T, K, device=dev)
+        b = torch.ops.mok.dispatch_mlp_swiglu_combine_bwd_bf16(x, [16], comb, [16], rw, [16], rw, [16], wsg, wrg, wsu, wru,
+                                                              wsd, wrd, f[0], f[1], f[2], f[3], f[4], f[5], f[6], x, [16],
+                                                              *sched, K, None, 28, MB, 256)
+        assert len(b) == 15 and tuple(b[10].shape) == (E_l, I, H) and tuple(b[14].shape) == (E_l, H, I)
+        assert tuple(torch.ops.mok.fwd_epilogue(f[7], comb, rw).shape) == (T, H)
+        assert tuple(torch.ops.mok.bwd_epilogue(b[0], comb).shape) == (T, H)
+        # MXFP8
+        q = lambda t: torch.ops.mok.mxfp8_quantize(t, True, True)
+        gq, uq, dq = q(wrg), q(wru), q(wrd)
+        assert tuple(gq[2].shape) == (E_l, H, I) and tuple(gq[3].shape) == (E_l * H // 128, I // 128, 32, 16)
+        fm = torch.ops.mok.dispatch_mlp_swiglu_combine_fwd_mxfp8(x, [16], comb, [16], wsg, gq[0], gq[1], wsu, uq[0], uq[1],
+                                                                wsd, dq[0], dq[1], *sched, K, None, 40, MB, 256)
+        assert len(fm) == 13 and tuple(fm[0].shape) == (H, MB) and fm[0].dtype == torch.float8_e4m3fn
+        assert tuple(fm[10].shape) == (I // 128, MB // 128, 32, 16) and tuple(fm[12].shape) == (MB, H)
+        rm = torch.ops.mok.recompute_forward_context_mxfp8(x, [16], wsg, gq[0], gq[1], wsu, uq[0], uq[1], *sched, K, None,
+                                                          40, MB, 256)
+        assert len(rm) == 11
+        bm = torch.ops.mok.dispatch_mlp_swiglu_combine_bwd_mxfp8(
+            x, [16], comb, [16], rw, [16], rw, [16], wsg, gq[2], gq[3], wsu, uq[2], uq[3], wsd, dq[2], dq[3],
+            fm[0], fm[1], fm[2], fm[3], fm[4], fm[5], fm[6], fm[7], fm[8], fm[9], fm[10], x, [16],
+            gq[0], gq[1], uq[0], uq[1], *sched, K, None, 28, MB, 256)
+        assert len(bm) == 18 and tuple(bm[10].shape) == (MB, H) and bm[10].dtype == torch.float8_e4m3fn
+        assert tuple(bm[13].shape) == (E_l, I, H)
