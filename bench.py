@@ -192,6 +192,106 @@ def run_reference_arm(args, rank, world):
     }), flush=True)
 
 
+class _AllToAllRows(torch.autograd.Function):
+    """`dist.all_to_all_single` over dim 0 with the reverse exchange as its gradient."""
+
+    @staticmethod
+    def forward(ctx, inp, out_splits, in_splits, group):
+        ctx.args = (out_splits, in_splits, group)
+        out = inp.new_empty((sum(out_splits),) + tuple(inp.shape[1:]))
+        dist.all_to_all_single(out, inp.contiguous(), out_splits, in_splits, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        out_splits, in_splits, group = ctx.args
+        gin = grad.new_empty((sum(in_splits),) + tuple(grad.shape[1:]))
+        dist.all_to_all_single(gin, grad.contiguous(), in_splits, out_splits, group=group)
+        return gin, None, None, None
+
+
+def torch_all_to_all_layer(group, x, top_experts, router_weights, wsg, wsu, wsd, wrg, wru, wrd):
+    """The same layer written with stock PyTorch ops and NCCL (or gloo) collectives: count routes per expert,
+    exchange the counts, sort the routes by expert, `all_to_all_single` the token rows to the experts' ranks,
+    `torch._grouped_mm` per local expert, send the rows back, weighted sum at home.  This is the "torch all-to-all"
+    baseline the reference compares itself with (its benchmarks/bench_nccl_torch.py:36-229), restated without TorchAO;
+    autograd provides the backward pass.  Split sizes are read on the host, as that baseline does."""
+    import torch.nn.functional as Fn
+    R = dist.get_world_size(group)
+    T, H = x.shape
+    K = top_experts.shape[1]
+    E_l = wrg.shape[0]
+    E = E_l * R
+    flat = top_experts.reshape(-1)
+    order = torch.argsort(flat, stable=True)                   # routes by expert, hence by destination rank
+    counts = torch.bincount(flat, minlength=E)
+    recv_counts = torch.empty_like(counts)
+    dist.all_to_all_single(recv_counts, counts, group=group)   # [R, E_l]: rows from rank r for local expert e
+    recv_mat = recv_counts.view(R, E_l)
+    send_splits = counts.view(R, E_l).sum(1).tolist()
+    recv_splits = recv_mat.sum(1).tolist()
+    rows = _AllToAllRows.apply(x[order // K], recv_splits, send_splits, group)
+    # received rows are grouped by (source rank, expert): regroup by expert
+    expert_of_row = torch.repeat_interleave(torch.arange(E_l, device=x.device).repeat(R), recv_mat.reshape(-1))
+    by_expert = torch.argsort(expert_of_row, stable=True)
+    xe = rows[by_expert]
+    offs = recv_mat.sum(0).cumsum(0).to(torch.int32)
+    gate = torch._grouped_mm(xe, wrg.transpose(1, 2), offs=offs)
+    up = torch._grouped_mm(xe, wru.transpose(1, 2), offs=offs)
+    y = torch._grouped_mm(Fn.silu(gate) * up, wrd.transpose(1, 2), offs=offs)
+    back = _AllToAllRows.apply(y[torch.argsort(by_expert)], send_splits, recv_splits, group)
+    routed = back[torch.argsort(order)].view(T, K, H)
+    out = torch.bmm(router_weights.to(routed.dtype).unsqueeze(1), routed).squeeze(1)
+    shared = (Fn.silu(x @ wsg.t()) * (x @ wsu.t())) @ wsd.t()
+    return out + shared
+
+
+def time_torch_all_to_all(group, timed, steps, warmup, x, te, rw, gy, weights):
+    """fwd + bwd of `torch_all_to_all_layer` (gradients of x, the router weights and all six weight tensors)."""
+    leaves = [x.detach().clone().requires_grad_(True), rw.detach().clone().requires_grad_(True)]
+    leaves += [w_.detach().requires_grad_(True) for w_ in weights]
+
+    def step():
+        out = torch_all_to_all_layer(group, leaves[0], te, leaves[1], *leaves[2:])
+        return torch.autograd.grad(out, leaves, gy)
+    for _ in range(warmup):
+        step()
+    return timed(step, steps) / steps
+
+
+def cublaslt_mxfp8_tflops(device, seconds=1.0):
+    """Library reference point for the MXFP8 numbers: an 8192^3 block-scaled E4M3 GEMM (E8M0 scale per 32 along K)
+    through torch._scaled_mm (cuBLASLt), as a burst of 20 calls and as a loop of about `seconds`.
+    Returns (burst TFLOP/s, sustained TFLOP/s) or a string saying why it could not run."""
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+        sa = torch.full((n, n // 32), 127, dtype=torch.uint8, device=device).view(torch.float8_e8m0fnu)
+        sb = torch.full((n, n // 32), 127, dtype=torch.uint8, device=device).view(torch.float8_e8m0fnu)
+
+        def mm():
+            return torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            mm()
+        torch.cuda.synchronize()
+        flops = 2.0 * n * n * n
+
+        def run(iters):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(iters):
+                mm()
+            end.record()
+            torch.cuda.synchronize()
+            return flops * iters / (start.elapsed_time(end) / 1000.0) / 1e12
+        burst = run(20)
+        sustained = run(max(20, int(seconds * burst * 1e12 / flops)))
+        return burst, sustained
+    except Exception as e:
+        return f"{type(e).__name__}: {str(e)[:160]}"
+
+
 def workload_config(name, n):
     T, H, I, E, K, mb, mult, routing = WORKLOADS[name]
     return {"workload": f"{name}: MoE layer fwd+bwd, {T} tokens/rank, hidden {H}, {E} routed experts ({E // n}/rank) + 1 shared, "
@@ -210,6 +310,8 @@ def main():
     ap.add_argument("--minibatch", type=int, default=0, help="override the workload's minibatch_size (overlap window)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-mxfp8", action="store_true", help="skip the MXFP8 leg (reported under the key \"mxfp8\")")
+    ap.add_argument("--no-torch-baseline", action="store_true",
+                    help="skip the stock-PyTorch all-to-all + grouped_mm baseline (reported under \"torch_all_to_all\")")
     ap.add_argument("--kernel-only", action="store_true", help="time only the dominant GEMM (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if not args.kernel_only else args.warmup
@@ -292,6 +394,10 @@ def main():
         sched = F.build_schedule(ws, cfg, te_d, num_local_experts=E_l)
         torch.cuda.synchronize()
         kern = time_dominant_kernel(_C, sched, x_d, wrg, wru, T, H, I, K, E_l, MB, args.steps, args.warmup, device)
+        if not args.no_mxfp8:
+            from mok import ops
+            qg, qu = (ops.mxfp8_quantize(w_, True, False) for w_ in (wrg, wru))
+            kern["mxfp8"] = time_dominant_kernel_mxfp8(_C, ops, sched, x_d, qg, qu, T, H, I, E_l, MB, args.steps, args.warmup, device)
         if rank == 0:
             print(json.dumps({"kernel_only": True, **kern}), flush=True)
         dist.destroy_process_group()
@@ -408,7 +514,28 @@ def main():
               "tflops_per_gpu": layer_flops(T, K, H, I) / (mx_ms / 1000.0) / 1e12,
               "fwd_ms": statistics.median(mx_f), "bwd_ms": statistics.median(mx_b),
               "note": "routed experts in block-scaled E4M3 (tcgen05 mxf8f6f4), shared expert BF16; inputs resident in HBM"}
+        mx["dominant_kernel"] = time_dominant_kernel_mxfp8(_C, ops, sched, x_d, qg, qu, T, H, I, E_l, MB, 5, 2, device)
         del qg, qu, qd
+        if rank == 0:
+            lib = cublaslt_mxfp8_tflops(device)
+            if isinstance(lib, tuple):
+                mx["cublaslt_mxfp8_tflops"] = {"burst": lib[0], "sustained": lib[1],
+                                               "note": "8192^3 torch._scaled_mm with E8M0 block scales, measured in this run"}
+            else:
+                mx["cublaslt_mxfp8_tflops"] = {"unavailable": lib}
+
+    # ---- baseline: the same layer with stock PyTorch ops (all_to_all_single + grouped_mm + autograd), BF16
+    tb = None
+    if not args.no_torch_baseline:
+        try:
+            tb_steps = max(2, min(args.steps, 5))
+            tb_ms = time_torch_all_to_all(group, timed, tb_steps, 2, x_d, te_d, rw_d, gy_d, (wsg, wsu, wsd, wrg, wru, wrd))
+            tb = {"value": T * world / (tb_ms / 1000.0), "unit": "tokens/s", "ms_per_step": tb_ms, "steps": tb_steps,
+                  "tflops_per_gpu": layer_flops(T, K, H, I) / (tb_ms / 1000.0) / 1e12,
+                  "note": "all_to_all_single (NCCL) + torch._grouped_mm + autograd, BF16, same inputs and weights"}
+        except Exception as e:      # a library baseline must not take the benchmark down
+            tb = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+        torch.cuda.empty_cache()
 
     if rank == 0:
         tokens = T * world
@@ -431,6 +558,8 @@ def main():
             line["mxfp8"] = mx
         if comm is not None:
             line["comm"] = comm
+        if tb is not None:
+            line["torch_all_to_all"] = tb
         if world == 1 and not args.no_cpu_baseline:
             Ts, Es, dt = cpu_oracle_sample(H, I, K)
             line["cpu_baseline"] = {
@@ -469,6 +598,35 @@ def time_dominant_kernel(_C, sched, x, wrg, wru, T, H, I, K, E_l, MB, steps, war
     padded = int(sched.num_tokens.item())
     return {"ms": ms, "flops_per_launch": flops, "tflops": flops / (ms / 1000.0) / 1e12,
             "rows": real_rows, "padded_rows": padded}
+
+
+def time_dominant_kernel_mxfp8(_C, ops, sched, x, qg, qu, T, H, I, E_l, MB, steps, warmup, device):
+    """Times the routed MXFP8 gate|up grouped GEMM alone (block-scaled E4M3, both products in one launch)."""
+    tpe = sched.tokens_per_expert
+    gob = torch.repeat_interleave(torch.arange(E_l, device=device, dtype=torch.int32), (tpe // 128).to(torch.int64))
+    gob = torch.cat([gob, torch.full((MB // 128 - gob.numel(),), -1, dtype=torch.int32, device=device)])
+    x_routed = x.repeat((MB + T - 1) // T, 1)[:MB].contiguous()
+    xq, xs, _, _ = ops.mxfp8_quantize(x_routed, True, False)
+    del x_routed
+    gate, up = (torch.empty(MB, I, dtype=torch.bfloat16, device=device) for _ in range(2))
+
+    def launch():
+        _C.grouped_gemm_mxfp8(1, xq, xs, qg[0], qg[1], gate, rows=MB, num_rows=sched.num_tokens, group_of_block=gob,
+                              G=E_l, N=I, K=H, B2=qu[0], B2_sc=qu[1], D2=up)
+    for _ in range(warmup):
+        launch()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        launch()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    real_rows = int((sched.peer_rank >= 0).sum().item())
+    flops = 4.0 * real_rows * H * I
+    return {"kernel": "grouped_gemm_mxfp8_kernel<gate|up>", "ms": ms, "flops_per_launch": flops,
+            "tflops": flops / (ms / 1000.0) / 1e12}
 
 
 if __name__ == "__main__":
