@@ -65,6 +65,7 @@ struct KParams {
     int dual;                        // MODE_NN: second (A2, B2) pair accumulates into the same tile
     __nv_bfloat16 *D, *D2, *D3;
     int ldd;
+    int wide_stores;                 // output rows are 32-byte aligned: the epilogue stores 32 bytes per instruction
     int has_limit;
     float limit;
     int accumulate;                  // MODE_WGRAD: add to the stored bf16 result instead of overwriting it
@@ -127,15 +128,21 @@ __device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, ui
     asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// 32 fp32 accumulator columns of one row -> 32 bf16 (64 bytes) in global memory
-__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const uint32_t (&r)[32]) {
+// 32 fp32 accumulator columns of one row -> 32 bf16 (64 bytes) in global memory; `wide`: the row is 32-byte
+// aligned, so two 32-byte stores (one full sector each) replace four 16-byte ones
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const uint32_t (&r)[32], bool wide) {
+    uint32_t w[16];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        st_global_v4(dst + 8 * q,
-                     pack_bf16(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1])),
-                     pack_bf16(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3])),
-                     pack_bf16(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5])),
-                     pack_bf16(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7])));
+    for (int i = 0; i < 16; ++i) w[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+    if (wide) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 16 * q), "r"(w[8 * q]), "r"(w[8 * q + 1]),
+                         "r"(w[8 * q + 2]), "r"(w[8 * q + 3]), "r"(w[8 * q + 4]), "r"(w[8 * q + 5]), "r"(w[8 * q + 6]), "r"(w[8 * q + 7])
+                         : "memory");
+    } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st_global_v4(dst + 8 * q, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
     }
 }
 
@@ -344,9 +351,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         }
                         h[i] = __float_as_uint(gf / (1.0f + __expf(-gf)) * uf);
                     }
-                    store_row32(p.D + off + c * 32, g);
-                    store_row32(p.D2 + off + c * 32, u);
-                    store_row32(p.D3 + off + c * 32, h);
+                    store_row32(p.D + off + c * 32, g, p.wide_stores);
+                    store_row32(p.D2 + off + c * 32, u, p.wide_stores);
+                    store_row32(p.D3 + off + c * 32, h, p.wide_stores);
                 }
             } else {
                 const int tile_row = ti.m_blk * G::TILE_M + row_in_tile;
@@ -386,7 +393,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             }
                         }
                     }
-                    if (row_ok) store_row32(dst + c * 32, r);
+                    if (row_ok) store_row32(dst + c * 32, r, p.wide_stores);
                 }
             }
             tc_fence_before();
@@ -488,6 +495,8 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     p.D2 = static_cast<__nv_bfloat16*>(g->D2);
     p.D3 = static_cast<__nv_bfloat16*>(g->D3);
     p.ldd = g->ldd;
+    p.wide_stores = g->ldd % 16 == 0 && ((reinterpret_cast<uintptr_t>(g->D) | reinterpret_cast<uintptr_t>(g->D2) |
+                                          reinterpret_cast<uintptr_t>(g->D3)) & 31) == 0;
     p.accumulate = g->accumulate;
     p.has_limit = g->has_swiglu_limit;
     p.limit = g->swiglu_limit;

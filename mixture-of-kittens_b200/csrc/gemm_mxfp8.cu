@@ -37,7 +37,7 @@ constexpr int SF_TILE = 512;                       // one 32 x 16-byte scale til
 constexpr int SF_BYTES = 3 * SF_TILE;              // SFA | SFB(cols 0..127) | SFB(cols 128..255)
 constexpr int STAGES = 6;
 constexpr int STAGE_TX = DATA_BYTES + SF_BYTES;    // bytes one CTA lands per stage
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;                  // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
 constexpr int TMEM_COLS = 512;
 constexpr int SF_COL0 = 256;                       // scale columns start after the accumulator
 constexpr int SF_SET_COLS = 16;                    // SFA 4 + SFB 8, padded
@@ -57,6 +57,7 @@ struct FParams {
     int a_ktiles, b_ktiles;          // scale tiles per row block of A / B (= contraction extent / 128)
     __nv_bfloat16 *D, *D2;
     int ldd;
+    int wide_stores;                 // D (and D2) rows are 32-byte aligned: the epilogue stores 32 bytes per instruction
     int32_t* status;
 };
 
@@ -114,6 +115,12 @@ __device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, ui
     asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// 32-byte store: one full sector per thread (the output rows are 32-byte aligned when the host sets wide_stores)
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t* v) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+                 "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+
 struct Maps {        // by-value kernel argument
     CUtensorMap A, B, A2, B2;          // E4M3 data, 128-byte swizzle, boxes of 128 x 128
     CUtensorMap SA, SB, SA2, SB2;      // scale tiles: rows of 128 u32
@@ -147,7 +154,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(tfull_bar, 1);
-        mbar_init(tempty_bar, 8);             // one arrival per epilogue warp of the pair
+        mbar_init(tempty_bar, 16);            // one arrival per epilogue warp of the pair
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -261,7 +268,9 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
         }
     } else {
         // ------------------------------------------------------------ epilogue
+        // warp w drains lanes 32*(w%4).. (the quarter of tensor memory it may read), columns 128*half..
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row_in_tile = static_cast<int>(cta) * 128 + quarter * 32 + lane;
         int local = 0;
         bool ok = true;
@@ -269,43 +278,49 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
             const Tile ti = sched.get(p, t);
             if (!mbar_wait(tfull_bar, local & 1, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * 128);
             const bool empty_k = ti.k_iters == 0;
-            // drain the accumulator into registers as packed bf16, then hand it back to the MMA lane
-            uint32_t packed[BN / 2];
+            // drain this warp's part of the accumulator into registers as packed bf16, then hand it back to the MMA lane
+            uint32_t packed[64];
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(t_addr + c * 32, r);
+            for (int c = 0; c < 4; c += 2) {
+                uint32_t r0[32], r1[32];
+                tmem_ld_32x32(t_addr + c * 32, r0);
+                tmem_ld_32x32(t_addr + c * 32 + 32, r1);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    packed[c * 16 + i] = empty_k ? 0u : pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                for (int i = 0; i < 16; ++i) {
+                    packed[c * 16 + i] = empty_k ? 0u : pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+                    packed[c * 16 + 16 + i] = empty_k ? 0u : pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
 
             const int tile_row = ti.m_blk * TILE_M + row_in_tile;
+            bool row_ok = true;
+            size_t row = static_cast<size_t>(tile_row);
+            __nv_bfloat16* dst;
+            int cols_left = 128;
             if (MODE == FMODE_DUALB) {
-                const size_t off = static_cast<size_t>(tile_row) * p.ldd + static_cast<size_t>(ti.n_blk) * 128;
-#pragma unroll
-                for (int q = 0; q < 16; ++q) {
-                    st_global_v4(p.D + off + 8 * q, packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-                    st_global_v4(p.D2 + off + 8 * q, packed[64 + 4 * q], packed[64 + 4 * q + 1], packed[64 + 4 * q + 2], packed[64 + 4 * q + 3]);
-                }
+                dst = (half ? p.D2 : p.D) + row * p.ldd + static_cast<size_t>(ti.n_blk) * 128;
             } else {
-                bool row_ok = true;
-                size_t row = static_cast<size_t>(tile_row);
                 if (MODE == FMODE_WGRAD) {
                     row_ok = tile_row < p.M;
                     row += static_cast<size_t>(ti.group) * p.M;
                 }
-                __nv_bfloat16* dst = p.D + row * p.ldd + static_cast<size_t>(ti.n_blk) * BN;
-                const int cols_left = p.N - ti.n_blk * BN;
-                if (row_ok) {
+                dst = p.D + row * p.ldd + static_cast<size_t>(ti.n_blk) * BN + half * 128;
+                cols_left = p.N - ti.n_blk * BN - half * 128;
+            }
+            if (row_ok) {
+                if (p.wide_stores) {
 #pragma unroll
-                    for (int q = 0; q < 32; ++q)
+                    for (int q = 0; q < 8; ++q)
+                        if (q * 16 < cols_left) st_global_v8(dst + 16 * q, &packed[8 * q]);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 16; ++q)
                         if (q * 8 < cols_left)
                             st_global_v4(dst + 8 * q, packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                 }
@@ -385,6 +400,7 @@ extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream
     p.D = static_cast<__nv_bfloat16*>(g->D);
     p.D2 = static_cast<__nv_bfloat16*>(g->D2);
     p.ldd = g->ldd;
+    p.wide_stores = g->ldd % 16 == 0 && reinterpret_cast<uintptr_t>(g->D) % 32 == 0 && reinterpret_cast<uintptr_t>(g->D2) % 32 == 0;
     p.status = g->status;
     Maps m;
     memset(&m, 0, sizeof(m));

@@ -5,8 +5,12 @@
 //   swiglu_fwd_quant_kernel SwiGLU forward + quantise  (reference: csrc/megakernel/swiglu.cuh:38-207)
 //   swiglu_bwd_quant_kernel de-quantise saved gate/up, SwiGLU backward, router-gradient partials,
 //                           quantise d_gate / d_up      (reference: swiglu.cuh:209-566)
-// One 128 x 128 tile per CTA, staged in shared memory with an odd word pitch so that both the
-// row-wise and the column-wise passes read it without bank conflicts.
+// One 128 x 128 tile per CTA, staged in shared memory as packed bf16 pairs with an odd word pitch,
+// so that the row-wise pass (a thread owns 32 columns of one row) and the column-wise pass (a
+// thread owns 32 rows of two adjacent columns) both read it without bank conflicts.  The kernels
+// are bound by HBM, but only if the per-element instruction count stays small: everything works on
+// bf16 pairs (packed abs/max for the block maximum, one conversion instruction per two outputs)
+// and global memory is touched 32 bytes per thread per instruction.
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -15,27 +19,45 @@ namespace mokb {
 namespace {
 
 constexpr int TILE = 128;
-constexpr int PITCH = TILE + 2;   // bf16 elements per smem row
-constexpr int TILE_ELEMS = TILE * PITCH;
+constexpr int WPITCH = TILE / 2 + 1;          // 32-bit words per smem row (65: odd)
+constexpr int TILE_WORDS = TILE * WPITCH;
 
-// 32 values -> 32 E4M3 bytes + scale byte (csrc/mxfp8.cuh:45-72)
-__device__ __forceinline__ uint32_t quantize_block(const float (&v)[32], uint32_t (&out)[8]) {
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// running per-half maximum of |x| over packed bf16 pairs
+__device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w) {
+    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&m),
+                                     __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w)));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// block maximum -> E8M0 scale byte and the exact reciprocal of the scale (csrc/mxfp8.cuh:45-60):
+// scale = max(amax / 448, 1e-12) rounded up to a power of two
+__device__ __forceinline__ uint32_t scale_byte(float amax, float* inv) {
     const float scale = fmaxf(amax * 0.002232142857f, 0.000000000001f);
     uint16_t sc2;
     asm volatile("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(sc2) : "f"(scale), "f"(scale));
     const uint32_t byte = sc2 & 0xFFu;
-    const float inv = __uint_as_float((254u - byte) << 23);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        uint16_t lo, hi;
-        asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(v[4 * i] * inv), "f"(v[4 * i + 1] * inv));
-        asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(v[4 * i + 2] * inv), "f"(v[4 * i + 3] * inv));
-        out[i] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-    }
+    *inv = __uint_as_float((254u - byte) << 23);
     return byte;
+}
+
+// four floats -> four E4M3 bytes (a in the lowest byte), round to nearest even, saturating (csrc/mxfp8.cuh:62-72)
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+    uint16_t lo, hi;
+    asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
+    asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+__device__ __forceinline__ void st_global_32B(void* p, const uint32_t (&v)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+                 "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+__device__ __forceinline__ void ld_global_32B(const void* p, uint32_t (&v)[8]) {
+    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]),
+                 "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "l"(p));
 }
 
 // byte offset of the scale of (row r, 32-element block kb) of a [rows, cols] matrix in the packed
@@ -45,52 +67,76 @@ __device__ __forceinline__ size_t scale_offset(int64_t r, int64_t kb, int64_t co
     return static_cast<size_t>((rt * col_tiles + ct) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + ki);
 }
 
-// Row-wise quantisation of a staged tile into q [rows, cols] (+ scales): item = (row, block of 32 columns).
-__device__ __forceinline__ void quantize_tile_rows(const __nv_bfloat16* tile, uint8_t* q, uint8_t* sc, int64_t row_base,
+// Row-wise quantisation of a staged tile into q [rows, cols] (+ scales): item = (row, block of 32 columns);
+// consecutive lanes take consecutive rows (conflict-free with the odd pitch).
+__device__ __forceinline__ void quantize_tile_rows(const uint32_t* tile, uint8_t* q, uint8_t* sc, int64_t row_base,
                                                    int64_t r0, int64_t c0, int64_t cols) {
     for (int item = threadIdx.x; item < TILE * 4; item += blockDim.x) {
-        const int r = item >> 2, kb = item & 3;
-        float v[32];
+        const int r = item & 127, kb = item >> 7;
+        uint32_t w[16];
+        uint32_t m = 0u;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __bfloat162float(tile[r * PITCH + kb * 32 + i]);
+        for (int i = 0; i < 16; ++i) {
+            w[i] = tile[r * WPITCH + kb * 16 + i];
+            m = absmax2(m, w[i]);
+        }
+        float inv;
+        const uint32_t byte = scale_byte(fmaxf(bf16_lo(m), bf16_hi(m)), &inv);
         uint32_t out[8];
-        const uint32_t byte = quantize_block(v, out);
-        uint4* dst = reinterpret_cast<uint4*>(q + (row_base + r0 + r) * cols + c0 + kb * 32);
-        dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
-        dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            out[i] = e4m3x4(bf16_lo(w[2 * i]) * inv, bf16_hi(w[2 * i]) * inv, bf16_lo(w[2 * i + 1]) * inv, bf16_hi(w[2 * i + 1]) * inv);
+        st_global_32B(q + (row_base + r0 + r) * cols + c0 + kb * 32, out);
         sc[scale_offset(row_base + r0 + r, (c0 >> 5) + kb, cols >> 7)] = static_cast<uint8_t>(byte);
     }
 }
 
-// Column-wise quantisation into qt [cols, rows] (+ scales): item = (column, block of 32 rows).
-__device__ __forceinline__ void quantize_tile_cols(const __nv_bfloat16* tile, uint8_t* qt, uint8_t* sct, int64_t col_base,
+// Column-wise quantisation into qt [cols, rows] (+ scales): item = (pair of adjacent columns, block of 32 rows);
+// consecutive lanes take consecutive column pairs.
+__device__ __forceinline__ void quantize_tile_cols(const uint32_t* tile, uint8_t* qt, uint8_t* sct, int64_t col_base,
                                                    int64_t r0, int64_t c0, int64_t rows) {
-    for (int item = threadIdx.x; item < TILE * 4; item += blockDim.x) {
-        const int c = item & 127, kb = item >> 7;
-        float v[32];
+    for (int item = threadIdx.x; item < (TILE / 2) * 4; item += blockDim.x) {
+        const int cp = item & 63, kb = item >> 6;
+        uint32_t w[32];
+        uint32_t m = 0u;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __bfloat162float(tile[(kb * 32 + i) * PITCH + c]);
+        for (int i = 0; i < 32; ++i) {
+            w[i] = tile[(kb * 32 + i) * WPITCH + cp];
+            m = absmax2(m, w[i]);
+        }
+        float inv_a, inv_b;
+        const uint32_t byte_a = scale_byte(bf16_lo(m), &inv_a);
+        const uint32_t byte_b = scale_byte(bf16_hi(m), &inv_b);
         uint32_t out[8];
-        const uint32_t byte = quantize_block(v, out);
-        uint4* dst = reinterpret_cast<uint4*>(qt + (col_base + c0 + c) * rows + r0 + kb * 32);
-        dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
-        dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
-        sct[scale_offset(col_base + c0 + c, (r0 >> 5) + kb, rows >> 7)] = static_cast<uint8_t>(byte);
+        const int64_t col = col_base + c0 + 2 * cp;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            out[i] = e4m3x4(bf16_lo(w[4 * i]) * inv_a, bf16_lo(w[4 * i + 1]) * inv_a, bf16_lo(w[4 * i + 2]) * inv_a, bf16_lo(w[4 * i + 3]) * inv_a);
+        st_global_32B(qt + col * rows + r0 + kb * 32, out);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            out[i] = e4m3x4(bf16_hi(w[4 * i]) * inv_b, bf16_hi(w[4 * i + 1]) * inv_b, bf16_hi(w[4 * i + 2]) * inv_b, bf16_hi(w[4 * i + 3]) * inv_b);
+        st_global_32B(qt + (col + 1) * rows + r0 + kb * 32, out);
+        sct[scale_offset(col, (r0 >> 5) + kb, rows >> 7)] = static_cast<uint8_t>(byte_a);
+        sct[scale_offset(col + 1, (r0 >> 5) + kb, rows >> 7)] = static_cast<uint8_t>(byte_b);
     }
 }
 
-__device__ __forceinline__ void load_tile_bf16(__nv_bfloat16* tile, const __nv_bfloat16* src, int64_t ld) {
-    for (int i = threadIdx.x; i < TILE * 16; i += blockDim.x) {
-        const int r = i >> 4, v = i & 15;
-        const uint4 val = *reinterpret_cast<const uint4*>(src + static_cast<int64_t>(r) * ld + v * 8);
-        uint32_t* d = reinterpret_cast<uint32_t*>(&tile[r * PITCH + v * 8]);
-        d[0] = val.x; d[1] = val.y; d[2] = val.z; d[3] = val.w;
+// 128 x 128 bf16 from global memory (row stride ld elements) into a staged tile, 32 bytes per thread per load
+__device__ __forceinline__ void load_tile_bf16(uint32_t* tile, const __nv_bfloat16* src, int64_t ld) {
+    // 1024 chunks of 32 bytes over 256 threads: all four loads are issued before the first store
+    uint32_t val[4][8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + 256 * k;
+        ld_global_32B(src + static_cast<int64_t>(i >> 3) * ld + (i & 7) * 16, val[k]);
     }
-}
-
-__device__ __forceinline__ float e4m3_to_float(uint8_t b) {
-    const __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
-    return __half2float(*reinterpret_cast<const __half*>(&h));
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + 256 * k;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tile[(i >> 3) * WPITCH + (i & 7) * 8 + j] = val[k][j];
+    }
 }
 
 __device__ __forceinline__ int live_rows(const int32_t* num_rows, int64_t cap) {
@@ -110,12 +156,12 @@ __device__ __forceinline__ bool tile_in_window(const RowWindow& w, int64_t cap, 
     return *r0 < live;
 }
 
-// grid (N/128, M/128, E), 256 threads.
+// grid (N/128, window rows/128, E), 256 threads.
 __global__ void __launch_bounds__(256) quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64_t N,
                                                        RowWindow win,
                                                        uint8_t* __restrict__ q, uint8_t* __restrict__ sc,
                                                        uint8_t* __restrict__ qt, uint8_t* __restrict__ sct) {
-    __shared__ __nv_bfloat16 tile[TILE_ELEMS];
+    __shared__ uint32_t tile[TILE_WORDS];
     const int64_t e = blockIdx.z;
     const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
     int64_t r0;
@@ -131,29 +177,37 @@ struct Clamp {
     float limit;
 };
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 // gate, up [rows, I] bf16 -> gate_q, up_q, hidden_q (row-wise) and hidden_qt (column-wise).
-// grid (I/128, rows_cap/128), 256 threads, 3 staged tiles.
+// grid (I/128, window rows/128), 256 threads, 3 staged tiles.
 __global__ void __launch_bounds__(256) swiglu_fwd_quant_kernel(
     const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up, int64_t rows_cap, int64_t I,
     RowWindow win, Clamp c,
     uint8_t* gate_q, uint8_t* gate_sc, uint8_t* up_q, uint8_t* up_sc,
     uint8_t* hid_q, uint8_t* hid_sc, uint8_t* hid_qt, uint8_t* hid_sct) {
-    extern __shared__ __nv_bfloat16 sm[];
-    __nv_bfloat16 *tg = sm, *tu = sm + TILE_ELEMS, *th = sm + 2 * TILE_ELEMS;
+    extern __shared__ uint32_t sm[];
+    uint32_t *tg = sm, *tu = sm + TILE_WORDS, *th = sm + 2 * TILE_WORDS;
     const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
     int64_t r0;
     if (!tile_in_window(win, rows_cap, &r0)) return;
     load_tile_bf16(tg, gate + r0 * I + c0, I);
     load_tile_bf16(tu, up + r0 * I + c0, I);
     __syncthreads();
-    for (int i = threadIdx.x; i < TILE * TILE; i += blockDim.x) {
-        const int r = i >> 7, col = i & 127;
-        float g = __bfloat162float(tg[r * PITCH + col]), u = __bfloat162float(tu[r * PITCH + col]);
+    for (int i = threadIdx.x; i < TILE * (TILE / 2); i += blockDim.x) {
+        const int r = i >> 6, wcol = i & 63;
+        const uint32_t gw = tg[r * WPITCH + wcol], uw = tu[r * WPITCH + wcol];
+        float g0 = bf16_lo(gw), g1 = bf16_hi(gw), u0 = bf16_lo(uw), u1 = bf16_hi(uw);
         if (c.on) {
-            g = fminf(g, c.limit);
-            u = fminf(fmaxf(u, -c.limit), c.limit);
+            g0 = fminf(g0, c.limit);
+            g1 = fminf(g1, c.limit);
+            u0 = fminf(fmaxf(u0, -c.limit), c.limit);
+            u1 = fminf(fmaxf(u1, -c.limit), c.limit);
         }
-        th[r * PITCH + col] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+        th[r * WPITCH + wcol] = pack2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
     }
     __syncthreads();
     quantize_tile_rows(tg, gate_q, gate_sc, 0, r0, c0, I);
@@ -162,24 +216,30 @@ __global__ void __launch_bounds__(256) swiglu_fwd_quant_kernel(
     quantize_tile_cols(th, hid_qt, hid_sct, 0, r0, c0, rows_cap);
 }
 
+// two E4M3 bytes (the low 16 bits of v) -> two floats
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t v) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v & 0xffffu), __NV_E4M3);
+    return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+
 // Saved gate/up (E4M3 + scales), d_hidden bf16 -> d_gate, d_up (bf16 staged), their row-wise and
 // column-wise quantisations, and the per-(row, 128-column block) router-gradient partial
-// sum(d_hidden * silu(g) * u) / w.  grid (I/128, rows_cap/128), 256 threads.
+// sum(d_hidden * silu(g) * u) / w.  grid (I/128, window rows/128), 256 threads.
 __global__ void __launch_bounds__(256) swiglu_bwd_quant_kernel(
     const uint8_t* __restrict__ gate_q, const uint8_t* __restrict__ gate_sc, const uint8_t* __restrict__ up_q,
     const uint8_t* __restrict__ up_sc, const __nv_bfloat16* __restrict__ d_hidden, int64_t rows_cap, int64_t I,
     RowWindow win, Clamp c, const float* __restrict__ row_scale,
     uint8_t* dg_q, uint8_t* dg_sc, uint8_t* dg_qt, uint8_t* dg_sct,
     uint8_t* du_q, uint8_t* du_sc, uint8_t* du_qt, uint8_t* du_sct, float* __restrict__ partials) {
-    extern __shared__ __nv_bfloat16 sm[];
-    __nv_bfloat16 *tdh = sm, *tdg = sm + TILE_ELEMS, *tdu = sm + 2 * TILE_ELEMS;
+    extern __shared__ uint32_t sm[];
+    uint32_t *tdh = sm, *tdg = sm + TILE_WORDS, *tdu = sm + 2 * TILE_WORDS;
     __shared__ float row_part[TILE][2];
     const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
     int64_t r0;
     if (!tile_in_window(win, rows_cap, &r0)) return;
     load_tile_bf16(tdh, d_hidden + r0 * I + c0, I);
     __syncthreads();
-    // two threads per row, 64 columns each (two scale blocks of 32)
+    // two threads per row, 64 columns each (two scale blocks of 32), columns in ascending order
     const int r = threadIdx.x & 127, half = threadIdx.x >> 7;
     const int64_t row = r0 + r;
     const float w = row_scale ? row_scale[row] : 1.0f;
@@ -188,28 +248,36 @@ __global__ void __launch_bounds__(256) swiglu_bwd_quant_kernel(
     for (int kb = half * 2; kb < half * 2 + 2; ++kb) {
         const float gs = __uint_as_float(static_cast<uint32_t>(gate_sc[scale_offset(row, (c0 >> 5) + kb, I >> 7)]) << 23);
         const float us = __uint_as_float(static_cast<uint32_t>(up_sc[scale_offset(row, (c0 >> 5) + kb, I >> 7)]) << 23);
-        const uint4* gp = reinterpret_cast<const uint4*>(gate_q + row * I + c0 + kb * 32);
-        const uint4* upp = reinterpret_cast<const uint4*>(up_q + row * I + c0 + kb * 32);
-        uint4 gv[2] = {gp[0], gp[1]}, uv[2] = {upp[0], upp[1]};
-        const uint8_t* gb = reinterpret_cast<const uint8_t*>(gv);
-        const uint8_t* ub = reinterpret_cast<const uint8_t*>(uv);
-#pragma unroll 8
-        for (int i = 0; i < 32; ++i) {
-            float g = e4m3_to_float(gb[i]) * gs, u = e4m3_to_float(ub[i]) * us;
-            const float dh = __bfloat162float(tdh[r * PITCH + kb * 32 + i]);
-            bool g_ok = true, u_ok = true;
-            if (c.on) {
-                g_ok = g <= c.limit;
-                u_ok = (u >= -c.limit) && (u <= c.limit);
-                g = fminf(g, c.limit);
-                u = fminf(fmaxf(u, -c.limit), c.limit);
+        uint32_t gv[8], uv[8];
+        ld_global_32B(gate_q + row * I + c0 + kb * 32, gv);
+        ld_global_32B(up_q + row * I + c0 + kb * 32, uv);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float2 gq = e4m3x2_to_float2(gv[i >> 1] >> ((i & 1) * 16));
+            const float2 uq = e4m3x2_to_float2(uv[i >> 1] >> ((i & 1) * 16));
+            const uint32_t dhw = tdh[r * WPITCH + kb * 16 + i];
+            const float gg[2] = {gq.x * gs, gq.y * gs}, uu[2] = {uq.x * us, uq.y * us};
+            const float dh[2] = {bf16_lo(dhw), bf16_hi(dhw)};
+            float dg[2], du[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float g = gg[j], u = uu[j];
+                bool g_ok = true, u_ok = true;
+                if (c.on) {
+                    g_ok = g <= c.limit;
+                    u_ok = (u >= -c.limit) && (u <= c.limit);
+                    g = fminf(g, c.limit);
+                    u = fminf(fmaxf(u, -c.limit), c.limit);
+                }
+                const float sig = 1.0f / (1.0f + __expf(-g));
+                const float silu = g * sig;
+                const float dsilu = (1.0f - silu) * sig + silu;
+                dg[j] = g_ok ? dsilu * u * dh[j] : 0.0f;
+                du[j] = u_ok ? silu * dh[j] : 0.0f;
+                partial += dh[j] * inv_w * (silu * u);
             }
-            const float sig = 1.0f / (1.0f + __expf(-g));
-            const float silu = g * sig;
-            const float dsilu = (1.0f - silu) * sig + silu;
-            tdg[r * PITCH + kb * 32 + i] = __float2bfloat16_rn(g_ok ? dsilu * u * dh : 0.0f);
-            tdu[r * PITCH + kb * 32 + i] = __float2bfloat16_rn(u_ok ? silu * dh : 0.0f);
-            partial += dh * inv_w * (silu * u);
+            tdg[r * WPITCH + kb * 16 + i] = pack2(dg[0], dg[1]);
+            tdu[r * WPITCH + kb * 16 + i] = pack2(du[0], du[1]);
         }
     }
     row_part[r][half] = partial;
@@ -235,17 +303,26 @@ __global__ void row_sum_kernel(const float* __restrict__ partials, int nblk, Row
 
 }  // namespace
 
+namespace {
+bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; }
+int check_window(const char* who, int row_begin, int* row_end, int64_t rows) {
+    if (*row_end <= 0) *row_end = static_cast<int>(rows);
+    MOKB_REQUIRE(row_begin >= 0 && row_begin % 128 == 0 && *row_end % 128 == 0 && row_begin <= *row_end && *row_end <= rows,
+                 "%s: bad row window [%d, %d) of %lld", who, row_begin, *row_end, static_cast<long long>(rows));
+    return MOKB_OK;
+}
+}  // namespace
+
 int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int32_t* num_rows, int row_begin, int row_end,
                   void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, cudaStream_t stream) {
-    if (row_end <= 0) row_end = static_cast<int>(M);
-    MOKB_REQUIRE(row_begin >= 0 && row_begin % 128 == 0 && row_end % 128 == 0 && row_begin <= row_end && row_end <= M,
-                 "mxfp8_quantize: bad row window");
-    if (row_begin == row_end) return MOKB_OK;
     MOKB_REQUIRE(x_bf16 != nullptr, "mxfp8_quantize: null input");
     MOKB_REQUIRE(E > 0 && M > 0 && N > 0 && M % 128 == 0 && N % 128 == 0, "mxfp8_quantize: M and N must be positive multiples of 128");
     MOKB_REQUIRE((x_fp8 == nullptr) == (x_sc == nullptr) && (x_fp8_t == nullptr) == (x_sc_t == nullptr),
                  "mxfp8_quantize: data and scale outputs go together");
     MOKB_REQUIRE(x_fp8 || x_fp8_t, "mxfp8_quantize: at least one quantised layout must be requested");
+    MOKB_REQUIRE(aligned32(x_bf16) && aligned32(x_fp8) && aligned32(x_fp8_t), "mxfp8_quantize: tensors must be 32-byte aligned");
+    MOKB_TRY(check_window("mxfp8_quantize", row_begin, &row_end, M));
+    if (row_begin == row_end) return MOKB_OK;
     MOKB_REQUIRE(E <= 65535 && M / 128 <= 65535, "mxfp8_quantize: tensor too large for one launch");
     const dim3 grid(static_cast<unsigned>(N / 128), static_cast<unsigned>((row_end - row_begin) / 128), static_cast<unsigned>(E));
     quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), M, N, RowWindow{num_rows, row_begin, row_end},
@@ -261,12 +338,12 @@ int swiglu_fwd_quant_impl(const void* gate, const void* up, int64_t rows_cap, in
                           void* hid_q, void* hid_sc, void* hid_qt, void* hid_sct, cudaStream_t stream) {
     MOKB_REQUIRE(gate && up && gate_q && gate_sc && up_q && up_sc && hid_q && hid_sc && hid_qt && hid_sct, "swiglu_fwd_quant: null pointer");
     MOKB_REQUIRE(rows_cap > 0 && rows_cap % 128 == 0 && I > 0 && I % 128 == 0 && rows_cap / 128 <= 65535, "swiglu_fwd_quant: bad sizes");
-    const size_t smem = 3 * TILE_ELEMS * sizeof(__nv_bfloat16);
-    MOKB_CUDA(cudaFuncSetAttribute(swiglu_fwd_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (row_end <= 0) row_end = static_cast<int>(rows_cap);
-    MOKB_REQUIRE(row_begin >= 0 && row_begin % 128 == 0 && row_end % 128 == 0 && row_begin <= row_end && row_end <= rows_cap,
-                 "swiglu_fwd_quant: bad row window");
+    MOKB_REQUIRE(aligned32(gate) && aligned32(up) && aligned32(gate_q) && aligned32(up_q) && aligned32(hid_q) && aligned32(hid_qt),
+                 "swiglu_fwd_quant: tensors must be 32-byte aligned");
+    MOKB_TRY(check_window("swiglu_fwd_quant", row_begin, &row_end, rows_cap));
     if (row_begin == row_end) return MOKB_OK;
+    const size_t smem = 3 * TILE_WORDS * sizeof(uint32_t);
+    MOKB_CUDA(cudaFuncSetAttribute(swiglu_fwd_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid(static_cast<unsigned>(I / 128), static_cast<unsigned>((row_end - row_begin) / 128));
     swiglu_fwd_quant_kernel<<<grid, 256, smem, stream>>>(
         static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), rows_cap, I, RowWindow{num_rows, row_begin, row_end},
@@ -287,12 +364,12 @@ int swiglu_bwd_quant_impl(const void* gate_q, const void* gate_sc, const void* u
                  "swiglu_bwd_quant: null pointer");
     MOKB_REQUIRE((partials == nullptr) == (row_grad == nullptr), "swiglu_bwd_quant: partials and row_grad go together");
     MOKB_REQUIRE(rows_cap > 0 && rows_cap % 128 == 0 && I > 0 && I % 128 == 0 && rows_cap / 128 <= 65535, "swiglu_bwd_quant: bad sizes");
-    const size_t smem = 3 * TILE_ELEMS * sizeof(__nv_bfloat16);
-    MOKB_CUDA(cudaFuncSetAttribute(swiglu_bwd_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (row_end <= 0) row_end = static_cast<int>(rows_cap);
-    MOKB_REQUIRE(row_begin >= 0 && row_begin % 128 == 0 && row_end % 128 == 0 && row_begin <= row_end && row_end <= rows_cap,
-                 "swiglu_bwd_quant: bad row window");
+    MOKB_REQUIRE(aligned32(gate_q) && aligned32(up_q) && aligned32(d_hidden) && aligned32(dg_q) && aligned32(dg_qt) && aligned32(du_q) &&
+                 aligned32(du_qt), "swiglu_bwd_quant: tensors must be 32-byte aligned");
+    MOKB_TRY(check_window("swiglu_bwd_quant", row_begin, &row_end, rows_cap));
     if (row_begin == row_end) return MOKB_OK;
+    const size_t smem = 3 * TILE_WORDS * sizeof(uint32_t);
+    MOKB_CUDA(cudaFuncSetAttribute(swiglu_bwd_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const RowWindow win{num_rows, row_begin, row_end};
     const dim3 grid(static_cast<unsigned>(I / 128), static_cast<unsigned>((row_end - row_begin) / 128));
     swiglu_bwd_quant_kernel<<<grid, 256, smem, stream>>>(
