@@ -44,7 +44,7 @@ extern "C" {
 #define MOKB_ST_SCHEDULE_OVERFLOW 1   /* padded rows exceed schedule_capacity */
 #define MOKB_ST_BARRIER_TIMEOUT 2     /* a peer never arrived at barrier_all */
 #define MOKB_ST_PIPELINE_TIMEOUT 3    /* an mbarrier wait inside a GEMM ran out */
-#define MOKB_ST_MACROBATCH_OVERFLOW 4 /* padded rows exceed macrobatch_size */
+#define MOKB_ST_MACROBATCH_OVERFLOW 4 /* reserved: every layer entry point splits the rows into macrobatches */
 
 const char* mokb_last_error(void);
 /* Compute capability major*10+minor of the current device, or a negative error. */
@@ -240,9 +240,14 @@ typedef struct {
     const void *w_routed_gate_t, *w_routed_gate_t_sc;                         /* [E_l, H, I] = W_gate^T quantised along I */
     const void *w_routed_up_t, *w_routed_up_t_sc;
     const void *w_routed_down_t, *w_routed_down_t_sc;                         /* [E_l, I, H] = W_down^T quantised along H */
-    /* saved forward context */
-    const void *x_fp8_t, *x_sc_t, *gate_shared, *gate_fp8, *gate_sc, *up_shared, *up_fp8, *up_sc;
-    const void *hidden_shared, *hidden_fp8_t, *hidden_sc_t;
+    /* saved forward context; the routed tensors are overwritten when later macrobatches are replayed */
+    void *x_fp8_t, *x_sc_t;
+    const void *gate_shared;
+    void *gate_fp8, *gate_sc;
+    const void *up_shared;
+    void *up_fp8, *up_sc;
+    const void *hidden_shared;
+    void *hidden_fp8_t, *hidden_sc_t;
     /* outputs (ops.py:903-921 of the reference) */
     void *d_x_shared, *d_x_routed;                                            /* [T, H], [MB, H] bf16 */
     void *d_gate_shared, *d_gate_fp8, *d_gate_sc;                             /* [T, I] bf16; [MB, I] */
@@ -255,13 +260,21 @@ typedef struct {
     void *d_y_fp8_t, *d_y_sc_t;                                               /* [H, MB] */
     void *d_gate_fp8_t, *d_gate_sc_t, *d_up_fp8_t, *d_up_sc_t;                /* [I, MB] */
     void *partials;                                                           /* [MB, I/128] f32 */
+    /* replay of macrobatches 1.. (the saved context holds macrobatch 0; the backward rebuilds the later ones into
+     * the context buffers, which it therefore overwrites, ops.py:785-791 of the reference).  Required only when
+     * schedule_capacity > macrobatch_size; null otherwise. */
+    const void *w_routed_gate, *w_routed_gate_sc, *w_routed_up, *w_routed_up_sc;   /* forward weights, quantised along H */
+    void *x_routed;                                                           /* [MB, H] bf16 */
+    void *x_fp8, *x_sc;                                                       /* [MB, H] */
+    void *gate_bf16, *up_bf16;                                                /* [MB, I] bf16 */
+    void *hidden_fp8, *hidden_sc;                                             /* [MB, I] */
     void* scratch;
     int32_t* status;
 } mokb_bwd_mxfp8_args;
 
 int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_args* args, void* stream);
 int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_args* args, void* stream);
-/* sizeof() of {mokb_fwd_mxfp8_args, mokb_bwd_mxfp8_args}. */
+/* sizeof() of {mokb_fwd_mxfp8_args, mokb_bwd_mxfp8_args, mokb_gemm_fp8_args}. */
 int mokb_struct_sizes_mxfp8(int* out, int n);
 
 /* ---- building blocks, exported for tests and micro-benchmarks.  They are the
@@ -300,7 +313,11 @@ int mokb_grouped_gemm_bf16(const mokb_gemm_args* args, void* stream);
  *   mode 0: D[rows,N] = A[rows,K] * B[g][N,K]^T, plus A2 * B2[g]^T into the same tile when A2 is given
  *   mode 1: D = A * B[g]^T and D2 = A * B2[g]^T in one pass (gate and up), N columns each
  *   mode 2: D[g][M,N] = A[M, cols_g] * B[N, cols_g]^T with cols_g = [off[g], off[g+1]) of the
- *           rows_static token columns of A [M, rows_static] and B [N, rows_static] (weight gradients) */
+ *           rows_static token columns of A [M, rows_static] and B [N, rows_static] (weight gradients).
+ *           t_first: A and B hold the token columns [t_first, t_first + rows_static) of the row space that
+ *           group_offsets refers to (a macrobatch of a longer schedule); offsets outside are not allowed.
+ *           accumulate != 0 adds to the stored bf16 D (a group with an empty window then leaves D untouched
+ *           instead of zeroing it). */
 typedef struct {
     int mode;
     int rows_static, row_begin, row_end;     /* as in mokb_gemm_args; multiples of 256 */
@@ -311,6 +328,7 @@ typedef struct {
     const void *A, *A_sc, *B, *B_sc, *A2, *A2_sc, *B2, *B2_sc;
     void *D, *D2;
     int ldd;
+    int t_first, accumulate;                 /* mode 2 only */
     int32_t* status;
 } mokb_gemm_fp8_args;
 int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* args, void* stream);

@@ -49,7 +49,11 @@ int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                       int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s);
 
-// MXFP8 codec launchers (quantize.cu); `num_rows` (device, optional) bounds the rows that are processed.
+// MXFP8 codec launchers (quantize.cu).  Rows [row_begin, min(row_end, *num_rows)) are processed (row_end = 0: all
+// M / rows_cap rows; `num_rows` is a device pointer, optional).  Row numbers are the caller's: a buffer holding only
+// rows [first, first + M) is passed with every pointer moved back by `first` rows (transposed tensors: by `first`
+// bytes, scale tensors: by first / 128 tiles along the row axis), and M / rows_cap stays the buffer's own row count,
+// which is also the row stride of the transposed outputs.
 int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int32_t* num_rows, int row_begin, int row_end,
                   void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, cudaStream_t stream);
 int swiglu_fwd_quant_impl(const void* gate, const void* up, int64_t rows_cap, int64_t I, const int32_t* num_rows,

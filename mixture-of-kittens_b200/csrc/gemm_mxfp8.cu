@@ -58,6 +58,8 @@ struct FParams {
     __nv_bfloat16 *D, *D2;
     int ldd;
     int wide_stores;                 // D (and D2) rows are 32-byte aligned: the epilogue stores 32 bytes per instruction
+    int accumulate;                  // FMODE_WGRAD: add to the stored bf16 result instead of overwriting it
+    int k_tile_origin;               // FMODE_WGRAD: the operands' first token column, in 128-token tiles, in group_offsets' row space
     int32_t* status;
 };
 
@@ -93,7 +95,7 @@ struct Sched {
             ti.n_blk = rem / m_blocks;
             ti.m_blk = rem - ti.n_blk * m_blocks;
             const int c0 = p.group_offsets[ti.group];
-            ti.k_tile0 = c0 / BKB;
+            ti.k_tile0 = c0 / BKB - p.k_tile_origin;
             ti.k_iters = (p.group_offsets[ti.group + 1] - c0) / BKB;
         } else {
             const int per = GROUP_M * n_blocks;
@@ -281,23 +283,6 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * 128);
             const bool empty_k = ti.k_iters == 0;
             // drain this warp's part of the accumulator into registers as packed bf16, then hand it back to the MMA lane
-            uint32_t packed[64];
-#pragma unroll
-            for (int c = 0; c < 4; c += 2) {
-                uint32_t r0[32], r1[32];
-                tmem_ld_32x32(t_addr + c * 32, r0);
-                tmem_ld_32x32(t_addr + c * 32 + 32, r1);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    packed[c * 16 + i] = empty_k ? 0u : pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
-                    packed[c * 16 + 16 + i] = empty_k ? 0u : pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
-
             const int tile_row = ti.m_blk * TILE_M + row_in_tile;
             bool row_ok = true;
             size_t row = static_cast<size_t>(tile_row);
@@ -313,6 +298,36 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
                 dst = p.D + row * p.ldd + static_cast<size_t>(ti.n_blk) * BN + half * 128;
                 cols_left = p.N - ti.n_blk * BN - half * 128;
             }
+            const bool add_old = MODE == FMODE_WGRAD && p.accumulate;
+            if (add_old && empty_k) row_ok = false;        // nothing to add: the stored gradient stays
+            uint32_t packed[64];
+#pragma unroll
+            for (int c = 0; c < 4; c += 2) {
+                uint32_t r0[32], r1[32];
+                tmem_ld_32x32(t_addr + c * 32, r0);
+                tmem_ld_32x32(t_addr + c * 32 + 32, r1);
+                tmem_ld_wait();
+                if (add_old && row_ok && c * 32 < cols_left) {      // fp32 accumulator + stored bf16, rounded once
+                    const uint32_t* old0 = reinterpret_cast<const uint32_t*>(dst + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 f0 = unpack_bf16(old0[i]), f1 = unpack_bf16(old0[16 + i]);
+                        r0[2 * i] = __float_as_uint(__uint_as_float(r0[2 * i]) + f0.x);
+                        r0[2 * i + 1] = __float_as_uint(__uint_as_float(r0[2 * i + 1]) + f0.y);
+                        r1[2 * i] = __float_as_uint(__uint_as_float(r1[2 * i]) + f1.x);
+                        r1[2 * i + 1] = __float_as_uint(__uint_as_float(r1[2 * i + 1]) + f1.y);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    packed[c * 16 + i] = empty_k ? 0u : pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+                    packed[c * 16 + 16 + i] = empty_k ? 0u : pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
+
             if (row_ok) {
                 if (p.wide_stores) {
 #pragma unroll
@@ -410,12 +425,15 @@ extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream
         // A [M, rows], B [N, rows]: the contraction runs over the token axis, one window per group
         MOKB_REQUIRE(g->M > 0 && g->M % 128 == 0 && g->N > 0 && g->N % 128 == 0, "grouped_gemm_mxfp8 WGRAD: M and N must be multiples of 128");
         MOKB_REQUIRE(g->group_offsets != nullptr, "grouped_gemm_mxfp8 WGRAD: group_offsets required");
+        MOKB_REQUIRE(g->t_first >= 0 && g->t_first % 128 == 0, "grouped_gemm_mxfp8 WGRAD: t_first must be a non-negative multiple of 128");
         MOKB_TRY(data_map(&m.A, g->A, rows, g->M));
         MOKB_TRY(data_map(&m.B, g->B, rows, g->N));
         MOKB_TRY(scale_map(&m.SA, g->A_sc, static_cast<uint64_t>(g->M / 128) * (rows / 128)));
         MOKB_TRY(scale_map(&m.SB, g->B_sc, static_cast<uint64_t>(g->N / 128) * (rows / 128)));
         m.A2 = m.A; m.B2 = m.B; m.SA2 = m.SA; m.SB2 = m.SB;
         p.a_ktiles = p.b_ktiles = static_cast<int>(rows / 128);
+        p.k_tile_origin = g->t_first / BKB;
+        p.accumulate = g->accumulate;
         return launch<FMODE_WGRAD>(m, p, g->G * ((g->M + TILE_M - 1) / TILE_M) * ((g->N + BN - 1) / BN), stream);
     }
     MOKB_REQUIRE(g->K > 0 && g->K % 128 == 0 && g->N > 0 && g->N % 128 == 0, "grouped_gemm_mxfp8: K and N must be multiples of 128");

@@ -108,7 +108,7 @@ extern "C" int mokb_struct_sizes(int* out, int n) {
 }
 
 extern "C" int mokb_struct_sizes_mxfp8(int* out, int n) {
-    const int sizes[2] = {(int)sizeof(mokb_fwd_mxfp8_args), (int)sizeof(mokb_bwd_mxfp8_args)};
-    for (int i = 0; i < n && i < 2; ++i) out[i] = sizes[i];
-    return 2;
+    const int sizes[3] = {(int)sizeof(mokb_fwd_mxfp8_args), (int)sizeof(mokb_bwd_mxfp8_args), (int)sizeof(mokb_gemm_fp8_args)};
+    for (int i = 0; i < n && i < 3; ++i) out[i] = sizes[i];
+    return 3;
 }

@@ -90,7 +90,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_arg
     // recompute only rebuilds macrobatch 0 (the saved context); the forward walks all of them, last first
     const int n_macro = with_down ? macrobatches(C, MB) : 1;
 
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, false, s, a->status, stream));
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, s, a->status, stream));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
     bool shared_done = false;
 
@@ -192,7 +192,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
     const float limv = a->swiglu_limit;
     const int n_macro = macrobatches(C, MB);
 
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, false, s, a->status, stream));
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, s, a->status, stream));
     const void* d_y_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->d_y_ptrs_host[a->ep_rank]));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
     auto wgrad = [&](const void* A, int M, const void* B, int N, void* D, int G, int rows, const int32_t* offs, int accumulate) -> int {

@@ -51,10 +51,9 @@ inline Scratch carve(void* base, int capacity, int E_l, int MB) {
 }
 
 // One CTA: segment offsets from tokens_per_expert, row-block -> expert table, per-macrobatch
-// offsets, and the capacity checks that the reference turns into a trap.
-// single_macrobatch != 0: the caller cannot split the rows, so N > MB is reported and nothing runs.
+// offsets, and the capacity check that the reference turns into a trap.
 __global__ void prologue_kernel(const int32_t* __restrict__ tokens_per_expert, const int32_t* __restrict__ num_tokens,
-                                int E_l, int capacity, int MB, int T, int single_macrobatch, Scratch s, int32_t* status) {
+                                int E_l, int capacity, int MB, int T, Scratch s, int32_t* status) {
     __shared__ int32_t offs[2049];
     __shared__ int32_t ok_s;
     if (threadIdx.x == 0) {
@@ -67,7 +66,6 @@ __global__ void prologue_kernel(const int32_t* __restrict__ tokens_per_expert, c
         const int n = *num_tokens;
         int ok = 1;
         if (n != run || n < 0 || n > capacity) { ok = 0; atomicCAS(status, MOKB_ST_OK, MOKB_ST_SCHEDULE_OVERFLOW); }
-        else if (single_macrobatch && n > MB) { ok = 0; atomicCAS(status, MOKB_ST_OK, MOKB_ST_MACROBATCH_OVERFLOW); }
         ok_s = ok;
         *s.n_rows = ok ? n : 0;
         s.shared_offsets[0] = 0;
@@ -102,10 +100,9 @@ __global__ void prologue_kernel(const int32_t* __restrict__ tokens_per_expert, c
     }
 }
 
-inline int run_prologue(const int32_t* tpe, const int32_t* num_tokens, int E_l, int C, int MB, int T, bool single_macrobatch,
-                        const Scratch& s, int32_t* status, cudaStream_t stream) {
+inline int run_prologue(const int32_t* tpe, const int32_t* num_tokens, int E_l, int C, int MB, int T, const Scratch& s, int32_t* status, cudaStream_t stream) {
     MOKB_REQUIRE(E_l <= 2048, "layer: at most 2048 local experts");
-    prologue_kernel<<<1, 256, 0, stream>>>(tpe, num_tokens, E_l, C, MB, T, single_macrobatch ? 1 : 0, s, status);
+    prologue_kernel<<<1, 256, 0, stream>>>(tpe, num_tokens, E_l, C, MB, T, s, status);
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     return MOKB_OK;

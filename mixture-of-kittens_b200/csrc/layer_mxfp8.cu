@@ -14,9 +14,17 @@ using namespace mokb;
 //             -> de-quantise saved gate/up, SwiGLU backward, router-gradient partials, quantise d_gate, d_up
 //             both ways -> d_x = d_gate_q * WgT_q^T + d_up_q * WuT_q^T -> combine;
 //             weight gradients contract the token-wise quantised tensors over each expert's rows.
-// The forward is cut into row windows (minibatch_size rows each): dispatch + quantise of window c+1 and the
-// combine of window c-1 run on the side streams while the GEMMs of window c run on the caller's stream.
-// In the backward, dispatch / combine overlap the shared expert's BF16 GEMMs and the weight gradients.
+//
+// Macrobatches: every [MB, .] / [., MB] buffer holds the rows of one macrobatch at a time.  The forward walks
+// the macrobatches last to first, so the buffers finally hold macrobatch 0 (the saved context); the backward
+// starts with macrobatch 0 from the context and replays the later ones (dispatch x, quantise, gate|up,
+// SwiGLU + quantise) into the same buffers, accumulating the weight gradients.  Kernels address rows by
+// their schedule row number; a buffer's pointers are moved back by the macrobatch's first row.
+//
+// Overlap: macrobatch 0 of the forward is cut into row windows (minibatch_size rows): dispatch + quantise of
+// window c+1 and the combine of window c-1 run on the side streams while the GEMMs of window c run on the
+// caller's stream.  In the backward, dispatch / combine overlap the shared expert's BF16 GEMMs and the
+// weight gradients.
 namespace mokb {
 namespace {
 
@@ -26,6 +34,65 @@ mokb_gemm_fp8_args fp8_base(int32_t* status) {
     g.G = 1;
     g.status = status;
     return g;
+}
+
+// Packed scale tensor [rows/128, cols/128, 32, 16] of a [rows, cols] matrix, moved back by `first` rows.
+inline void* rebase_scales(const void* sc, int first, int cols) {
+    return reinterpret_cast<void*>(reinterpret_cast<uintptr_t>(sc) - static_cast<size_t>(first / 128) * (cols / 128) * 512);
+}
+// Token-wise ("transposed") E4M3 tensor [cols, MB], token r of the macrobatch at column r - first: moved back by `first` bytes;
+// its scale tensor [cols/128, MB/128, 32, 16] by first/128 tiles.
+inline void* rebase_t(const void* p, int first) {
+    return reinterpret_cast<void*>(reinterpret_cast<uintptr_t>(p) - static_cast<size_t>(first));
+}
+inline void* rebase_scales_t(const void* sc, int first) {
+    return reinterpret_cast<void*>(reinterpret_cast<uintptr_t>(sc) - static_cast<size_t>(first / 128) * 512);
+}
+
+// The routed forward tensors of one macrobatch, addressed by schedule row.
+struct FwdView {
+    void *x_routed, *x_fp8, *x_sc, *x_fp8_t, *x_sc_t;
+    void *gate_bf16, *up_bf16, *gate_fp8, *gate_sc, *up_fp8, *up_sc;
+    void *hidden_fp8, *hidden_sc, *hidden_fp8_t, *hidden_sc_t;
+};
+
+FwdView fwd_view(int lo, int H, int I, void* x_routed, void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, void* gate_bf16,
+                 void* up_bf16, void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc, void* hidden_fp8, void* hidden_sc,
+                 void* hidden_fp8_t, void* hidden_sc_t) {
+    FwdView v;
+    v.x_routed = rebase(x_routed, lo, 2ull * H);
+    v.x_fp8 = rebase(x_fp8, lo, 1ull * H);
+    v.x_sc = rebase_scales(x_sc, lo, H);
+    v.x_fp8_t = rebase_t(x_fp8_t, lo);
+    v.x_sc_t = rebase_scales_t(x_sc_t, lo);
+    v.gate_bf16 = rebase(gate_bf16, lo, 2ull * I);
+    v.up_bf16 = rebase(up_bf16, lo, 2ull * I);
+    v.gate_fp8 = rebase(gate_fp8, lo, 1ull * I);
+    v.gate_sc = rebase_scales(gate_sc, lo, I);
+    v.up_fp8 = rebase(up_fp8, lo, 1ull * I);
+    v.up_sc = rebase_scales(up_sc, lo, I);
+    v.hidden_fp8 = rebase(hidden_fp8, lo, 1ull * I);
+    v.hidden_sc = rebase_scales(hidden_sc, lo, I);
+    v.hidden_fp8_t = rebase_t(hidden_fp8_t, lo);
+    v.hidden_sc_t = rebase_scales_t(hidden_sc_t, lo);
+    return v;
+}
+
+struct GateUpWeights {
+    const void *gate, *gate_sc, *up, *up_sc;
+};
+
+// rows [r0, r1) of macrobatch rows [.., hi): gate|up GEMM, then SwiGLU + quantisation of gate, up and hidden
+int gate_up_swiglu(const FwdView& v, const GateUpWeights& w, const Scratch& s, int r0, int r1, int hi, int MB, int E_l, int H, int I,
+                   int has_limit, float limit, int32_t* status, cudaStream_t stream) {
+    mokb_gemm_fp8_args f = fp8_base(status);
+    f.mode = 1; f.rows_static = hi; f.row_begin = r0; f.row_end = r1;
+    f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
+    f.A = v.x_fp8; f.A_sc = v.x_sc; f.B = w.gate; f.B_sc = w.gate_sc; f.B2 = w.up; f.B2_sc = w.up_sc;
+    f.D = v.gate_bf16; f.D2 = v.up_bf16; f.ldd = I;
+    MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
+    return swiglu_fwd_quant_impl(v.gate_bf16, v.up_bf16, MB, I, s.n_rows, r0, r1, has_limit, limit, v.gate_fp8, v.gate_sc, v.up_fp8,
+                                 v.up_sc, v.hidden_fp8, v.hidden_sc, v.hidden_fp8_t, v.hidden_sc_t, stream);
 }
 
 }  // namespace
@@ -45,74 +112,85 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
         MOKB_REQUIRE(a->combine_ptrs_host && a->w_shared_down && a->w_routed_down && a->w_routed_down_sc && a->y_shared && a->y_routed,
                      "fwd_mxfp8: null down/combine pointer");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
-    const Scratch s = carve(a->scratch, a->schedule_capacity, E_l, MB);
+    const int C = a->schedule_capacity;
+    const Scratch s = carve(a->scratch, C, E_l, MB);
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
     cudaStream_t s_in = overlap ? as->s1 : stream, s_out = overlap ? as->s2 : stream;
     const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
-    // overlap windows: rows [r0, r1) flow dispatch+quantise (side stream 1) -> GEMMs (caller's stream) -> combine (side stream 2)
-    const int chunk = chunk_rows_for(MB, a->minibatch_size);
-    const int nchunks = (MB + chunk - 1) / chunk;
+    // recompute only rebuilds macrobatch 0 (the saved context); the forward walks all of them, last first
+    const int n_macro = with_down ? macrobatches(C, MB) : 1;
+    const GateUpWeights wgu{a->w_routed_gate, a->w_routed_gate_sc, a->w_routed_up, a->w_routed_up_sc};
 
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, true, s, a->status, stream));
-    if (overlap) {
-        MOKB_CUDA(cudaEventRecord(as->fork, stream));
-        MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
-        if (with_down) MOKB_CUDA(cudaStreamWaitEvent(s_out, as->fork, 0));
-    }
-    // dispatch + quantise (row-wise for the GEMM, token-wise for the weight gradients), window by window
-    for (int c = 0; c < nchunks; ++c) {
-        const int r0 = c * chunk, r1 = r0 + chunk < MB ? r0 + chunk : MB;
-        MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, r0, r1, a->topk, H,
-                                    a->x_routed, nullptr, nullptr, comm_blocks, s_in));
-        MOKB_TRY(quantize_impl(a->x_routed, 1, MB, H, s.n_rows, r0, r1, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, s_in));
-        if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
-    }
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, s, a->status, stream));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
+    bool shared_done = false;
 
-    // shared expert (BF16)
-    mokb_gemm_args g = gemm_base(a->status);
-    g.mode = 1; g.rows_static = T; g.N = I; g.K = H;
-    g.A = x_local; g.lda = H; g.B = a->w_shared_gate; g.B2 = a->w_shared_up; g.ldb = H;
-    g.D = a->gate_shared; g.D2 = a->up_shared; g.D3 = a->hidden_shared; g.ldd = I;
-    g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    if (with_down) {
-        g = gemm_base(a->status);
-        g.mode = 0; g.rows_static = T; g.N = H; g.K = I;
-        g.A = a->hidden_shared; g.lda = I; g.B = a->w_shared_down; g.ldb = I; g.D = a->y_shared; g.ldd = H;
-        MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    }
+    for (int mi = 0; mi < n_macro; ++mi) {
+        const int m = n_macro - 1 - mi;
+        const int lo = m * MB, hi = (lo + MB < C) ? lo + MB : C;
+        // only macrobatch 0 (the one that is always populated) is cut into overlap windows
+        const int chunk = m == 0 ? chunk_rows_for(MB, a->minibatch_size) : MB;
+        const int nchunks = (hi - lo + chunk - 1) / chunk;
+        const FwdView v = fwd_view(lo, H, I, a->x_routed, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, a->gate_bf16, a->up_bf16, a->gate_fp8,
+                                   a->gate_sc, a->up_fp8, a->up_sc, a->hidden_fp8, a->hidden_sc, a->hidden_fp8_t, a->hidden_sc_t);
+        void* y_r = with_down ? rebase(a->y_routed, lo, 2ull * H) : nullptr;
 
-    // routed experts (MXFP8), window by window behind the dispatch
-    for (int c = 0; c < nchunks; ++c) {
-        const int r0 = c * chunk, r1 = r0 + chunk < MB ? r0 + chunk : MB;
-        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
-        mokb_gemm_fp8_args f = fp8_base(a->status);
-        f.mode = 1; f.rows_static = MB; f.row_begin = r0; f.row_end = r1;
-        f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
-        f.A = a->x_fp8; f.A_sc = a->x_sc; f.B = a->w_routed_gate; f.B_sc = a->w_routed_gate_sc; f.B2 = a->w_routed_up; f.B2_sc = a->w_routed_up_sc;
-        f.D = a->gate_bf16; f.D2 = a->up_bf16; f.ldd = I;
-        MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-        MOKB_TRY(swiglu_fwd_quant_impl(a->gate_bf16, a->up_bf16, MB, I, s.n_rows, r0, r1, a->has_swiglu_limit, a->swiglu_limit, a->gate_fp8,
-                                       a->gate_sc, a->up_fp8, a->up_sc, a->hidden_fp8, a->hidden_sc, a->hidden_fp8_t, a->hidden_sc_t, stream));
-        if (!with_down) continue;
-        f = fp8_base(a->status);
-        f.mode = 0; f.rows_static = MB; f.row_begin = r0; f.row_end = r1;
-        f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = H; f.K = I;
-        f.A = a->hidden_fp8; f.A_sc = a->hidden_sc; f.B = a->w_routed_down; f.B_sc = a->w_routed_down_sc; f.D = a->y_routed; f.ldd = H;
-        MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-        if (overlap) {
-            MOKB_CUDA(cudaEventRecord(as->ev_out[c], stream));
-            MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[c], 0));
+        if (overlap) {     // everything enqueued so far (previous macrobatch included) precedes this one's side work
+            MOKB_CUDA(cudaEventRecord(as->fork, stream));
+            MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
+            if (with_down) MOKB_CUDA(cudaStreamWaitEvent(s_out, as->fork, 0));
         }
-        MOKB_TRY(combine_rows_impl(a->y_routed, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, r0, r1, H,
-                                   nullptr, nullptr, comm_blocks, s_out));
-    }
-    if (overlap && with_down) {
-        MOKB_CUDA(cudaEventRecord(as->join2, s_out));
-        MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
+        // dispatch + quantise (row-wise for the GEMM, token-wise for the weight gradients), window by window
+        for (int c = 0; c < nchunks; ++c) {
+            const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
+            MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
+                                        v.x_routed, nullptr, nullptr, comm_blocks, s_in));
+            MOKB_TRY(quantize_impl(v.x_routed, 1, MB, H, s.n_rows, r0, r1, v.x_fp8, v.x_sc, v.x_fp8_t, v.x_sc_t, s_in));
+            if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+        }
+
+        if (!shared_done) {
+            // shared expert (BF16): gate/up + SwiGLU in one pass, then down (independent of the dispatch)
+            shared_done = true;
+            mokb_gemm_args g = gemm_base(a->status);
+            g.mode = 1; g.rows_static = T; g.N = I; g.K = H;
+            g.A = x_local; g.lda = H; g.B = a->w_shared_gate; g.B2 = a->w_shared_up; g.ldb = H;
+            g.D = a->gate_shared; g.D2 = a->up_shared; g.D3 = a->hidden_shared; g.ldd = I;
+            g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
+            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+            if (with_down) {
+                g = gemm_base(a->status);
+                g.mode = 0; g.rows_static = T; g.N = H; g.K = I;
+                g.A = a->hidden_shared; g.lda = I; g.B = a->w_shared_down; g.ldb = I; g.D = a->y_shared; g.ldd = H;
+                MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+            }
+        }
+
+        // routed experts (MXFP8), window by window behind the dispatch
+        for (int c = 0; c < nchunks; ++c) {
+            const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
+            if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
+            MOKB_TRY(gate_up_swiglu(v, wgu, s, r0, r1, hi, MB, E_l, H, I, a->has_swiglu_limit, a->swiglu_limit, a->status, stream));
+            if (!with_down) continue;
+            mokb_gemm_fp8_args f = fp8_base(a->status);
+            f.mode = 0; f.rows_static = hi; f.row_begin = r0; f.row_end = r1;
+            f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = H; f.K = I;
+            f.A = v.hidden_fp8; f.A_sc = v.hidden_sc; f.B = a->w_routed_down; f.B_sc = a->w_routed_down_sc; f.D = y_r; f.ldd = H;
+            MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
+            // combine: push the window's rows back to slot t*K+k of their home ranks
+            if (overlap) {
+                MOKB_CUDA(cudaEventRecord(as->ev_out[c], stream));
+                MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[c], 0));
+            }
+            MOKB_TRY(combine_rows_impl(y_r, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, H,
+                                       nullptr, nullptr, comm_blocks, s_out));
+        }
+        if (overlap && with_down) {    // the next macrobatch overwrites y_routed: the combine must be done with it
+            MOKB_CUDA(cudaEventRecord(as->join2, s_out));
+            MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
+        }
     }
     return MOKB_OK;
 }
@@ -132,7 +210,13 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
     MOKB_REQUIRE(a->d_y_routed && a->d_y_fp8_t && a->d_y_sc_t && a->d_gate_fp8_t && a->d_gate_sc_t && a->d_up_fp8_t && a->d_up_sc_t && a->partials,
                  "bwd_mxfp8: null work buffer");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
-    const Scratch s = carve(a->scratch, a->schedule_capacity, E_l, MB);
+    const int C = a->schedule_capacity;
+    const int n_macro = macrobatches(C, MB);
+    if (n_macro > 1)
+        MOKB_REQUIRE(a->w_routed_gate && a->w_routed_gate_sc && a->w_routed_up && a->w_routed_up_sc && a->x_routed && a->x_fp8 && a->x_sc &&
+                     a->gate_bf16 && a->up_bf16 && a->hidden_fp8 && a->hidden_sc,
+                     "bwd_mxfp8: schedule_capacity > macrobatch_size needs the forward weights and the replay work buffers");
+    const Scratch s = carve(a->scratch, C, E_l, MB);
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
@@ -140,71 +224,113 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
     const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
     const int lim = a->has_swiglu_limit;
     const float limv = a->swiglu_limit;
+    const GateUpWeights wgu{a->w_routed_gate, a->w_routed_gate_sc, a->w_routed_up, a->w_routed_up_sc};
 
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, a->schedule_capacity, MB, T, true, s, a->status, stream));
-    if (overlap) {
-        MOKB_CUDA(cudaEventRecord(as->fork, stream));
-        MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
-    }
-    MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB, a->topk, H,
-                                a->d_y_routed, a->router_weight_ptrs_host, s.w_row, comm_blocks, s_in));
-    MOKB_TRY(quantize_impl(a->d_y_routed, 1, MB, H, s.n_rows, 0, MB, a->d_y_fp8, a->d_y_sc, a->d_y_fp8_t, a->d_y_sc_t, s_in));
-    if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, s, a->status, stream));
     const void* d_y_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->d_y_ptrs_host[a->ep_rank]));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
 
-    // ---- shared expert (BF16)
-    mokb_gemm_args g = gemm_base(a->status);
-    g.mode = 2; g.rows_static = T; g.N = I; g.K = H;
-    g.A = d_y_local; g.lda = H; g.B = a->w_shared_down; g.ldb = I; g.D = a->d_hidden_shared; g.ldd = I;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    MOKB_TRY(mokb_swiglu_bwd(a->gate_shared, a->up_shared, a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, nullptr,
-                             nullptr, T, I, lim, limv, stream));
-    g = gemm_base(a->status);
-    g.mode = 2; g.rows_static = T; g.N = H; g.K = I;
-    g.A = a->d_gate_shared; g.B = a->w_shared_gate; g.A2 = a->d_up_shared; g.B2 = a->w_shared_up; g.lda = I; g.ldb = H;
-    g.D = a->d_x_shared; g.ldd = H;
-    MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-    auto wgrad_bf16 = [&](const void* A, int M, const void* B, int N, void* D) -> int {
-        mokb_gemm_args w = gemm_base(a->status);
-        w.mode = 3; w.rows_static = T; w.G = 1; w.M = M; w.N = N; w.group_offsets = s.shared_offsets;
-        w.A = A; w.lda = M; w.B = B; w.ldb = N; w.D = D; w.ldd = N;
-        return mokb_grouped_gemm_bf16(&w, stream);
-    };
-    MOKB_TRY(wgrad_bf16(d_y_local, H, a->hidden_shared, I, a->d_w_shared_down));
-    MOKB_TRY(wgrad_bf16(a->d_gate_shared, I, x_local, H, a->d_w_shared_gate));
-    MOKB_TRY(wgrad_bf16(a->d_up_shared, I, x_local, H, a->d_w_shared_up));
+    for (int m = 0; m < n_macro; ++m) {
+        const int lo = m * MB, hi = (lo + MB < C) ? lo + MB : C;
+        // the context (macrobatch 0: as saved; later ones: rebuilt below) and the work buffers, addressed by schedule row
+        const FwdView v = fwd_view(lo, H, I, a->x_routed, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, a->gate_bf16, a->up_bf16, a->gate_fp8,
+                                   a->gate_sc, a->up_fp8, a->up_sc, a->hidden_fp8, a->hidden_sc, a->hidden_fp8_t, a->hidden_sc_t);
+        void* d_y_r = rebase(a->d_y_routed, lo, 2ull * H);
+        void* d_y_fp8 = rebase(a->d_y_fp8, lo, 1ull * H);
+        void* d_y_sc = rebase_scales(a->d_y_sc, lo, H);
+        void* d_y_fp8_t = rebase_t(a->d_y_fp8_t, lo);
+        void* d_y_sc_t = rebase_scales_t(a->d_y_sc_t, lo);
+        void* d_hidden_r = rebase(a->d_hidden_routed, lo, 2ull * I);
+        void* d_gate_fp8 = rebase(a->d_gate_fp8, lo, 1ull * I);
+        void* d_gate_sc = rebase_scales(a->d_gate_sc, lo, I);
+        void* d_gate_fp8_t = rebase_t(a->d_gate_fp8_t, lo);
+        void* d_gate_sc_t = rebase_scales_t(a->d_gate_sc_t, lo);
+        void* d_up_fp8 = rebase(a->d_up_fp8, lo, 1ull * I);
+        void* d_up_sc = rebase_scales(a->d_up_sc, lo, I);
+        void* d_up_fp8_t = rebase_t(a->d_up_fp8_t, lo);
+        void* d_up_sc_t = rebase_scales_t(a->d_up_sc_t, lo);
+        void* d_x_r = rebase(a->d_x_routed, lo, 2ull * H);
+        float* w_row = rebase(s.w_row, lo, 4);
+        float* d_w_row = rebase(s.d_w_row, lo, 4);
+        float* partials = rebase(static_cast<float*>(a->partials), lo, 4ull * (I / 128));
 
-    // ---- routed experts (MXFP8)
-    if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
-    mokb_gemm_fp8_args f = fp8_base(a->status);
-    f.mode = 0; f.rows_static = MB; f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
-    f.A = a->d_y_fp8; f.A_sc = a->d_y_sc; f.B = a->w_routed_down_t; f.B_sc = a->w_routed_down_t_sc; f.D = a->d_hidden_routed; f.ldd = I;
-    MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-    MOKB_TRY(swiglu_bwd_quant_impl(a->gate_fp8, a->gate_sc, a->up_fp8, a->up_sc, a->d_hidden_routed, MB, I, s.n_rows, 0, MB, lim, limv, s.w_row,
-                                   a->d_gate_fp8, a->d_gate_sc, a->d_gate_fp8_t, a->d_gate_sc_t, a->d_up_fp8, a->d_up_sc, a->d_up_fp8_t,
-                                   a->d_up_sc_t, static_cast<float*>(a->partials), s.d_w_row, stream));
-    f = fp8_base(a->status);
-    f.mode = 0; f.rows_static = MB; f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = H; f.K = I;
-    f.A = a->d_gate_fp8; f.A_sc = a->d_gate_sc; f.B = a->w_routed_gate_t; f.B_sc = a->w_routed_gate_t_sc;
-    f.A2 = a->d_up_fp8; f.A2_sc = a->d_up_sc; f.B2 = a->w_routed_up_t; f.B2_sc = a->w_routed_up_t_sc; f.D = a->d_x_routed; f.ldd = H;
-    MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-    if (overlap) {
-        MOKB_CUDA(cudaEventRecord(as->ev_out[0], stream));
-        MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[0], 0));
+        if (overlap) {     // the previous macrobatch's weight gradients still read the buffers the dispatches below overwrite
+            MOKB_CUDA(cudaEventRecord(as->fork, stream));
+            MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
+        }
+        if (m > 0) {       // replay: pull x again and quantise it both ways
+            MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
+                                        v.x_routed, nullptr, nullptr, comm_blocks, s_in));
+            MOKB_TRY(quantize_impl(v.x_routed, 1, MB, H, s.n_rows, lo, hi, v.x_fp8, v.x_sc, v.x_fp8_t, v.x_sc_t, s_in));
+        }
+        // reverse combine: pull d_y rows scaled by the route's router weight, quantise them both ways
+        MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
+                                    d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in));
+        MOKB_TRY(quantize_impl(d_y_r, 1, MB, H, s.n_rows, lo, hi, d_y_fp8, d_y_sc, d_y_fp8_t, d_y_sc_t, s_in));
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
+
+        if (m == 0) {
+            // ---- shared expert (BF16; overlaps the dispatch above)
+            mokb_gemm_args g = gemm_base(a->status);
+            g.mode = 2; g.rows_static = T; g.N = I; g.K = H;
+            g.A = d_y_local; g.lda = H; g.B = a->w_shared_down; g.ldb = I; g.D = a->d_hidden_shared; g.ldd = I;
+            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+            MOKB_TRY(mokb_swiglu_bwd(a->gate_shared, a->up_shared, a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, nullptr,
+                                     nullptr, T, I, lim, limv, stream));
+            g = gemm_base(a->status);
+            g.mode = 2; g.rows_static = T; g.N = H; g.K = I;
+            g.A = a->d_gate_shared; g.B = a->w_shared_gate; g.A2 = a->d_up_shared; g.B2 = a->w_shared_up; g.lda = I; g.ldb = H;
+            g.D = a->d_x_shared; g.ldd = H;
+            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+            auto wgrad_bf16 = [&](const void* A, int M, const void* B, int N, void* D) -> int {
+                mokb_gemm_args w = gemm_base(a->status);
+                w.mode = 3; w.rows_static = T; w.G = 1; w.M = M; w.N = N; w.group_offsets = s.shared_offsets;
+                w.A = A; w.lda = M; w.B = B; w.ldb = N; w.D = D; w.ldd = N;
+                return mokb_grouped_gemm_bf16(&w, stream);
+            };
+            MOKB_TRY(wgrad_bf16(d_y_local, H, a->hidden_shared, I, a->d_w_shared_down));
+            MOKB_TRY(wgrad_bf16(a->d_gate_shared, I, x_local, H, a->d_w_shared_gate));
+            MOKB_TRY(wgrad_bf16(a->d_up_shared, I, x_local, H, a->d_w_shared_up));
+        }
+
+        // ---- routed experts of this macrobatch (MXFP8)
+        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
+        if (m > 0)         // replay gate|up + SwiGLU + quantisation into the context buffers
+            MOKB_TRY(gate_up_swiglu(v, wgu, s, lo, hi, hi, MB, E_l, H, I, lim, limv, a->status, stream));
+        mokb_gemm_fp8_args f = fp8_base(a->status);
+        f.mode = 0; f.rows_static = hi; f.row_begin = lo; f.row_end = hi;
+        f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
+        f.A = d_y_fp8; f.A_sc = d_y_sc; f.B = a->w_routed_down_t; f.B_sc = a->w_routed_down_t_sc; f.D = d_hidden_r; f.ldd = I;
+        MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
+        MOKB_TRY(swiglu_bwd_quant_impl(v.gate_fp8, v.gate_sc, v.up_fp8, v.up_sc, d_hidden_r, MB, I, s.n_rows, lo, hi, lim, limv, w_row,
+                                       d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t, d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t,
+                                       partials, d_w_row, stream));
+        f = fp8_base(a->status);
+        f.mode = 0; f.rows_static = hi; f.row_begin = lo; f.row_end = hi;
+        f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = H; f.K = I;
+        f.A = d_gate_fp8; f.A_sc = d_gate_sc; f.B = a->w_routed_gate_t; f.B_sc = a->w_routed_gate_t_sc;
+        f.A2 = d_up_fp8; f.A2_sc = d_up_sc; f.B2 = a->w_routed_up_t; f.B2_sc = a->w_routed_up_t_sc; f.D = d_x_r; f.ldd = H;
+        MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
+        // reverse dispatch: push d_x rows and the per-route router-weight gradient home (overlaps the weight gradients)
+        if (overlap) {
+            MOKB_CUDA(cudaEventRecord(as->ev_out[0], stream));
+            MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[0], 0));
+        }
+        MOKB_TRY(combine_rows_impl(d_x_r, a->d_x_routed_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi,
+                                   H, d_w_row, a->d_router_weight_ptrs_host, comm_blocks, s_out));
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->join2, s_out));
+        const int32_t* offs = s.mb_offsets + static_cast<size_t>(m) * (E_l + 1);
+        auto wgrad_fp8 = [&](const void* A, const void* A_sc, int M, const void* B, const void* B_sc, int N, void* D) -> int {
+            mokb_gemm_fp8_args w = fp8_base(a->status);
+            w.mode = 2; w.rows_static = MB; w.t_first = lo; w.G = E_l; w.M = M; w.N = N; w.group_offsets = offs; w.accumulate = m > 0;
+            w.A = A; w.A_sc = A_sc; w.B = B; w.B_sc = B_sc; w.D = D; w.ldd = N;
+            return mokb_grouped_gemm_mxfp8(&w, stream);
+        };
+        // the token-wise tensors are passed as they lie in memory ([., MB], first token column = lo)
+        MOKB_TRY(wgrad_fp8(a->d_y_fp8_t, a->d_y_sc_t, H, a->hidden_fp8_t, a->hidden_sc_t, I, a->d_w_routed_down));
+        MOKB_TRY(wgrad_fp8(a->d_gate_fp8_t, a->d_gate_sc_t, I, a->x_fp8_t, a->x_sc_t, H, a->d_w_routed_gate));
+        MOKB_TRY(wgrad_fp8(a->d_up_fp8_t, a->d_up_sc_t, I, a->x_fp8_t, a->x_sc_t, H, a->d_w_routed_up));
+        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
     }
-    MOKB_TRY(combine_rows_impl(a->d_x_routed, a->d_x_routed_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, MB, 0, MB,
-                               H, s.d_w_row, a->d_router_weight_ptrs_host, comm_blocks, s_out));
-    if (overlap) MOKB_CUDA(cudaEventRecord(as->join2, s_out));
-    auto wgrad_fp8 = [&](const void* A, const void* A_sc, int M, const void* B, const void* B_sc, int N, void* D) -> int {
-        mokb_gemm_fp8_args w = fp8_base(a->status);
-        w.mode = 2; w.rows_static = MB; w.G = E_l; w.M = M; w.N = N; w.group_offsets = s.expert_offsets;
-        w.A = A; w.A_sc = A_sc; w.B = B; w.B_sc = B_sc; w.D = D; w.ldd = N;
-        return mokb_grouped_gemm_mxfp8(&w, stream);
-    };
-    MOKB_TRY(wgrad_fp8(a->d_y_fp8_t, a->d_y_sc_t, H, a->hidden_fp8_t, a->hidden_sc_t, I, a->d_w_routed_down));
-    MOKB_TRY(wgrad_fp8(a->d_gate_fp8_t, a->d_gate_sc_t, I, a->x_fp8_t, a->x_sc_t, H, a->d_w_routed_gate));
-    MOKB_TRY(wgrad_fp8(a->d_up_fp8_t, a->d_up_sc_t, I, a->x_fp8_t, a->x_sc_t, H, a->d_w_routed_up));
-    if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
     return MOKB_OK;
 }

@@ -139,20 +139,16 @@ __device__ __forceinline__ void load_tile_bf16(uint32_t* tile, const __nv_bfloat
     }
 }
 
-__device__ __forceinline__ int live_rows(const int32_t* num_rows, int64_t cap) {
-    if (!num_rows) return static_cast<int>(cap);
-    const int n = *num_rows;
-    return (n < 0 || n > cap) ? 0 : n;
-}
-
-// rows [begin, min(end, *num_rows)) of a tensor with `cap` rows; the grid's y index counts 128-row tiles from `begin`
+// Rows [begin, min(end, *num_rows)); the grid's y index counts 128-row tiles from `begin`.  Row numbers are those of the
+// caller's row space (the schedule's, for the layer): a buffer that holds only rows [first, first + M) of it is passed
+// with its pointers moved back by `first` rows, so begin/end may exceed the buffer's own row count M.
 struct RowWindow {
     const int32_t* num_rows;
     int begin, end;
 };
-__device__ __forceinline__ bool tile_in_window(const RowWindow& w, int64_t cap, int64_t* r0) {
+__device__ __forceinline__ bool tile_in_window(const RowWindow& w, int64_t* r0) {
     *r0 = static_cast<int64_t>(blockIdx.y) * TILE + w.begin;
-    const int live = min(live_rows(w.num_rows, cap), w.end);
+    const int live = w.num_rows ? min(max(*w.num_rows, 0), w.end) : w.end;
     return *r0 < live;
 }
 
@@ -165,7 +161,7 @@ __global__ void __launch_bounds__(256) quantize_kernel(const __nv_bfloat16* __re
     const int64_t e = blockIdx.z;
     const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
     int64_t r0;
-    if (!tile_in_window(win, M, &r0)) return;
+    if (!tile_in_window(win, &r0)) return;
     load_tile_bf16(tile, x + (e * M + r0) * N + c0, N);
     __syncthreads();
     if (q) quantize_tile_rows(tile, q, sc, e * M, r0, c0, N);
@@ -193,7 +189,7 @@ __global__ void __launch_bounds__(256) swiglu_fwd_quant_kernel(
     uint32_t *tg = sm, *tu = sm + TILE_WORDS, *th = sm + 2 * TILE_WORDS;
     const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
     int64_t r0;
-    if (!tile_in_window(win, rows_cap, &r0)) return;
+    if (!tile_in_window(win, &r0)) return;
     load_tile_bf16(tg, gate + r0 * I + c0, I);
     load_tile_bf16(tu, up + r0 * I + c0, I);
     __syncthreads();
@@ -236,7 +232,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_quant_kernel(
     __shared__ float row_part[TILE][2];
     const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
     int64_t r0;
-    if (!tile_in_window(win, rows_cap, &r0)) return;
+    if (!tile_in_window(win, &r0)) return;
     load_tile_bf16(tdh, d_hidden + r0 * I + c0, I);
     __syncthreads();
     // two threads per row, 64 columns each (two scale blocks of 32), columns in ascending order
@@ -290,9 +286,8 @@ __global__ void __launch_bounds__(256) swiglu_bwd_quant_kernel(
 }
 
 // row_grad[row] = sum over the column blocks of partials[row, :], in block order (fixed, reproducible)
-__global__ void row_sum_kernel(const float* __restrict__ partials, int nblk, RowWindow win, int64_t rows_cap,
-                               float* __restrict__ out) {
-    const int rows = min(live_rows(win.num_rows, rows_cap), win.end);
+__global__ void row_sum_kernel(const float* __restrict__ partials, int nblk, RowWindow win, float* __restrict__ out) {
+    const int rows = win.num_rows ? min(max(*win.num_rows, 0), win.end) : win.end;
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x + win.begin; row < rows;
          row += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         float s = 0.0f;
@@ -307,8 +302,8 @@ namespace {
 bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; }
 int check_window(const char* who, int row_begin, int* row_end, int64_t rows) {
     if (*row_end <= 0) *row_end = static_cast<int>(rows);
-    MOKB_REQUIRE(row_begin >= 0 && row_begin % 128 == 0 && *row_end % 128 == 0 && row_begin <= *row_end && *row_end <= rows,
-                 "%s: bad row window [%d, %d) of %lld", who, row_begin, *row_end, static_cast<long long>(rows));
+    MOKB_REQUIRE(row_begin >= 0 && row_begin % 128 == 0 && *row_end % 128 == 0 && row_begin <= *row_end && *row_end - row_begin <= rows,
+                 "%s: bad row window [%d, %d) for %lld rows", who, row_begin, *row_end, static_cast<long long>(rows));
     return MOKB_OK;
 }
 }  // namespace
@@ -381,7 +376,7 @@ int swiglu_bwd_quant_impl(const void* gate_q, const void* gate_sc, const void* u
     note_launch();
     if (row_grad) {
         const int blocks = min(sm_count() * 4, (row_end - row_begin + 255) / 256);
-        row_sum_kernel<<<blocks, 256, 0, stream>>>(partials, static_cast<int>(I / 128), win, rows_cap, row_grad);
+        row_sum_kernel<<<blocks, 256, 0, stream>>>(partials, static_cast<int>(I / 128), win, row_grad);
         MOKB_CUDA(cudaGetLastError());
         note_launch();
     }

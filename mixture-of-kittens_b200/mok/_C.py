@@ -78,7 +78,8 @@ class GemmFp8Args(ctypes.Structure):
     _fields_ = [("mode", c_int), ("rows_static", c_int), ("row_begin", c_int), ("row_end", c_int), ("num_rows", c_vp),
                 ("group_of_block", c_vp), ("group_offsets", c_vp), ("G", c_int), ("M", c_int), ("N", c_int), ("K", c_int),
                 ("A", c_vp), ("A_sc", c_vp), ("B", c_vp), ("B_sc", c_vp), ("A2", c_vp), ("A2_sc", c_vp), ("B2", c_vp),
-                ("B2_sc", c_vp), ("D", c_vp), ("D2", c_vp), ("ldd", c_int), ("status", c_vp)]
+                ("B2_sc", c_vp), ("D", c_vp), ("D2", c_vp), ("ldd", c_int), ("t_first", c_int), ("accumulate", c_int),
+                ("status", c_vp)]
 
 
 def _sig(name, restype, *argtypes):
@@ -417,7 +418,8 @@ def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None
 
 
 def grouped_gemm_mxfp8(mode, A, A_sc, B, B_sc, D, *, rows=None, num_rows=None, group_of_block=None, group_offsets=None,
-                       G=1, M=0, N=0, K=0, A2=None, A2_sc=None, B2=None, B2_sc=None, D2=None, ldd=None, row_begin=0, row_end=0):
+                       G=1, M=0, N=0, K=0, A2=None, A2_sc=None, B2=None, B2_sc=None, D2=None, ldd=None, row_begin=0, row_end=0,
+                       t_first=0, accumulate=False):
     g = GemmFp8Args()
     g.mode = mode
     g.rows_static = (A.shape[0] if mode != 2 else A.shape[1]) if rows is None else rows
@@ -428,6 +430,7 @@ def grouped_gemm_mxfp8(mode, A, A_sc, B, B_sc, D, *, rows=None, num_rows=None, g
     g.A2, g.A2_sc, g.B2, g.B2_sc = _p(A2), _p(A2_sc), _p(B2), _p(B2_sc)
     g.D, g.D2 = _p(D), _p(D2)
     g.ldd = D.shape[-1] if ldd is None else ldd
+    g.t_first, g.accumulate = t_first, int(bool(accumulate))
     g.status = _p(status_tensor(A.device))
     _ck(lib.mokb_grouped_gemm_mxfp8(ctypes.byref(g), _stream()))
 

@@ -42,6 +42,8 @@ class BwdMxfp8Args(ctypes.Structure):
             "d_hidden_shared", "d_hidden_routed", "d_y_fp8", "d_y_sc",
             "d_w_shared_gate", "d_w_routed_gate", "d_w_shared_up", "d_w_routed_up", "d_w_shared_down", "d_w_routed_down",
             "d_y_routed", "d_y_fp8_t", "d_y_sc_t", "d_gate_fp8_t", "d_gate_sc_t", "d_up_fp8_t", "d_up_sc_t", "partials",
+            "w_routed_gate", "w_routed_gate_sc", "w_routed_up", "w_routed_up_sc",
+            "x_routed", "x_fp8", "x_sc", "gate_bf16", "up_bf16", "hidden_fp8", "hidden_sc",
             "scratch", "status")])
 
 
@@ -52,11 +54,11 @@ lib.mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8.argtypes = [ctypes.POINTER(BwdMxf
 lib.mokb_struct_sizes_mxfp8.restype = c_int
 lib.mokb_struct_sizes_mxfp8.argtypes = [ctypes.POINTER(c_int), c_int]
 
-_sizes = (c_int * 2)()
-lib.mokb_struct_sizes_mxfp8(_sizes, 2)
-if tuple(_sizes) != (ctypes.sizeof(FwdMxfp8Args), ctypes.sizeof(BwdMxfp8Args)):
-    raise ImportError(f"MXFP8 struct layout mismatch: library {tuple(_sizes)}, binding "
-                      f"{(ctypes.sizeof(FwdMxfp8Args), ctypes.sizeof(BwdMxfp8Args))}")
+_sizes = (c_int * 3)()
+lib.mokb_struct_sizes_mxfp8(_sizes, 3)
+_mine = (ctypes.sizeof(FwdMxfp8Args), ctypes.sizeof(BwdMxfp8Args), ctypes.sizeof(_C.GemmFp8Args))
+if tuple(_sizes) != _mine:
+    raise ImportError(f"MXFP8 struct layout mismatch: library {tuple(_sizes)}, binding {_mine}")
 
 EXPORTED = ["mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8", "mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8",
             "mokb_struct_sizes_mxfp8"]
@@ -178,6 +180,11 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
             torch.empty(MB, I // 128, dtype=torch.float32, device=dev)]
     (a.d_y_routed, a.d_y_fp8_t, a.d_y_sc_t, a.d_gate_fp8_t, a.d_gate_sc_t, a.d_up_fp8_t, a.d_up_sc_t,
      a.partials) = map(_p, work)
+    if a.schedule_capacity > MB:      # later macrobatches are replayed: forward weights and the forward's work buffers
+        replay = [w_routed_gate, w_routed_gate_sc, w_routed_up, w_routed_up_sc, torch.empty(MB, H, **bf), *_q(MB, H, dev),
+                  torch.empty(MB, I, **bf), torch.empty(MB, I, **bf), *_q(MB, I, dev)]
+        (a.w_routed_gate, a.w_routed_gate_sc, a.w_routed_up, a.w_routed_up_sc, a.x_routed, a.x_fp8, a.x_sc, a.gate_bf16,
+         a.up_bf16, a.hidden_fp8, a.hidden_sc) = map(_p, replay)
     _ck(lib.mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(ctypes.byref(a), _stream()))
     return (d_x_shared, d_x_routed, d_gate_shared, d_gate_fp8, d_gate_sc, d_up_shared, d_up_fp8, d_up_sc,
             d_hidden_shared, d_hidden_routed, d_y_fp8, d_y_sc, d_w_shared_gate, d_w_routed_gate, d_w_shared_up,

@@ -130,18 +130,3 @@ def test_several_macrobatches_with_replay_match_the_single_macrobatch_result(MB,
     # bit-reproducible across runs as well
     _, out_b, _, _, grads_b, _ = run_layer(ranks[0], 4, MB=MB, mb=mb)
     assert torch.equal(out, out_b) and all(torch.equal(a, b) for a, b in zip(grads, grads_b))
-
-
-def test_mxfp8_macrobatch_too_small_is_reported_not_fatal():
-    # the MXFP8 layer handles one macrobatch; more rows than that are reported through the status word
-    from mok import _C, functional as F, ops
-    ranks = O.make_inputs(R=1, T=512, H=256, I=256, E=4, K=2, seed=3, routing="gaussian")
-    group = init_single_rank_group()
-    inp = to_dev(ranks[0])
-    cfg = F.MoKConfig(minibatch_size=256, macrobatch_size=512)
-    ws = F.get_workspace(cfg, group, device=torch.device("cuda", 0), num_local_tokens=512, hidden_size=256, topk=2)
-    sched = F.build_schedule(ws, cfg, inp.top_experts, num_local_experts=4)
-    q = [ops.mxfp8_quantize(w, True, False)[:2] for w in (inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down)]
-    F.forward(cfg, ws, sched, inp.x, inp.router_weights, inp.w_shared_gate, inp.w_shared_up, inp.w_shared_down, *q)
-    torch.cuda.synchronize()
-    assert _C.check_status() == _C.ST_MACROBATCH_OVERFLOW

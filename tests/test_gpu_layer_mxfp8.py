@@ -14,13 +14,13 @@ GRAD_KEYS = ("d_x", "d_router_weights", "d_w_routed_gate", "d_w_routed_up", "d_w
              "d_w_shared_gate", "d_w_shared_up", "d_w_shared_down")
 
 
-def run_mxfp8(inp_cpu, E_l, *, limit=None, recompute=False):
+def run_mxfp8(inp_cpu, E_l, *, limit=None, recompute=False, MB=None, mb=256):
     from mok import _C, functional as F, ops
     group = init_single_rank_group()
     inp = to_dev(inp_cpu)
     T, H = inp.x.shape
     K = inp.top_experts.shape[1]
-    cfg = F.MoKConfig(minibatch_size=256, macrobatch_size=T * K * 2)
+    cfg = F.MoKConfig(minibatch_size=mb, macrobatch_size=MB or T * K * 2)
     ws = F.get_workspace(cfg, group, device=torch.device("cuda", 0), num_local_tokens=T, hidden_size=H, topk=K)
     sched = F.build_schedule(ws, cfg, inp.top_experts, num_local_experts=E_l)
     gq, gs, gtq, gts = ops.mxfp8_quantize(inp.w_routed_gate, True, True)
@@ -91,3 +91,36 @@ def test_mxfp8_recompute_is_bit_identical_and_deterministic():
     assert torch.equal(out1, out2)
     for a, b in zip(g1, g2):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("MB,mb", [(512, 256), (768, 256), (1024, 512)])
+def test_mxfp8_several_macrobatches_with_replay_match_the_single_macrobatch_result(MB, mb):
+    # capacity 2048 rows, ~1300-1500 of them used: 2-3 populated macrobatches and at least one empty one.
+    # Macrobatch boundaries are multiples of 256 rows, so no 32-token scale block straddles one: everything
+    # except the accumulation order of the routed weight gradients is the same arithmetic as in one macrobatch.
+    ranks = O.make_inputs(R=1, T=512, H=256, I=256, E=4, K=2, seed=3, routing="gaussian")
+    ranks[0].grad_output = (ranks[0].grad_output.float() * 256 ** -0.5).to(torch.bfloat16)
+    s1, out1, ctx1, _, g1, ws1 = run_mxfp8(ranks[0], 4)
+    N = int(s1.num_tokens.item())
+    assert N > MB
+    combine1 = ws1.combine_buffer.clone()
+    sm, outm, ctxm, ctxm2, gm, wsm = run_mxfp8(ranks[0], 4, MB=MB, mb=mb, recompute=True)
+    assert torch.equal(out1, outm)
+    assert torch.equal(combine1, wsm.combine_buffer)
+    named = dict(zip(GRAD_KEYS, zip(g1, gm)))
+    for k in ("d_x", "d_router_weights", "d_w_shared_gate", "d_w_shared_up", "d_w_shared_down"):
+        assert torch.equal(*named[k]), k
+    for k in ("d_w_routed_gate", "d_w_routed_up", "d_w_routed_down"):       # bf16 accumulation across macrobatches
+        a, b = named[k]
+        assert_close(k, a.cpu(), b, (0.02, 8e-3))
+    # recompute rebuilds macrobatch 0, which is what the forward saved (the backward has since replayed later ones)
+    for pair_single, pair_re, transposed in ((ctx1.x_routed, ctxm2.x_routed, True), (ctx1.gate_routed, ctxm2.gate_routed, False),
+                                             (ctx1.up_routed, ctxm2.up_routed, False), (ctx1.hidden_routed, ctxm2.hidden_routed, True)):
+        a, b = pair_single[0].view(torch.uint8), pair_re[0].view(torch.uint8)
+        if transposed:
+            assert torch.equal(a[:, :MB], b[:, :MB])
+        else:
+            assert torch.equal(a[:MB], b[:MB])
+    # bit-reproducible across runs
+    _, outb, _, _, gb, _ = run_mxfp8(ranks[0], 4, MB=MB, mb=mb)
+    assert torch.equal(outm, outb) and all(torch.equal(a, b) for a, b in zip(gm, gb))
