@@ -312,6 +312,7 @@ def main():
     ap.add_argument("--no-mxfp8", action="store_true", help="skip the MXFP8 leg (reported under the key \"mxfp8\")")
     ap.add_argument("--no-torch-baseline", action="store_true",
                     help="skip the stock-PyTorch all-to-all + grouped_mm baseline (reported under \"torch_all_to_all\")")
+    ap.add_argument("--trace", default="", help="write the launch timeline of one BF16 and one MXFP8 step of rank 0 to this file")
     ap.add_argument("--kernel-only", action="store_true", help="time only the dominant GEMM (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if not args.kernel_only else args.warmup
@@ -428,6 +429,14 @@ def main():
         fwd_ms.append(ev[0].elapsed_time(ev[1]))
         bwd_ms.append(ev[1].elapsed_time(ev[2]))
 
+    trace_lines = []
+    if args.trace:
+        torch.cuda.synchronize()
+        dist.barrier()
+        _C.trace_begin()
+        step(x_d, te_d, rw_d, gy_d)
+        trace_lines += [("bf16",) + rec for rec in _C.trace_end()]
+
     # ---- end to end: inputs start in pinned host memory, result checksums come back to the host
     x_e, gy_e, te_e, rw_e = (torch.empty_like(t, device=device) for t in (x_h, gy_h, te_h, rw_h))
     res_h = torch.empty(2, dtype=torch.float32).pin_memory()
@@ -510,6 +519,12 @@ def main():
             mx_f.append(ev[0].elapsed_time(ev[1]))
             mx_b.append(ev[1].elapsed_time(ev[2]))
         assert _C.check_status() == 0, "device status word set during the MXFP8 steps"
+        if args.trace:
+            torch.cuda.synchronize()
+            dist.barrier()
+            _C.trace_begin()
+            step_mx()
+            trace_lines += [("mxfp8",) + rec for rec in _C.trace_end()]
         mx = {"value": T * world / (mx_ms / 1000.0), "unit": "tokens/s", "ms_per_step": mx_ms,
               "tflops_per_gpu": layer_flops(T, K, H, I) / (mx_ms / 1000.0) / 1e12,
               "fwd_ms": statistics.median(mx_f), "bwd_ms": statistics.median(mx_b),
@@ -536,6 +551,12 @@ def main():
         except Exception as e:      # a library baseline must not take the benchmark down
             tb = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
         torch.cuda.empty_cache()
+
+    if rank == 0 and args.trace:
+        with open(args.trace, "w") as f:
+            f.write("# leg tag first_row stream begin_ms end_ms\n")
+            for rec in trace_lines:
+                f.write(" ".join(str(v) for v in rec) + "\n")
 
     if rank == 0:
         tokens = T * world

@@ -54,6 +54,14 @@ int mokb_sm_count(void);
 int mokb_struct_sizes(int* out, int n);
 /* Number of kernels this library has launched in this process (all threads). */
 unsigned long long mokb_launch_count(void);
+/* Launch timeline, a diagnostic with no counterpart in the reference (its benchmarks time whole passes,
+ * benchmarks/utils.py:66-110).  After mokb_trace_begin(stream) every launcher of this library brackets what it
+ * enqueues with two timing events (up to 8192 launches; one host thread).  mokb_trace_end synchronises the
+ * device, stops recording and writes one line per launcher call, "tag arg stream_no begin_ms end_ms" with times
+ * relative to the begin call and streams numbered in order of first use; it returns the number of bytes the
+ * full text needs (write again with a larger buffer if that exceeds cap), or -1 on a CUDA error. */
+int mokb_trace_begin(void* stream);
+long long mokb_trace_end(char* out, size_t cap);
 
 /* ---- route all-gather: replaces `_C.all_gather_top_experts`
  * (csrc/utils.cuh:191-249).  Copies this rank's [numel] int32 routes into slot

@@ -171,6 +171,7 @@ extern "C" int mokb_set_barrier_timeout_ms(int ms) {
 
 extern "C" int mokb_all_gather_top_experts(const int32_t* top_experts, const uint64_t* gather_buffer_ptrs_host,
                                            int ep_size, int rank, int64_t numel, void* stream) {
+    TraceScope trace(static_cast<cudaStream_t>(stream), "all_gather_top_experts");
     MOKB_REQUIRE(top_experts != nullptr, "all_gather_top_experts: null input");
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP && rank >= 0 && rank < ep_size, "all_gather_top_experts: bad ep_size/rank");
     MOKB_REQUIRE(numel > 0 && numel % 4 == 0, "all_gather_top_experts: numel must be a positive multiple of 4");
@@ -190,6 +191,7 @@ extern "C" int mokb_all_gather_top_experts(const int32_t* top_experts, const uin
 
 extern "C" int mokb_barrier_all(const uint64_t* barrier_ptrs_host, int ep_size, int rank, int32_t* target,
                                 int32_t* status, void* stream) {
+    TraceScope trace(static_cast<cudaStream_t>(stream), "barrier_all");
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP && rank >= 0 && rank < ep_size, "barrier_all: bad ep_size/rank");
     MOKB_REQUIRE(target && status, "barrier_all: null pointer");
     PeerPtrs peers;
@@ -211,6 +213,7 @@ int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t
                        const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                        int row_divisor, int64_t hidden, void* dst, const uint64_t* row_scale_ptrs_host,
                        float* row_scale_out, int blocks, cudaStream_t s) {
+    TraceScope trace(s, row_scale_ptrs_host ? "dispatch_scaled" : "dispatch", row_begin);
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "dispatch_rows: bad ep_size");
     MOKB_REQUIRE(peer_rank && peer_token_idx && dst, "dispatch_rows: null pointer");
     MOKB_REQUIRE(max_rows >= 0 && row_divisor >= 1 && hidden > 0 && hidden % 8 == 0, "dispatch_rows: bad sizes");
@@ -242,6 +245,7 @@ int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t
 int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_size, const int32_t* peer_rank,
                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                       int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s) {
+    TraceScope trace(s, "combine", row_begin);
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "combine_rows: bad ep_size");
     MOKB_REQUIRE(src && peer_rank && peer_token_idx, "combine_rows: null pointer");
     MOKB_REQUIRE(max_rows >= 0 && hidden > 0 && hidden % 8 == 0, "combine_rows: bad sizes");

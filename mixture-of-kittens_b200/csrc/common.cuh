@@ -32,6 +32,16 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
     do { int _r = (expr); if (_r != MOKB_OK) return _r; } while (0)
 
 int sm_count();
+// Launch timeline (diagnostic, off unless mokb_trace_begin was called): an object of this class in a launcher
+// brackets everything the launcher enqueues on `stream` with two timing events.
+class TraceScope {
+public:
+    TraceScope(cudaStream_t stream, const char* tag, int arg = 0);
+    ~TraceScope();
+private:
+    int slot_;
+    cudaStream_t stream_;
+};
 void note_launch(int n = 1);   // counts kernels launched by this library (reported by the benchmark)
 
 // 2-D bf16/u8 tensor map with 128-byte swizzle: `inner` contiguous elements,

@@ -190,6 +190,7 @@ extern "C" int mokb_swiglu_fwd(const void* gate, const void* up, void* hidden, c
 extern "C" int mokb_swiglu_bwd(const void* gate, const void* up, const void* d_hidden, void* d_gate, void* d_up,
                                const float* row_scale, float* row_grad_out, const int32_t* num_rows,
                                int64_t max_rows, int64_t cols, int has_limit, float limit, void* stream) {
+    TraceScope trace(static_cast<cudaStream_t>(stream), "swiglu_bwd");
     MOKB_REQUIRE(gate && up && d_hidden && d_gate && d_up, "swiglu_bwd: null pointer");
     MOKB_REQUIRE(max_rows >= 0 && cols > 0 && cols % 8 == 0, "swiglu_bwd: bad sizes");
     if (max_rows == 0) return MOKB_OK;
@@ -205,6 +206,7 @@ extern "C" int mokb_swiglu_bwd(const void* gate, const void* up, const void* d_h
 
 extern "C" int mokb_fwd_epilogue(const void* y_shared, const void* combine_buffer, const float* topk_weights,
                                  void* output, int64_t num_local_tokens, int64_t hidden, int topk, void* stream) {
+    TraceScope trace(static_cast<cudaStream_t>(stream), "fwd_epilogue");
     MOKB_REQUIRE(y_shared && combine_buffer && topk_weights && output, "fwd_epilogue: null pointer");
     MOKB_REQUIRE(num_local_tokens > 0 && hidden > 0 && hidden % 8 == 0 && topk > 0 && topk <= 255, "fwd_epilogue: bad sizes");
     const int vec = static_cast<int>(hidden / 8);
@@ -218,6 +220,7 @@ extern "C" int mokb_fwd_epilogue(const void* y_shared, const void* combine_buffe
 
 extern "C" int mokb_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* d_x,
                                  int64_t num_local_tokens, int64_t hidden, int topk, void* stream) {
+    TraceScope trace(static_cast<cudaStream_t>(stream), "bwd_epilogue");
     MOKB_REQUIRE(d_x_shared && d_x_routed_buffer && d_x, "bwd_epilogue: null pointer");
     MOKB_REQUIRE(num_local_tokens > 0 && hidden > 0 && hidden % 8 == 0 && topk > 0 && topk <= 255, "bwd_epilogue: bad sizes");
     const int vec = static_cast<int>(hidden / 8);

@@ -473,6 +473,8 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     MOKB_REQUIRE(g != nullptr, "grouped_gemm: null args");
     MOKB_REQUIRE(g->mode >= 0 && g->mode <= 3, "grouped_gemm: unknown mode %d", g->mode);
+    static const char* const kTags[4] = {"gemm_bf16_nt", "gemm_bf16_gate_up_swiglu", "gemm_bf16_nn", "gemm_bf16_wgrad"};
+    TraceScope trace(stream, kTags[g->mode], g->row_begin);
     MOKB_REQUIRE(g->A && g->B && g->D && g->status, "grouped_gemm: null pointer");
     MOKB_REQUIRE(g->G >= 1, "grouped_gemm: G must be >= 1");
     MOKB_REQUIRE(g->rows_static >= 0 && g->rows_static % 128 == 0, "grouped_gemm: rows must be a multiple of 128");

@@ -397,6 +397,8 @@ using namespace mokb;
 extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     MOKB_REQUIRE(g != nullptr, "grouped_gemm_mxfp8: null args");
+    static const char* const kTags[3] = {"gemm_mxfp8_nt", "gemm_mxfp8_gate_up", "gemm_mxfp8_wgrad"};
+    TraceScope trace(stream, kTags[g->mode >= 0 && g->mode <= 2 ? g->mode : 0], g->row_begin);
     MOKB_REQUIRE(g->mode >= 0 && g->mode <= 2, "grouped_gemm_mxfp8: unknown mode %d", g->mode);
     MOKB_REQUIRE(g->A && g->A_sc && g->B && g->B_sc && g->D && g->status, "grouped_gemm_mxfp8: null pointer");
     MOKB_REQUIRE(g->G >= 1 && g->ldd % 8 == 0, "grouped_gemm_mxfp8: bad G or ldd");

@@ -90,6 +90,72 @@ extern "C" const char* mokb_last_error(void) { return mokb::g_error; }
 
 extern "C" int mokb_sm_count(void) { return mokb::sm_count(); }
 
+// ---------------------------------------------------------------- launch timeline
+namespace mokb {
+namespace {
+struct TraceRec {
+    cudaEvent_t begin, end;
+    const char* tag;
+    int arg;
+    cudaStream_t stream;
+};
+constexpr int kTraceMax = 8192;
+TraceRec g_trace[kTraceMax];
+int g_trace_n = 0;
+bool g_trace_on = false;
+cudaEvent_t g_trace_t0 = nullptr;
+}  // namespace
+
+TraceScope::TraceScope(cudaStream_t stream, const char* tag, int arg) : slot_(-1), stream_(stream) {
+    if (!g_trace_on || g_trace_n >= kTraceMax) return;
+    TraceRec& r = g_trace[g_trace_n];
+    if (!r.begin && (cudaEventCreate(&r.begin) != cudaSuccess || cudaEventCreate(&r.end) != cudaSuccess)) return;
+    r.tag = tag;
+    r.arg = arg;
+    r.stream = stream;
+    if (cudaEventRecord(r.begin, stream) != cudaSuccess) return;
+    slot_ = g_trace_n++;
+}
+TraceScope::~TraceScope() {
+    if (slot_ >= 0) cudaEventRecord(g_trace[slot_].end, stream_);
+}
+}  // namespace mokb
+
+extern "C" int mokb_trace_begin(void* stream) {
+    using namespace mokb;
+    if (!g_trace_t0) MOKB_CUDA(cudaEventCreate(&g_trace_t0));
+    g_trace_n = 0;
+    MOKB_CUDA(cudaEventRecord(g_trace_t0, static_cast<cudaStream_t>(stream)));
+    g_trace_on = true;
+    return MOKB_OK;
+}
+
+extern "C" long long mokb_trace_end(char* out, size_t cap) {
+    using namespace mokb;
+    g_trace_on = false;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    // streams are numbered in order of first appearance
+    cudaStream_t seen[16];
+    int n_seen = 0;
+    size_t used = 0;
+    for (int i = 0; i < g_trace_n; ++i) {
+        const TraceRec& r = g_trace[i];
+        int sid = 0;
+        while (sid < n_seen && seen[sid] != r.stream) ++sid;
+        if (sid == n_seen && n_seen < 16) seen[n_seen++] = r.stream;
+        float t0 = 0.f, t1 = 0.f;
+        if (cudaEventElapsedTime(&t0, g_trace_t0, r.begin) != cudaSuccess || cudaEventElapsedTime(&t1, g_trace_t0, r.end) != cudaSuccess)
+            continue;
+        char line[160];
+        const int len = snprintf(line, sizeof(line), "%s %d %d %.4f %.4f\n", r.tag, r.arg, sid, t0, t1);
+        if (out && used + len < cap) memcpy(out + used, line, len);
+        used += len;
+    }
+    if (out && cap) out[used < cap ? used : cap - 1] = 0;
+    g_trace_n = 0;
+    return static_cast<long long>(used);
+}
+
 extern "C" unsigned long long mokb_launch_count(void) { return __atomic_load_n(&mokb::g_launches, __ATOMIC_RELAXED); }
 
 extern "C" int mokb_device_arch(void) {

@@ -178,37 +178,80 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+__device__ __forceinline__ void st_global_16B(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Row-wise quantisation straight from registers: this thread holds 16 consecutive bf16 of a row as 8 packed
+// words, the neighbouring lane (lane ^ 1) the other half of the 32-element block.  Writes 16 E4M3 bytes; the
+// even lane of the pair also writes the block's scale byte.
+__device__ __forceinline__ void quantize_half_block(const uint32_t (&w)[8], uint8_t* q_dst, uint8_t* sc_dst, bool writes_scale) {
+    uint32_t m = 0u;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = absmax2(m, w[j]);
+    float amax = fmaxf(bf16_lo(m), bf16_hi(m));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    float inv;
+    const uint32_t byte = scale_byte(amax, &inv);
+    uint32_t out[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        out[j] = e4m3x4(bf16_lo(w[2 * j]) * inv, bf16_hi(w[2 * j]) * inv, bf16_lo(w[2 * j + 1]) * inv, bf16_hi(w[2 * j + 1]) * inv);
+    st_global_16B(q_dst, out[0], out[1], out[2], out[3]);
+    if (writes_scale) *sc_dst = static_cast<uint8_t>(byte);
+}
+
 // gate, up [rows, I] bf16 -> gate_q, up_q, hidden_q (row-wise) and hidden_qt (column-wise).
-// grid (I/128, window rows/128), 256 threads, 3 staged tiles.
-__global__ void __launch_bounds__(256) swiglu_fwd_quant_kernel(
+// grid (I/128, window rows/128), 256 threads.  Thread (row, v) owns columns [16v, 16v+16) of its row in four
+// row groups: gate, up and hidden are quantised row-wise from registers (pairs of lanes share a 32-column block);
+// only hidden is staged (one tile) for the column-wise pass.
+__global__ void __launch_bounds__(256, 3) swiglu_fwd_quant_kernel(
     const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up, int64_t rows_cap, int64_t I,
     RowWindow win, Clamp c,
     uint8_t* gate_q, uint8_t* gate_sc, uint8_t* up_q, uint8_t* up_sc,
     uint8_t* hid_q, uint8_t* hid_sc, uint8_t* hid_qt, uint8_t* hid_sct) {
-    extern __shared__ uint32_t sm[];
-    uint32_t *tg = sm, *tu = sm + TILE_WORDS, *th = sm + 2 * TILE_WORDS;
+    __shared__ uint32_t th[TILE_WORDS];
     const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
     int64_t r0;
     if (!tile_in_window(win, &r0)) return;
-    load_tile_bf16(tg, gate + r0 * I + c0, I);
-    load_tile_bf16(tu, up + r0 * I + c0, I);
-    __syncthreads();
-    for (int i = threadIdx.x; i < TILE * (TILE / 2); i += blockDim.x) {
-        const int r = i >> 6, wcol = i & 63;
-        const uint32_t gw = tg[r * WPITCH + wcol], uw = tu[r * WPITCH + wcol];
-        float g0 = bf16_lo(gw), g1 = bf16_hi(gw), u0 = bf16_lo(uw), u1 = bf16_hi(uw);
-        if (c.on) {
-            g0 = fminf(g0, c.limit);
-            g1 = fminf(g1, c.limit);
-            u0 = fminf(fmaxf(u0, -c.limit), c.limit);
-            u1 = fminf(fmaxf(u1, -c.limit), c.limit);
+    // two rounds of two row groups: four 32-byte loads in flight per thread, then the arithmetic
+#pragma unroll 1
+    for (int k0 = 0; k0 < 4; k0 += 2) {
+        uint32_t gw[2][8], uw[2][8];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int i = threadIdx.x + 256 * (k0 + k);
+            const int64_t off = (r0 + (i >> 3)) * I + c0 + (i & 7) * 16;
+            ld_global_32B(gate + off, gw[k]);
+            ld_global_32B(up + off, uw[k]);
         }
-        th[r * WPITCH + wcol] = pack2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int i = threadIdx.x + 256 * (k0 + k);
+            const int r = i >> 3, v = i & 7;
+            const int64_t row = r0 + r;
+            const int64_t col = c0 + v * 16;
+            const size_t sc_off = scale_offset(row, col >> 5, I >> 7);
+            const bool even = (v & 1) == 0;
+            quantize_half_block(gw[k], gate_q + row * I + col, gate_sc + sc_off, even);
+            quantize_half_block(uw[k], up_q + row * I + col, up_sc + sc_off, even);
+            uint32_t hw[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float g0 = bf16_lo(gw[k][j]), g1 = bf16_hi(gw[k][j]), u0 = bf16_lo(uw[k][j]), u1 = bf16_hi(uw[k][j]);
+                if (c.on) {
+                    g0 = fminf(g0, c.limit);
+                    g1 = fminf(g1, c.limit);
+                    u0 = fminf(fmaxf(u0, -c.limit), c.limit);
+                    u1 = fminf(fmaxf(u1, -c.limit), c.limit);
+                }
+                hw[j] = pack2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                th[r * WPITCH + v * 8 + j] = hw[j];
+            }
+            quantize_half_block(hw, hid_q + row * I + col, hid_sc + sc_off, even);
+        }
     }
     __syncthreads();
-    quantize_tile_rows(tg, gate_q, gate_sc, 0, r0, c0, I);
-    quantize_tile_rows(tu, up_q, up_sc, 0, r0, c0, I);
-    quantize_tile_rows(th, hid_q, hid_sc, 0, r0, c0, I);
     quantize_tile_cols(th, hid_qt, hid_sct, 0, r0, c0, rows_cap);
 }
 
@@ -218,42 +261,63 @@ __device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t v) {
     return __half22float2(*reinterpret_cast<const __half2*>(&h));
 }
 
-// Saved gate/up (E4M3 + scales), d_hidden bf16 -> d_gate, d_up (bf16 staged), their row-wise and
-// column-wise quantisations, and the per-(row, 128-column block) router-gradient partial
-// sum(d_hidden * silu(g) * u) / w.  grid (I/128, window rows/128), 256 threads.
-__global__ void __launch_bounds__(256) swiglu_bwd_quant_kernel(
+// Row-wise quantisation of one whole 32-element block: 16 packed words in shared memory.
+__device__ __forceinline__ void quantize_block_smem(const uint32_t* src, uint8_t* q_dst, uint8_t* sc_dst) {
+    uint32_t w[16];
+    uint32_t m = 0u;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        w[j] = src[j];
+        m = absmax2(m, w[j]);
+    }
+    float inv;
+    const uint32_t byte = scale_byte(fmaxf(bf16_lo(m), bf16_hi(m)), &inv);
+    uint32_t out[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        out[j] = e4m3x4(bf16_lo(w[2 * j]) * inv, bf16_hi(w[2 * j]) * inv, bf16_lo(w[2 * j + 1]) * inv, bf16_hi(w[2 * j + 1]) * inv);
+    st_global_32B(q_dst, out);
+    *sc_dst = static_cast<uint8_t>(byte);
+}
+
+// Saved gate/up (E4M3 + scales), d_hidden bf16 -> d_gate, d_up, their row-wise and column-wise quantisations,
+// and the per-(row, 128-column block) router-gradient partial sum(d_hidden * silu(g) * u) / w.
+// grid (I/128, window rows/128), 256 threads: two threads per row, 64 columns (two scale blocks) each, columns in
+// ascending order.  d_gate / d_up are quantised row-wise from registers and staged (two tiles) for the column-wise pass.
+__global__ void __launch_bounds__(256, 3) swiglu_bwd_quant_kernel(
     const uint8_t* __restrict__ gate_q, const uint8_t* __restrict__ gate_sc, const uint8_t* __restrict__ up_q,
     const uint8_t* __restrict__ up_sc, const __nv_bfloat16* __restrict__ d_hidden, int64_t rows_cap, int64_t I,
     RowWindow win, Clamp c, const float* __restrict__ row_scale,
     uint8_t* dg_q, uint8_t* dg_sc, uint8_t* dg_qt, uint8_t* dg_sct,
     uint8_t* du_q, uint8_t* du_sc, uint8_t* du_qt, uint8_t* du_sct, float* __restrict__ partials) {
     extern __shared__ uint32_t sm[];
-    uint32_t *tdh = sm, *tdg = sm + TILE_WORDS, *tdu = sm + 2 * TILE_WORDS;
+    uint32_t *tdg = sm, *tdu = sm + TILE_WORDS;
     __shared__ float row_part[TILE][2];
     const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
     int64_t r0;
     if (!tile_in_window(win, &r0)) return;
-    load_tile_bf16(tdh, d_hidden + r0 * I + c0, I);
-    __syncthreads();
-    // two threads per row, 64 columns each (two scale blocks of 32), columns in ascending order
     const int r = threadIdx.x & 127, half = threadIdx.x >> 7;
     const int64_t row = r0 + r;
     const float w = row_scale ? row_scale[row] : 1.0f;
     const float inv_w = w > 0.0f ? 1.0f / w : 0.0f;
     float partial = 0.0f;
+#pragma unroll 1
     for (int kb = half * 2; kb < half * 2 + 2; ++kb) {
-        const float gs = __uint_as_float(static_cast<uint32_t>(gate_sc[scale_offset(row, (c0 >> 5) + kb, I >> 7)]) << 23);
-        const float us = __uint_as_float(static_cast<uint32_t>(up_sc[scale_offset(row, (c0 >> 5) + kb, I >> 7)]) << 23);
-        uint32_t gv[8], uv[8];
-        ld_global_32B(gate_q + row * I + c0 + kb * 32, gv);
-        ld_global_32B(up_q + row * I + c0 + kb * 32, uv);
+        const int64_t col = c0 + kb * 32;
+        const size_t sc_off = scale_offset(row, col >> 5, I >> 7);
+        const float gs = __uint_as_float(static_cast<uint32_t>(gate_sc[sc_off]) << 23);
+        const float us = __uint_as_float(static_cast<uint32_t>(up_sc[sc_off]) << 23);
+        uint32_t gv[8], uv[8], dh[16];
+        ld_global_32B(gate_q + row * I + col, gv);
+        ld_global_32B(up_q + row * I + col, uv);
+        ld_global_32B(d_hidden + row * I + col, reinterpret_cast<uint32_t (&)[8]>(dh[0]));
+        ld_global_32B(d_hidden + row * I + col + 16, reinterpret_cast<uint32_t (&)[8]>(dh[8]));
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const float2 gq = e4m3x2_to_float2(gv[i >> 1] >> ((i & 1) * 16));
             const float2 uq = e4m3x2_to_float2(uv[i >> 1] >> ((i & 1) * 16));
-            const uint32_t dhw = tdh[r * WPITCH + kb * 16 + i];
             const float gg[2] = {gq.x * gs, gq.y * gs}, uu[2] = {uq.x * us, uq.y * us};
-            const float dh[2] = {bf16_lo(dhw), bf16_hi(dhw)};
+            const float dhv[2] = {bf16_lo(dh[i]), bf16_hi(dh[i])};
             float dg[2], du[2];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -268,19 +332,20 @@ __global__ void __launch_bounds__(256) swiglu_bwd_quant_kernel(
                 const float sig = 1.0f / (1.0f + __expf(-g));
                 const float silu = g * sig;
                 const float dsilu = (1.0f - silu) * sig + silu;
-                dg[j] = g_ok ? dsilu * u * dh[j] : 0.0f;
-                du[j] = u_ok ? silu * dh[j] : 0.0f;
-                partial += dh[j] * inv_w * (silu * u);
+                dg[j] = g_ok ? dsilu * u * dhv[j] : 0.0f;
+                du[j] = u_ok ? silu * dhv[j] : 0.0f;
+                partial += dhv[j] * inv_w * (silu * u);
             }
             tdg[r * WPITCH + kb * 16 + i] = pack2(dg[0], dg[1]);
             tdu[r * WPITCH + kb * 16 + i] = pack2(du[0], du[1]);
         }
+        // row-wise pass on the words this thread has just staged (its own: no barrier needed)
+        quantize_block_smem(tdg + r * WPITCH + kb * 16, dg_q + row * I + col, dg_sc + sc_off);
+        quantize_block_smem(tdu + r * WPITCH + kb * 16, du_q + row * I + col, du_sc + sc_off);
     }
     row_part[r][half] = partial;
     __syncthreads();
     if (partials && half == 0) partials[row * (I >> 7) + blockIdx.x] = row_part[r][0] + row_part[r][1];
-    quantize_tile_rows(tdg, dg_q, dg_sc, 0, r0, c0, I);
-    quantize_tile_rows(tdu, du_q, du_sc, 0, r0, c0, I);
     quantize_tile_cols(tdg, dg_qt, dg_sct, 0, r0, c0, rows_cap);
     quantize_tile_cols(tdu, du_qt, du_sct, 0, r0, c0, rows_cap);
 }
@@ -310,6 +375,7 @@ int check_window(const char* who, int row_begin, int* row_end, int64_t rows) {
 
 int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int32_t* num_rows, int row_begin, int row_end,
                   void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, cudaStream_t stream) {
+    TraceScope trace(stream, "quantize", row_begin);
     MOKB_REQUIRE(x_bf16 != nullptr, "mxfp8_quantize: null input");
     MOKB_REQUIRE(E > 0 && M > 0 && N > 0 && M % 128 == 0 && N % 128 == 0, "mxfp8_quantize: M and N must be positive multiples of 128");
     MOKB_REQUIRE((x_fp8 == nullptr) == (x_sc == nullptr) && (x_fp8_t == nullptr) == (x_sc_t == nullptr),
@@ -331,16 +397,15 @@ int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int
 int swiglu_fwd_quant_impl(const void* gate, const void* up, int64_t rows_cap, int64_t I, const int32_t* num_rows,
                           int row_begin, int row_end, int has_limit, float limit, void* gate_q, void* gate_sc, void* up_q, void* up_sc,
                           void* hid_q, void* hid_sc, void* hid_qt, void* hid_sct, cudaStream_t stream) {
+    TraceScope trace(stream, "swiglu_fwd_quant", row_begin);
     MOKB_REQUIRE(gate && up && gate_q && gate_sc && up_q && up_sc && hid_q && hid_sc && hid_qt && hid_sct, "swiglu_fwd_quant: null pointer");
     MOKB_REQUIRE(rows_cap > 0 && rows_cap % 128 == 0 && I > 0 && I % 128 == 0 && rows_cap / 128 <= 65535, "swiglu_fwd_quant: bad sizes");
     MOKB_REQUIRE(aligned32(gate) && aligned32(up) && aligned32(gate_q) && aligned32(up_q) && aligned32(hid_q) && aligned32(hid_qt),
                  "swiglu_fwd_quant: tensors must be 32-byte aligned");
     MOKB_TRY(check_window("swiglu_fwd_quant", row_begin, &row_end, rows_cap));
     if (row_begin == row_end) return MOKB_OK;
-    const size_t smem = 3 * TILE_WORDS * sizeof(uint32_t);
-    MOKB_CUDA(cudaFuncSetAttribute(swiglu_fwd_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid(static_cast<unsigned>(I / 128), static_cast<unsigned>((row_end - row_begin) / 128));
-    swiglu_fwd_quant_kernel<<<grid, 256, smem, stream>>>(
+    swiglu_fwd_quant_kernel<<<grid, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), rows_cap, I, RowWindow{num_rows, row_begin, row_end},
         Clamp{has_limit, limit},
         static_cast<uint8_t*>(gate_q), static_cast<uint8_t*>(gate_sc), static_cast<uint8_t*>(up_q), static_cast<uint8_t*>(up_sc),
@@ -355,6 +420,7 @@ int swiglu_bwd_quant_impl(const void* gate_q, const void* gate_sc, const void* u
                           const float* row_scale, void* dg_q, void* dg_sc, void* dg_qt, void* dg_sct,
                           void* du_q, void* du_sc, void* du_qt, void* du_sct, float* partials, float* row_grad,
                           cudaStream_t stream) {
+    TraceScope trace(stream, "swiglu_bwd_quant", row_begin);
     MOKB_REQUIRE(gate_q && gate_sc && up_q && up_sc && d_hidden && dg_q && dg_sc && dg_qt && dg_sct && du_q && du_sc && du_qt && du_sct,
                  "swiglu_bwd_quant: null pointer");
     MOKB_REQUIRE((partials == nullptr) == (row_grad == nullptr), "swiglu_bwd_quant: partials and row_grad go together");
@@ -363,7 +429,7 @@ int swiglu_bwd_quant_impl(const void* gate_q, const void* gate_sc, const void* u
                  aligned32(du_qt), "swiglu_bwd_quant: tensors must be 32-byte aligned");
     MOKB_TRY(check_window("swiglu_bwd_quant", row_begin, &row_end, rows_cap));
     if (row_begin == row_end) return MOKB_OK;
-    const size_t smem = 3 * TILE_WORDS * sizeof(uint32_t);
+    const size_t smem = 2 * TILE_WORDS * sizeof(uint32_t);
     MOKB_CUDA(cudaFuncSetAttribute(swiglu_bwd_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const RowWindow win{num_rows, row_begin, row_end};
     const dim3 grid(static_cast<unsigned>(I / 128), static_cast<unsigned>((row_end - row_begin) / 128));

@@ -206,6 +206,7 @@ extern "C" int mokb_schedule(const int32_t* topk_all, int ep_size, int num_local
                              int32_t* peer_rank, int32_t* peer_token_idx, int32_t* num_tokens,
                              int32_t* tokens_per_expert, void* scratch, int32_t* status, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    TraceScope trace(stream, "schedule");
     MOKB_REQUIRE(topk_all && peer_rank && peer_token_idx && num_tokens && tokens_per_expert && scratch && status,
                  "schedule: null pointer");
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "schedule: ep_size %d out of range", ep_size);

@@ -95,6 +95,8 @@ _sig("mokb_sm_count", c_int)
 _sig("mokb_struct_sizes", c_int, ctypes.POINTER(c_int), c_int)
 _sig("mokb_set_barrier_timeout_ms", c_int, c_int)
 _sig("mokb_launch_count", ctypes.c_ulonglong)
+_sig("mokb_trace_begin", c_int, c_vp)
+_sig("mokb_trace_end", ctypes.c_longlong, ctypes.c_char_p, c_sz)
 _sig("mokb_all_gather_top_experts", c_int, c_vp, c_u64p, c_int, c_int, c_i64, c_vp)
 _sig("mokb_barrier_all", c_int, c_u64p, c_int, c_int, c_vp, c_vp, c_vp)
 _sig("mokb_schedule_scratch_bytes", c_sz, c_int, c_int)
@@ -115,11 +117,31 @@ _sig("mokb_swiglu_bwd", c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c
 
 EXPORTED = [
     "mokb_last_error", "mokb_device_arch", "mokb_sm_count", "mokb_struct_sizes", "mokb_set_barrier_timeout_ms", "mokb_launch_count",
+    "mokb_trace_begin", "mokb_trace_end",
     "mokb_all_gather_top_experts", "mokb_barrier_all", "mokb_schedule_scratch_bytes", "mokb_schedule", "mokb_schedule_noalloc",
     "mokb_mxfp8_quantize", "mokb_fwd_epilogue", "mokb_bwd_epilogue", "mokb_layer_scratch_bytes",
     "mokb_dispatch_mlp_swiglu_combine_fwd_bf16", "mokb_dispatch_mlp_swiglu_combine_bwd_bf16",
     "mokb_grouped_gemm_bf16", "mokb_grouped_gemm_mxfp8", "mokb_dispatch_rows", "mokb_combine_rows", "mokb_swiglu_fwd", "mokb_swiglu_bwd",
 ]
+
+
+def trace_begin():
+    """Start recording the launch timeline of this library (diagnostic)."""
+    _ck(lib.mokb_trace_begin(_stream()))
+
+
+def trace_end():
+    """Stop recording; returns [(tag, arg, stream_no, begin_ms, end_ms)] for every launcher call since trace_begin."""
+    cap = 1 << 20
+    buf = ctypes.create_string_buffer(cap)
+    need = lib.mokb_trace_end(buf, cap)
+    if need < 0:
+        raise MokError("trace_end: CUDA error")
+    out = []
+    for line in buf.value.decode().splitlines():
+        tag, arg, sid, t0, t1 = line.split()
+        out.append((tag, int(arg), int(sid), float(t0), float(t1)))
+    return out
 
 
 def _check_struct_layout():

@@ -130,3 +130,22 @@ def test_several_macrobatches_with_replay_match_the_single_macrobatch_result(MB,
     # bit-reproducible across runs as well
     _, out_b, _, _, grads_b, _ = run_layer(ranks[0], 4, MB=MB, mb=mb)
     assert torch.equal(out, out_b) and all(torch.equal(a, b) for a, b in zip(grads, grads_b))
+
+
+def test_launch_timeline_records_every_phase_in_order():
+    from mok import _C
+    ranks = O.make_inputs(R=1, T=512, H=256, I=256, E=4, K=2, seed=3, routing="gaussian")
+    run_layer(ranks[0], 4)                   # warm-up: streams, events, function attributes
+    torch.cuda.synchronize()
+    _C.trace_begin()
+    run_layer(ranks[0], 4)
+    recs = _C.trace_end()
+    tags = [r[0] for r in recs]
+    for expected in ("schedule", "dispatch", "gemm_bf16_gate_up_swiglu", "gemm_bf16_nt",
+                     "combine", "fwd_epilogue", "dispatch_scaled", "gemm_bf16_nn", "swiglu_bwd", "gemm_bf16_wgrad", "bwd_epilogue"):
+        assert expected in tags, expected
+    assert all(0.0 <= b <= e for _, _, _, b, e in recs)
+    assert len({r[2] for r in recs}) == 3    # the caller's stream and the two side streams
+    first = {t: min(r[3] for r in recs if r[0] == t) for t in set(tags)}
+    assert first["schedule"] < first["dispatch"] < first["combine"] < first["fwd_epilogue"] < first["dispatch_scaled"] < first["bwd_epilogue"]
+    assert _C.trace_end() == []              # recording has stopped
