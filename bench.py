@@ -622,18 +622,23 @@ def time_dominant_kernel(_C, sched, x, wrg, wru, T, H, I, K, E_l, MB, steps, war
 
 
 def time_dominant_kernel_mxfp8(_C, ops, sched, x, qg, qu, T, H, I, E_l, MB, steps, warmup, device):
-    """Times the routed MXFP8 gate|up grouped GEMM alone (block-scaled E4M3, both products in one launch)."""
+    """Times the routed MXFP8 gate|up grouped GEMM alone: block-scaled E4M3, both products in one launch, SwiGLU and
+    the quantisation of gate, up and hidden in its epilogue (the form the layer runs)."""
     tpe = sched.tokens_per_expert
     gob = torch.repeat_interleave(torch.arange(E_l, device=device, dtype=torch.int32), (tpe // 128).to(torch.int64))
     gob = torch.cat([gob, torch.full((MB // 128 - gob.numel(),), -1, dtype=torch.int32, device=device)])
     x_routed = x.repeat((MB + T - 1) // T, 1)[:MB].contiguous()
     xq, xs, _, _ = ops.mxfp8_quantize(x_routed, True, False)
     del x_routed
-    gate, up = (torch.empty(MB, I, dtype=torch.bfloat16, device=device) for _ in range(2))
+    u8 = dict(dtype=torch.uint8, device=device)
+    outs = []
+    for _ in range(3):                                   # gate, up, hidden: E4M3 [MB, I] + packed scales
+        outs += [torch.empty(MB, I, **u8), torch.empty(MB // 128, I // 128, 32, 16, **u8)]
+    outs += [torch.empty(I, MB, **u8), torch.empty(I // 128, MB // 128, 32, 16, **u8)]      # hidden along tokens
 
     def launch():
-        _C.grouped_gemm_mxfp8(1, xq, xs, qg[0], qg[1], gate, rows=MB, num_rows=sched.num_tokens, group_of_block=gob,
-                              G=E_l, N=I, K=H, B2=qu[0], B2_sc=qu[1], D2=up)
+        _C.grouped_gemm_mxfp8(3, xq, xs, qg[0], qg[1], None, rows=MB, num_rows=sched.num_tokens, group_of_block=gob,
+                              G=E_l, N=I, K=H, B2=qu[0], B2_sc=qu[1], quantised_outputs=outs, t_rows=MB)
     for _ in range(warmup):
         launch()
     torch.cuda.synchronize()
@@ -646,7 +651,7 @@ def time_dominant_kernel_mxfp8(_C, ops, sched, x, qg, qu, T, H, I, E_l, MB, step
     ms = start.elapsed_time(end) / steps
     real_rows = int((sched.peer_rank >= 0).sum().item())
     flops = 4.0 * real_rows * H * I
-    return {"kernel": "grouped_gemm_mxfp8_kernel<gate|up>", "ms": ms, "flops_per_launch": flops,
+    return {"kernel": "grouped_gemm_mxfp8_kernel<gate|up + SwiGLU + quantise>", "ms": ms, "flops_per_launch": flops,
             "tflops": flops / (ms / 1000.0) / 1e12}
 
 

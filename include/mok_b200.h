@@ -222,7 +222,6 @@ typedef struct {
     /* work */
     void *x_routed;                                                           /* [MB, H] bf16 */
     void *x_fp8, *x_sc;                                                       /* [MB, H] */
-    void *gate_bf16, *up_bf16;                                                /* [MB, I] bf16 */
     void *hidden_fp8, *hidden_sc;                                             /* [MB, I] */
     void* scratch;                                                            /* mokb_layer_scratch_bytes() */
     int32_t* status;
@@ -274,7 +273,6 @@ typedef struct {
     const void *w_routed_gate, *w_routed_gate_sc, *w_routed_up, *w_routed_up_sc;   /* forward weights, quantised along H */
     void *x_routed;                                                           /* [MB, H] bf16 */
     void *x_fp8, *x_sc;                                                       /* [MB, H] */
-    void *gate_bf16, *up_bf16;                                                /* [MB, I] bf16 */
     void *hidden_fp8, *hidden_sc;                                             /* [MB, I] */
     void* scratch;
     int32_t* status;
@@ -325,7 +323,12 @@ int mokb_grouped_gemm_bf16(const mokb_gemm_args* args, void* stream);
  *           t_first: A and B hold the token columns [t_first, t_first + rows_static) of the row space that
  *           group_offsets refers to (a macrobatch of a longer schedule); offsets outside are not allowed.
  *           accumulate != 0 adds to the stored bf16 D (a group with an empty window then leaves D untouched
- *           instead of zeroing it). */
+ *           instead of zeroing it).
+ *   mode 3: the two products of mode 1 without the bf16 round trip: gate and up are rounded to bf16 in the
+ *           epilogue, hidden = SwiGLU(gate, up) (clamped if has_swiglu_limit), and the kernel writes gate_q, up_q,
+ *           hid_q [rows, N] E4M3 with scales along columns and hid_qt [N, t_rows] with scales along tokens: what
+ *           mode 1 followed by the reference's SwiGLU + quantise pass produces (grouped_gemm.cuh:295-359,
+ *           swiglu.cuh:38-207).  D and D2 are not used. */
 typedef struct {
     int mode;
     int rows_static, row_begin, row_end;     /* as in mokb_gemm_args; multiples of 256 */
@@ -337,6 +340,9 @@ typedef struct {
     void *D, *D2;
     int ldd;
     int t_first, accumulate;                 /* mode 2 only */
+    void *gate_q, *gate_sc, *up_q, *up_sc, *hid_q, *hid_sc, *hid_qt, *hid_sct;   /* mode 3 only */
+    int t_rows, has_swiglu_limit;
+    float swiglu_limit;
     int32_t* status;
 } mokb_gemm_fp8_args;
 int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* args, void* stream);

@@ -66,9 +66,6 @@ int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
 // which is also the row stride of the transposed outputs.
 int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int32_t* num_rows, int row_begin, int row_end,
                   void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, cudaStream_t stream);
-int swiglu_fwd_quant_impl(const void* gate, const void* up, int64_t rows_cap, int64_t I, const int32_t* num_rows,
-                          int row_begin, int row_end, int has_limit, float limit, void* gate_q, void* gate_sc, void* up_q, void* up_sc,
-                          void* hid_q, void* hid_sc, void* hid_qt, void* hid_sct, cudaStream_t stream);
 int swiglu_bwd_quant_impl(const void* gate_q, const void* gate_sc, const void* up_q, const void* up_sc, const void* d_hidden,
                           int64_t rows_cap, int64_t I, const int32_t* num_rows, int row_begin, int row_end, int has_limit, float limit,
                           const float* row_scale, void* dg_q, void* dg_sc, void* dg_qt, void* dg_sct,

@@ -124,10 +124,6 @@ struct Sched {
     }
 };
 
-// x * sigmoid(x) with the fast exponential and the fast division (2 ulp, and no call into the IEEE division's slow
-// path from the epilogue); the result is rounded to bf16 right after
-__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
-
 __device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -353,7 +349,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             gf = fminf(gf, p.limit);
                             uf = fminf(fmaxf(uf, -p.limit), p.limit);
                         }
-                        h[i] = __float_as_uint(silu_fast(gf) * uf);
+                        h[i] = __float_as_uint(gf / (1.0f + __expf(-gf)) * uf);
                     }
                     store_row32(p.D + off + c * 32, g, p.wide_stores);
                     store_row32(p.D2 + off + c * 32, u, p.wide_stores);

@@ -10,6 +10,10 @@
 //   FMODE_NT     D[rows,N] = A[rows,K] * W[g][N,K]^T (+ A2 * W2[g]^T)   down, both input gradients
 //   FMODE_DUALB  D = A * Wg[g]^T, D2 = A * Wu[g]^T, one 128+128 column tile  gate and up
 //   FMODE_WGRAD  D[g][M,N] = A[M, cols_g] * B[N, cols_g]^T                weight gradients
+//   FMODE_GATEUP_QUANT  the products of FMODE_DUALB, kept on chip: the epilogue rounds gate and up to bf16,
+//                computes hidden = SwiGLU(gate, up) and writes the MXFP8 forms the layer saves and consumes
+//                (gate, up, hidden quantised along columns; hidden also along tokens) instead of bf16 gate / up
+//                (the reference fuses the same quantisation into its gate/up epilogue, grouped_gemm.cuh:295-359)
 //
 // A CTA pair (cluster of 2, cta_group::2) computes a 256 x 256 tile; K advances 128 bytes per
 // stage (4 MMAs of K = 32).  Per stage each CTA stages 16 KB of A, 16 KB of B and three
@@ -24,6 +28,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "mxfp8_codec.cuh"
 
 namespace mokb {
 namespace {
@@ -44,7 +49,8 @@ constexpr int SF_SET_COLS = 16;                    // SFA 4 + SFB 8, padded
 constexpr int GROUP_M = 4;
 constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * (DATA_BYTES + SF_BYTES) + 1024 + 256;
 
-enum { FMODE_NT = 0, FMODE_DUALB = 1, FMODE_WGRAD = 2 };
+enum { FMODE_NT = 0, FMODE_DUALB = 1, FMODE_WGRAD = 2, FMODE_GATEUP_QUANT = 3 };
+template <int MODE> constexpr bool kGateUp = MODE == FMODE_DUALB || MODE == FMODE_GATEUP_QUANT;
 
 struct FParams {
     int rows_cap, row_begin, row_end;
@@ -60,6 +66,11 @@ struct FParams {
     int wide_stores;                 // D (and D2) rows are 32-byte aligned: the epilogue stores 32 bytes per instruction
     int accumulate;                  // FMODE_WGRAD: add to the stored bf16 result instead of overwriting it
     int k_tile_origin;               // FMODE_WGRAD: the operands' first token column, in 128-token tiles, in group_offsets' row space
+    // FMODE_GATEUP_QUANT outputs: E4M3 [rows, N] + packed scales for gate, up, hidden; hidden also as [N, t_rows]
+    uint8_t *gate_q, *gate_sc, *up_q, *up_sc, *hid_q, *hid_sc, *hid_qt, *hid_sct;
+    int t_rows;
+    int has_limit;
+    float limit;
     int32_t* status;
 };
 
@@ -82,7 +93,7 @@ struct Sched {
             const int hi = min(rows, p.row_end), lo = min(p.row_begin, hi);
             m_first = lo / TILE_M;
             m_blocks = (hi - lo) / TILE_M;
-            n_blocks = MODE == FMODE_DUALB ? p.N / 128 : (p.N + BN - 1) / BN;
+            n_blocks = kGateUp<MODE> ? p.N / 128 : (p.N + BN - 1) / BN;
             total = m_blocks * n_blocks;
         }
     }
@@ -121,6 +132,25 @@ __device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, ui
 __device__ __forceinline__ void st_global_v8(void* p, const uint32_t* v) {
     asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
                  "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+
+// 64 consecutive columns of one row (32 bf16 pairs in registers) -> two 32-element MXFP8 blocks of q [rows, N]
+__device__ __forceinline__ void quantize_row_blocks(const uint32_t (&w)[32], uint8_t* q, uint8_t* sc, int64_t row, int64_t col0, int64_t N) {
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        uint32_t m = 0u;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) m = absmax2(m, w[b * 16 + j]);
+        float inv;
+        const uint32_t byte = scale_byte(fmaxf(bf16_lo(m), bf16_hi(m)), &inv);
+        uint32_t out[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            out[j] = e4m3x4(bf16_lo(w[b * 16 + 2 * j]) * inv, bf16_hi(w[b * 16 + 2 * j]) * inv,
+                            bf16_lo(w[b * 16 + 2 * j + 1]) * inv, bf16_hi(w[b * 16 + 2 * j + 1]) * inv);
+        st_global_32B(q + row * N + col0 + b * 32, out);
+        sc[scale_offset(row, (col0 >> 5) + b, N >> 7)] = static_cast<uint8_t>(byte);
+    }
 }
 
 struct Maps {        // by-value kernel argument
@@ -163,7 +193,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
     }
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&tm.A); tma_prefetch_desc(&tm.B); tma_prefetch_desc(&tm.SA); tma_prefetch_desc(&tm.SB);
-        if (MODE == FMODE_DUALB || p.dual) { tma_prefetch_desc(&tm.B2); tma_prefetch_desc(&tm.SB2); }
+        if (kGateUp<MODE> || p.dual) { tma_prefetch_desc(&tm.B2); tma_prefetch_desc(&tm.SB2); }
         if (p.dual) { tma_prefetch_desc(&tm.A2); tma_prefetch_desc(&tm.SA2); }
     }
     if (warp == 1) {
@@ -211,7 +241,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
                         const CUtensorMap* tsa = second ? &tm.SA2 : &tm.SA;
                         tma_load_2d_pair(a_dst, ta, fb, kt * BKB, row0);
                         tma_load_2d_pair(sfa_dst, tsa, fb, 0, (row0 / 128) * p.a_ktiles + kt);
-                        if (MODE == FMODE_DUALB) {
+                        if (kGateUp<MODE>) {
                             const int brow = ti.group * p.b_rows_per_group + ti.n_blk * 128;
                             tma_load_2d_pair(b_dst, cta == 0 ? &tm.B : &tm.B2, fb, kt * BKB, brow);
                             tma_load_2d_pair(sfa_dst + SF_TILE, &tm.SB, fb, 0, (brow / 128) * p.b_ktiles + kt);
@@ -280,6 +310,71 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
             const Tile ti = sched.get(p, t);
             if (!mbar_wait(tfull_bar, local & 1, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
             tc_fence_after();
+            if (MODE == FMODE_GATEUP_QUANT) {
+                // This warp: 32 rows (its lanes) x gate columns [64 half, +64) and the matching up columns of the tile.
+                const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+                uint32_t gw[32], uw[32];                    // bf16 pairs: the values the bf16 path would have stored
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32x32(t_lane + half * 64 + c * 32, r0);
+                    tmem_ld_32x32(t_lane + 128 + half * 64 + c * 32, r1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        gw[c * 16 + i] = pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+                        uw[c * 16 + i] = pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
+
+                const int64_t row = static_cast<int64_t>(ti.m_blk) * TILE_M + row_in_tile;
+                const int64_t col0 = static_cast<int64_t>(ti.n_blk) * 128 + half * 64;
+                const int64_t N = p.N;
+                // along columns: this thread owns two whole 32-column blocks of its row in each tensor
+                quantize_row_blocks(gw, p.gate_q, p.gate_sc, row, col0, N);
+                quantize_row_blocks(uw, p.up_q, p.up_sc, row, col0, N);
+                // hidden only now: gate and up die pair by pair as it is computed (96 live values would not fit)
+                uint32_t hw[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float g0 = bf16_lo(gw[i]), g1 = bf16_hi(gw[i]), u0 = bf16_lo(uw[i]), u1 = bf16_hi(uw[i]);
+                    if (p.has_limit) {
+                        g0 = fminf(g0, p.limit);
+                        g1 = fminf(g1, p.limit);
+                        u0 = fminf(fmaxf(u0, -p.limit), p.limit);
+                        u1 = fminf(fmaxf(u1, -p.limit), p.limit);
+                    }
+                    hw[i] = pack2(__fdividef(g0, 1.0f + __expf(-g0)) * u0, __fdividef(g1, 1.0f + __expf(-g1)) * u1);
+                }
+                quantize_row_blocks(hw, p.hid_q, p.hid_sc, row, col0, N);
+                // along tokens: the warp's 32 lanes are one 32-token block of each of its 64 columns
+                const int64_t row_blk0 = static_cast<int64_t>(ti.m_blk) * TILE_M + static_cast<int>(cta) * 128 + quarter * 32;
+                uint32_t my_scales = 0u;                    // lane j keeps the two scale bytes of column pair j
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    uint32_t m = hw[j] & 0x7fff7fffu;
+#pragma unroll
+                    for (int d = 16; d >= 1; d >>= 1) m = absmax2(m, __shfl_xor_sync(0xffffffffu, m, d));
+                    float inv_a, inv_b;
+                    const uint32_t byte_a = scale_byte(bf16_lo(m), &inv_a);
+                    const uint32_t byte_b = scale_byte(bf16_hi(m), &inv_b);
+                    uint16_t pair;
+                    asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(pair) : "f"(bf16_lo(hw[j]) * inv_a), "f"(bf16_hi(hw[j]) * inv_b));
+                    const int64_t col = col0 + 2 * j;
+                    p.hid_qt[col * p.t_rows + row] = static_cast<uint8_t>(pair & 0xffu);
+                    p.hid_qt[(col + 1) * p.t_rows + row] = static_cast<uint8_t>(pair >> 8);
+                    if (lane == j) my_scales = byte_a | (byte_b << 8);
+                }
+                {
+                    const int64_t col = col0 + 2 * lane;
+                    p.hid_sct[scale_offset(col, row_blk0 >> 5, p.t_rows >> 7)] = static_cast<uint8_t>(my_scales & 0xffu);
+                    p.hid_sct[scale_offset(col + 1, row_blk0 >> 5, p.t_rows >> 7)] = static_cast<uint8_t>(my_scales >> 8);
+                }
+                continue;
+            }
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * 128);
             const bool empty_k = ti.k_iters == 0;
             // drain this warp's part of the accumulator into registers as packed bf16, then hand it back to the MMA lane
@@ -397,10 +492,10 @@ using namespace mokb;
 extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     MOKB_REQUIRE(g != nullptr, "grouped_gemm_mxfp8: null args");
-    static const char* const kTags[3] = {"gemm_mxfp8_nt", "gemm_mxfp8_gate_up", "gemm_mxfp8_wgrad"};
-    TraceScope trace(stream, kTags[g->mode >= 0 && g->mode <= 2 ? g->mode : 0], g->row_begin);
-    MOKB_REQUIRE(g->mode >= 0 && g->mode <= 2, "grouped_gemm_mxfp8: unknown mode %d", g->mode);
-    MOKB_REQUIRE(g->A && g->A_sc && g->B && g->B_sc && g->D && g->status, "grouped_gemm_mxfp8: null pointer");
+    static const char* const kTags[4] = {"gemm_mxfp8_nt", "gemm_mxfp8_gate_up", "gemm_mxfp8_wgrad", "gemm_mxfp8_gate_up_swiglu_quant"};
+    TraceScope trace(stream, kTags[g->mode >= 0 && g->mode <= 3 ? g->mode : 0], g->row_begin);
+    MOKB_REQUIRE(g->mode >= 0 && g->mode <= 3, "grouped_gemm_mxfp8: unknown mode %d", g->mode);
+    MOKB_REQUIRE(g->A && g->A_sc && g->B && g->B_sc && (g->D || g->mode == FMODE_GATEUP_QUANT) && g->status, "grouped_gemm_mxfp8: null pointer");
     MOKB_REQUIRE(g->G >= 1 && g->ldd % 8 == 0, "grouped_gemm_mxfp8: bad G or ldd");
     MOKB_REQUIRE(g->rows_static > 0 && g->rows_static % 256 == 0, "grouped_gemm_mxfp8: rows must be a positive multiple of 256");
     FParams p;
@@ -447,11 +542,27 @@ extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream
     m.A2 = m.A; m.B2 = m.B; m.SA2 = m.SA; m.SB2 = m.SB;
     p.a_ktiles = p.b_ktiles = g->K / 128;
     p.b_rows_per_group = g->N;
-    if (g->mode == FMODE_DUALB) {
-        MOKB_REQUIRE(g->B2 && g->B2_sc && g->D2, "grouped_gemm_mxfp8 DUALB: B2, B2_sc and D2 required");
+    if (g->mode == FMODE_DUALB || g->mode == FMODE_GATEUP_QUANT) {
+        MOKB_REQUIRE(g->B2 && g->B2_sc, "grouped_gemm_mxfp8 gate/up: B2 and B2_sc required");
         MOKB_TRY(data_map(&m.B2, g->B2, g->K, brows));
         MOKB_TRY(scale_map(&m.SB2, g->B2_sc, (brows / 128) * (g->K / 128)));
-        return launch<FMODE_DUALB>(m, p, m_tiles * (g->N / 128), stream);
+        if (g->mode == FMODE_DUALB) {
+            MOKB_REQUIRE(g->D2 != nullptr, "grouped_gemm_mxfp8 mode 1: D2 required");
+            return launch<FMODE_DUALB>(m, p, m_tiles * (g->N / 128), stream);
+        }
+        MOKB_REQUIRE(g->gate_q && g->gate_sc && g->up_q && g->up_sc && g->hid_q && g->hid_sc && g->hid_qt && g->hid_sct,
+                     "grouped_gemm_mxfp8 mode 3: all eight quantised outputs required");
+        MOKB_REQUIRE(g->t_rows > 0 && g->t_rows % 128 == 0, "grouped_gemm_mxfp8 mode 3: t_rows must be a positive multiple of 128");
+        MOKB_REQUIRE(((reinterpret_cast<uintptr_t>(g->gate_q) | reinterpret_cast<uintptr_t>(g->up_q) | reinterpret_cast<uintptr_t>(g->hid_q)) & 31) == 0,
+                     "grouped_gemm_mxfp8 mode 3: quantised outputs must be 32-byte aligned");
+        p.gate_q = static_cast<uint8_t*>(g->gate_q); p.gate_sc = static_cast<uint8_t*>(g->gate_sc);
+        p.up_q = static_cast<uint8_t*>(g->up_q); p.up_sc = static_cast<uint8_t*>(g->up_sc);
+        p.hid_q = static_cast<uint8_t*>(g->hid_q); p.hid_sc = static_cast<uint8_t*>(g->hid_sc);
+        p.hid_qt = static_cast<uint8_t*>(g->hid_qt); p.hid_sct = static_cast<uint8_t*>(g->hid_sct);
+        p.t_rows = g->t_rows;
+        p.has_limit = g->has_swiglu_limit;
+        p.limit = g->swiglu_limit;
+        return launch<FMODE_GATEUP_QUANT>(m, p, m_tiles * (g->N / 128), stream);
     }
     if (g->A2) {
         MOKB_REQUIRE(g->A2_sc && g->B2 && g->B2_sc, "grouped_gemm_mxfp8: the second operand pair needs data and scales");

@@ -8,8 +8,9 @@ using namespace mokb;
 //
 // Dataflow (quantisation points as in the reference):
 //   forward   dispatch x -> quantise x row-wise (GEMM operand) and token-wise (saved for wgrad)
-//             gate, up = x_q * Wg_q^T, x_q * Wu_q^T (bf16) -> SwiGLU -> quantise gate, up (saved),
-//             hidden row-wise (GEMM operand) and token-wise (saved) -> y = hidden_q * Wd_q^T -> combine
+//             gate, up = x_q * Wg_q^T, x_q * Wu_q^T, rounded to bf16 in the GEMM epilogue, which also applies SwiGLU
+//             and quantises gate, up (saved) and hidden row-wise (GEMM operand) and token-wise (saved)
+//             -> y = hidden_q * Wd_q^T -> combine
 //   backward  pull d_y * w -> quantise both ways -> d_hidden = d_y_q * WdT_q^T
 //             -> de-quantise saved gate/up, SwiGLU backward, router-gradient partials, quantise d_gate, d_up
 //             both ways -> d_x = d_gate_q * WgT_q^T + d_up_q * WuT_q^T -> combine;
@@ -52,12 +53,12 @@ inline void* rebase_scales_t(const void* sc, int first) {
 // The routed forward tensors of one macrobatch, addressed by schedule row.
 struct FwdView {
     void *x_routed, *x_fp8, *x_sc, *x_fp8_t, *x_sc_t;
-    void *gate_bf16, *up_bf16, *gate_fp8, *gate_sc, *up_fp8, *up_sc;
+    void *gate_fp8, *gate_sc, *up_fp8, *up_sc;
     void *hidden_fp8, *hidden_sc, *hidden_fp8_t, *hidden_sc_t;
 };
 
-FwdView fwd_view(int lo, int H, int I, void* x_routed, void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, void* gate_bf16,
-                 void* up_bf16, void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc, void* hidden_fp8, void* hidden_sc,
+FwdView fwd_view(int lo, int H, int I, void* x_routed, void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t,
+                 void* gate_fp8, void* gate_sc, void* up_fp8, void* up_sc, void* hidden_fp8, void* hidden_sc,
                  void* hidden_fp8_t, void* hidden_sc_t) {
     FwdView v;
     v.x_routed = rebase(x_routed, lo, 2ull * H);
@@ -65,8 +66,6 @@ FwdView fwd_view(int lo, int H, int I, void* x_routed, void* x_fp8, void* x_sc, 
     v.x_sc = rebase_scales(x_sc, lo, H);
     v.x_fp8_t = rebase_t(x_fp8_t, lo);
     v.x_sc_t = rebase_scales_t(x_sc_t, lo);
-    v.gate_bf16 = rebase(gate_bf16, lo, 2ull * I);
-    v.up_bf16 = rebase(up_bf16, lo, 2ull * I);
     v.gate_fp8 = rebase(gate_fp8, lo, 1ull * I);
     v.gate_sc = rebase_scales(gate_sc, lo, I);
     v.up_fp8 = rebase(up_fp8, lo, 1ull * I);
@@ -82,17 +81,17 @@ struct GateUpWeights {
     const void *gate, *gate_sc, *up, *up_sc;
 };
 
-// rows [r0, r1) of macrobatch rows [.., hi): gate|up GEMM, then SwiGLU + quantisation of gate, up and hidden
+// rows [r0, r1) of macrobatch rows [.., hi): gate|up GEMM whose epilogue applies SwiGLU and writes gate, up and hidden in MXFP8
 int gate_up_swiglu(const FwdView& v, const GateUpWeights& w, const Scratch& s, int r0, int r1, int hi, int MB, int E_l, int H, int I,
                    int has_limit, float limit, int32_t* status, cudaStream_t stream) {
     mokb_gemm_fp8_args f = fp8_base(status);
-    f.mode = 1; f.rows_static = hi; f.row_begin = r0; f.row_end = r1;
+    f.mode = 3; f.rows_static = hi; f.row_begin = r0; f.row_end = r1;
     f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
     f.A = v.x_fp8; f.A_sc = v.x_sc; f.B = w.gate; f.B_sc = w.gate_sc; f.B2 = w.up; f.B2_sc = w.up_sc;
-    f.D = v.gate_bf16; f.D2 = v.up_bf16; f.ldd = I;
-    MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-    return swiglu_fwd_quant_impl(v.gate_bf16, v.up_bf16, MB, I, s.n_rows, r0, r1, has_limit, limit, v.gate_fp8, v.gate_sc, v.up_fp8,
-                                 v.up_sc, v.hidden_fp8, v.hidden_sc, v.hidden_fp8_t, v.hidden_sc_t, stream);
+    f.gate_q = v.gate_fp8; f.gate_sc = v.gate_sc; f.up_q = v.up_fp8; f.up_sc = v.up_sc;
+    f.hid_q = v.hidden_fp8; f.hid_sc = v.hidden_sc; f.hid_qt = v.hidden_fp8_t; f.hid_sct = v.hidden_sc_t;
+    f.t_rows = MB; f.has_swiglu_limit = has_limit; f.swiglu_limit = limit; f.ldd = I;
+    return mokb_grouped_gemm_mxfp8(&f, stream);
 }
 
 }  // namespace
@@ -106,7 +105,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
                  a->w_routed_up_sc, "fwd_mxfp8: null input");
     MOKB_REQUIRE(a->x_fp8_t && a->x_sc_t && a->gate_shared && a->up_shared && a->hidden_shared && a->gate_fp8 && a->gate_sc &&
                  a->up_fp8 && a->up_sc && a->hidden_fp8_t && a->hidden_sc_t, "fwd_mxfp8: null output");
-    MOKB_REQUIRE(a->x_routed && a->x_fp8 && a->x_sc && a->gate_bf16 && a->up_bf16 && a->hidden_fp8 && a->hidden_sc, "fwd_mxfp8: null work buffer");
+    MOKB_REQUIRE(a->x_routed && a->x_fp8 && a->x_sc && a->hidden_fp8 && a->hidden_sc, "fwd_mxfp8: null work buffer");
     const bool with_down = !a->skip_down_combine;
     if (with_down)
         MOKB_REQUIRE(a->combine_ptrs_host && a->w_shared_down && a->w_routed_down && a->w_routed_down_sc && a->y_shared && a->y_routed,
@@ -133,7 +132,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
         // only macrobatch 0 (the one that is always populated) is cut into overlap windows
         const int chunk = m == 0 ? chunk_rows_for(MB, a->minibatch_size) : MB;
         const int nchunks = (hi - lo + chunk - 1) / chunk;
-        const FwdView v = fwd_view(lo, H, I, a->x_routed, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, a->gate_bf16, a->up_bf16, a->gate_fp8,
+        const FwdView v = fwd_view(lo, H, I, a->x_routed, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, a->gate_fp8,
                                    a->gate_sc, a->up_fp8, a->up_sc, a->hidden_fp8, a->hidden_sc, a->hidden_fp8_t, a->hidden_sc_t);
         void* y_r = with_down ? rebase(a->y_routed, lo, 2ull * H) : nullptr;
 
@@ -214,7 +213,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
     const int n_macro = macrobatches(C, MB);
     if (n_macro > 1)
         MOKB_REQUIRE(a->w_routed_gate && a->w_routed_gate_sc && a->w_routed_up && a->w_routed_up_sc && a->x_routed && a->x_fp8 && a->x_sc &&
-                     a->gate_bf16 && a->up_bf16 && a->hidden_fp8 && a->hidden_sc,
+                     a->hidden_fp8 && a->hidden_sc,
                      "bwd_mxfp8: schedule_capacity > macrobatch_size needs the forward weights and the replay work buffers");
     const Scratch s = carve(a->scratch, C, E_l, MB);
     const bool overlap = overlap_enabled();
@@ -233,7 +232,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
     for (int m = 0; m < n_macro; ++m) {
         const int lo = m * MB, hi = (lo + MB < C) ? lo + MB : C;
         // the context (macrobatch 0: as saved; later ones: rebuilt below) and the work buffers, addressed by schedule row
-        const FwdView v = fwd_view(lo, H, I, a->x_routed, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, a->gate_bf16, a->up_bf16, a->gate_fp8,
+        const FwdView v = fwd_view(lo, H, I, a->x_routed, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, a->gate_fp8,
                                    a->gate_sc, a->up_fp8, a->up_sc, a->hidden_fp8, a->hidden_sc, a->hidden_fp8_t, a->hidden_sc_t);
         void* d_y_r = rebase(a->d_y_routed, lo, 2ull * H);
         void* d_y_fp8 = rebase(a->d_y_fp8, lo, 1ull * H);

@@ -2,7 +2,7 @@
 // ("normal") and/or along columns ("transposed": the quantisation of x^T), scales laid out
 // in the 32 x 16-byte tiles that tcgen05 block-scaled MMA consumes.
 //   quantize_kernel         plain quantiser            (reference: csrc/mxfp8.cuh:188-278)
-//   swiglu_fwd_quant_kernel SwiGLU forward + quantise  (reference: csrc/megakernel/swiglu.cuh:38-207)
+//   (SwiGLU forward + quantise is the epilogue of the MXFP8 gate/up GEMM, gemm_mxfp8.cu)
 //   swiglu_bwd_quant_kernel de-quantise saved gate/up, SwiGLU backward, router-gradient partials,
 //                           quantise d_gate / d_up      (reference: swiglu.cuh:209-566)
 // One 128 x 128 tile per CTA, staged in shared memory as packed bf16 pairs with an odd word pitch,
@@ -14,6 +14,7 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
+#include "mxfp8_codec.cuh"
 
 namespace mokb {
 namespace {
@@ -21,51 +22,6 @@ namespace {
 constexpr int TILE = 128;
 constexpr int WPITCH = TILE / 2 + 1;          // 32-bit words per smem row (65: odd)
 constexpr int TILE_WORDS = TILE * WPITCH;
-
-__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-
-// running per-half maximum of |x| over packed bf16 pairs
-__device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w) {
-    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&m),
-                                     __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w)));
-    return *reinterpret_cast<const uint32_t*>(&r);
-}
-
-// block maximum -> E8M0 scale byte and the exact reciprocal of the scale (csrc/mxfp8.cuh:45-60):
-// scale = max(amax / 448, 1e-12) rounded up to a power of two
-__device__ __forceinline__ uint32_t scale_byte(float amax, float* inv) {
-    const float scale = fmaxf(amax * 0.002232142857f, 0.000000000001f);
-    uint16_t sc2;
-    asm volatile("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(sc2) : "f"(scale), "f"(scale));
-    const uint32_t byte = sc2 & 0xFFu;
-    *inv = __uint_as_float((254u - byte) << 23);
-    return byte;
-}
-
-// four floats -> four E4M3 bytes (a in the lowest byte), round to nearest even, saturating (csrc/mxfp8.cuh:62-72)
-__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
-    uint16_t lo, hi;
-    asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
-    asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
-    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-}
-
-__device__ __forceinline__ void st_global_32B(void* p, const uint32_t (&v)[8]) {
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
-                 "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
-}
-__device__ __forceinline__ void ld_global_32B(const void* p, uint32_t (&v)[8]) {
-    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]),
-                 "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "l"(p));
-}
-
-// byte offset of the scale of (row r, 32-element block kb) of a [rows, cols] matrix in the packed
-// [rows/128, cols/128, 32, 16] layout (csrc/mxfp8.cuh:184)
-__device__ __forceinline__ size_t scale_offset(int64_t r, int64_t kb, int64_t col_tiles) {
-    const int64_t rt = r >> 7, ri = r & 127, ct = kb >> 2, ki = kb & 3;
-    return static_cast<size_t>((rt * col_tiles + ct) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + ki);
-}
 
 // Row-wise quantisation of a staged tile into q [rows, cols] (+ scales): item = (row, block of 32 columns);
 // consecutive lanes take consecutive rows (conflict-free with the odd pitch).
@@ -173,87 +129,6 @@ struct Clamp {
     float limit;
 };
 
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-__device__ __forceinline__ void st_global_16B(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-
-// Row-wise quantisation straight from registers: this thread holds 16 consecutive bf16 of a row as 8 packed
-// words, the neighbouring lane (lane ^ 1) the other half of the 32-element block.  Writes 16 E4M3 bytes; the
-// even lane of the pair also writes the block's scale byte.
-__device__ __forceinline__ void quantize_half_block(const uint32_t (&w)[8], uint8_t* q_dst, uint8_t* sc_dst, bool writes_scale) {
-    uint32_t m = 0u;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) m = absmax2(m, w[j]);
-    float amax = fmaxf(bf16_lo(m), bf16_hi(m));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    float inv;
-    const uint32_t byte = scale_byte(amax, &inv);
-    uint32_t out[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-        out[j] = e4m3x4(bf16_lo(w[2 * j]) * inv, bf16_hi(w[2 * j]) * inv, bf16_lo(w[2 * j + 1]) * inv, bf16_hi(w[2 * j + 1]) * inv);
-    st_global_16B(q_dst, out[0], out[1], out[2], out[3]);
-    if (writes_scale) *sc_dst = static_cast<uint8_t>(byte);
-}
-
-// gate, up [rows, I] bf16 -> gate_q, up_q, hidden_q (row-wise) and hidden_qt (column-wise).
-// grid (I/128, window rows/128), 256 threads.  Thread (row, v) owns columns [16v, 16v+16) of its row in four
-// row groups: gate, up and hidden are quantised row-wise from registers (pairs of lanes share a 32-column block);
-// only hidden is staged (one tile) for the column-wise pass.
-__global__ void __launch_bounds__(256, 3) swiglu_fwd_quant_kernel(
-    const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up, int64_t rows_cap, int64_t I,
-    RowWindow win, Clamp c,
-    uint8_t* gate_q, uint8_t* gate_sc, uint8_t* up_q, uint8_t* up_sc,
-    uint8_t* hid_q, uint8_t* hid_sc, uint8_t* hid_qt, uint8_t* hid_sct) {
-    __shared__ uint32_t th[TILE_WORDS];
-    const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
-    int64_t r0;
-    if (!tile_in_window(win, &r0)) return;
-    // two rounds of two row groups: four 32-byte loads in flight per thread, then the arithmetic
-#pragma unroll 1
-    for (int k0 = 0; k0 < 4; k0 += 2) {
-        uint32_t gw[2][8], uw[2][8];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int i = threadIdx.x + 256 * (k0 + k);
-            const int64_t off = (r0 + (i >> 3)) * I + c0 + (i & 7) * 16;
-            ld_global_32B(gate + off, gw[k]);
-            ld_global_32B(up + off, uw[k]);
-        }
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int i = threadIdx.x + 256 * (k0 + k);
-            const int r = i >> 3, v = i & 7;
-            const int64_t row = r0 + r;
-            const int64_t col = c0 + v * 16;
-            const size_t sc_off = scale_offset(row, col >> 5, I >> 7);
-            const bool even = (v & 1) == 0;
-            quantize_half_block(gw[k], gate_q + row * I + col, gate_sc + sc_off, even);
-            quantize_half_block(uw[k], up_q + row * I + col, up_sc + sc_off, even);
-            uint32_t hw[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float g0 = bf16_lo(gw[k][j]), g1 = bf16_hi(gw[k][j]), u0 = bf16_lo(uw[k][j]), u1 = bf16_hi(uw[k][j]);
-                if (c.on) {
-                    g0 = fminf(g0, c.limit);
-                    g1 = fminf(g1, c.limit);
-                    u0 = fminf(fmaxf(u0, -c.limit), c.limit);
-                    u1 = fminf(fmaxf(u1, -c.limit), c.limit);
-                }
-                hw[j] = pack2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
-                th[r * WPITCH + v * 8 + j] = hw[j];
-            }
-            quantize_half_block(hw, hid_q + row * I + col, hid_sc + sc_off, even);
-        }
-    }
-    __syncthreads();
-    quantize_tile_cols(th, hid_qt, hid_sct, 0, r0, c0, rows_cap);
-}
 
 // two E4M3 bytes (the low 16 bits of v) -> two floats
 __device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t v) {
@@ -389,27 +264,6 @@ int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int
     quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), M, N, RowWindow{num_rows, row_begin, row_end},
                                               static_cast<uint8_t*>(x_fp8), static_cast<uint8_t*>(x_sc),
                                               static_cast<uint8_t*>(x_fp8_t), static_cast<uint8_t*>(x_sc_t));
-    MOKB_CUDA(cudaGetLastError());
-    note_launch();
-    return MOKB_OK;
-}
-
-int swiglu_fwd_quant_impl(const void* gate, const void* up, int64_t rows_cap, int64_t I, const int32_t* num_rows,
-                          int row_begin, int row_end, int has_limit, float limit, void* gate_q, void* gate_sc, void* up_q, void* up_sc,
-                          void* hid_q, void* hid_sc, void* hid_qt, void* hid_sct, cudaStream_t stream) {
-    TraceScope trace(stream, "swiglu_fwd_quant", row_begin);
-    MOKB_REQUIRE(gate && up && gate_q && gate_sc && up_q && up_sc && hid_q && hid_sc && hid_qt && hid_sct, "swiglu_fwd_quant: null pointer");
-    MOKB_REQUIRE(rows_cap > 0 && rows_cap % 128 == 0 && I > 0 && I % 128 == 0 && rows_cap / 128 <= 65535, "swiglu_fwd_quant: bad sizes");
-    MOKB_REQUIRE(aligned32(gate) && aligned32(up) && aligned32(gate_q) && aligned32(up_q) && aligned32(hid_q) && aligned32(hid_qt),
-                 "swiglu_fwd_quant: tensors must be 32-byte aligned");
-    MOKB_TRY(check_window("swiglu_fwd_quant", row_begin, &row_end, rows_cap));
-    if (row_begin == row_end) return MOKB_OK;
-    const dim3 grid(static_cast<unsigned>(I / 128), static_cast<unsigned>((row_end - row_begin) / 128));
-    swiglu_fwd_quant_kernel<<<grid, 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), rows_cap, I, RowWindow{num_rows, row_begin, row_end},
-        Clamp{has_limit, limit},
-        static_cast<uint8_t*>(gate_q), static_cast<uint8_t*>(gate_sc), static_cast<uint8_t*>(up_q), static_cast<uint8_t*>(up_sc),
-        static_cast<uint8_t*>(hid_q), static_cast<uint8_t*>(hid_sc), static_cast<uint8_t*>(hid_qt), static_cast<uint8_t*>(hid_sct));
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     return MOKB_OK;

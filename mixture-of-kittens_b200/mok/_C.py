@@ -75,11 +75,13 @@ class GemmArgs(ctypes.Structure):
 
 
 class GemmFp8Args(ctypes.Structure):
-    _fields_ = [("mode", c_int), ("rows_static", c_int), ("row_begin", c_int), ("row_end", c_int), ("num_rows", c_vp),
-                ("group_of_block", c_vp), ("group_offsets", c_vp), ("G", c_int), ("M", c_int), ("N", c_int), ("K", c_int),
-                ("A", c_vp), ("A_sc", c_vp), ("B", c_vp), ("B_sc", c_vp), ("A2", c_vp), ("A2_sc", c_vp), ("B2", c_vp),
-                ("B2_sc", c_vp), ("D", c_vp), ("D2", c_vp), ("ldd", c_int), ("t_first", c_int), ("accumulate", c_int),
-                ("status", c_vp)]
+    _fields_ = (
+        [("mode", c_int), ("rows_static", c_int), ("row_begin", c_int), ("row_end", c_int), ("num_rows", c_vp),
+         ("group_of_block", c_vp), ("group_offsets", c_vp), ("G", c_int), ("M", c_int), ("N", c_int), ("K", c_int),
+         ("A", c_vp), ("A_sc", c_vp), ("B", c_vp), ("B_sc", c_vp), ("A2", c_vp), ("A2_sc", c_vp), ("B2", c_vp),
+         ("B2_sc", c_vp), ("D", c_vp), ("D2", c_vp), ("ldd", c_int), ("t_first", c_int), ("accumulate", c_int)]
+        + [(n, c_vp) for n in ("gate_q", "gate_sc", "up_q", "up_sc", "hid_q", "hid_sc", "hid_qt", "hid_sct")]
+        + [("t_rows", c_int), ("has_swiglu_limit", c_int), ("swiglu_limit", c_f32), ("status", c_vp)])
 
 
 def _sig(name, restype, *argtypes):
@@ -441,7 +443,8 @@ def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None
 
 def grouped_gemm_mxfp8(mode, A, A_sc, B, B_sc, D, *, rows=None, num_rows=None, group_of_block=None, group_offsets=None,
                        G=1, M=0, N=0, K=0, A2=None, A2_sc=None, B2=None, B2_sc=None, D2=None, ldd=None, row_begin=0, row_end=0,
-                       t_first=0, accumulate=False):
+                       t_first=0, accumulate=False, quantised_outputs=None, t_rows=0, swiglu_limit=None):
+    """`quantised_outputs` (mode 3): (gate_q, gate_sc, up_q, up_sc, hid_q, hid_sc, hid_qt, hid_sct); D is then unused."""
     g = GemmFp8Args()
     g.mode = mode
     g.rows_static = (A.shape[0] if mode != 2 else A.shape[1]) if rows is None else rows
@@ -451,8 +454,13 @@ def grouped_gemm_mxfp8(mode, A, A_sc, B, B_sc, D, *, rows=None, num_rows=None, g
     g.A, g.A_sc, g.B, g.B_sc = _p(A), _p(A_sc), _p(B), _p(B_sc)
     g.A2, g.A2_sc, g.B2, g.B2_sc = _p(A2), _p(A2_sc), _p(B2), _p(B2_sc)
     g.D, g.D2 = _p(D), _p(D2)
-    g.ldd = D.shape[-1] if ldd is None else ldd
+    g.ldd = (D.shape[-1] if D is not None else N) if ldd is None else ldd
     g.t_first, g.accumulate = t_first, int(bool(accumulate))
+    if quantised_outputs is not None:
+        (g.gate_q, g.gate_sc, g.up_q, g.up_sc, g.hid_q, g.hid_sc, g.hid_qt, g.hid_sct) = map(_p, quantised_outputs)
+        g.t_rows = t_rows
+        g.has_swiglu_limit = 0 if swiglu_limit is None else 1
+        g.swiglu_limit = 0.0 if swiglu_limit is None else float(swiglu_limit)
     g.status = _p(status_tensor(A.device))
     _ck(lib.mokb_grouped_gemm_mxfp8(ctypes.byref(g), _stream()))
 

@@ -24,7 +24,7 @@ class FwdMxfp8Args(ctypes.Structure):
             "w_routed_gate", "w_routed_gate_sc", "w_routed_up", "w_routed_up_sc", "w_routed_down", "w_routed_down_sc",
             "x_fp8_t", "x_sc_t", "gate_shared", "up_shared", "hidden_shared", "gate_fp8", "gate_sc", "up_fp8", "up_sc",
             "hidden_fp8_t", "hidden_sc_t", "y_shared", "y_routed",
-            "x_routed", "x_fp8", "x_sc", "gate_bf16", "up_bf16", "hidden_fp8", "hidden_sc", "scratch", "status")]
+            "x_routed", "x_fp8", "x_sc", "hidden_fp8", "hidden_sc", "scratch", "status")]
         + [("skip_down_combine", c_int)])
 
 
@@ -43,7 +43,7 @@ class BwdMxfp8Args(ctypes.Structure):
             "d_w_shared_gate", "d_w_routed_gate", "d_w_shared_up", "d_w_routed_up", "d_w_shared_down", "d_w_routed_down",
             "d_y_routed", "d_y_fp8_t", "d_y_sc_t", "d_gate_fp8_t", "d_gate_sc_t", "d_up_fp8_t", "d_up_sc_t", "partials",
             "w_routed_gate", "w_routed_gate_sc", "w_routed_up", "w_routed_up_sc",
-            "x_routed", "x_fp8", "x_sc", "gate_bf16", "up_bf16", "hidden_fp8", "hidden_sc",
+            "x_routed", "x_fp8", "x_sc", "hidden_fp8", "hidden_sc",
             "scratch", "status")])
 
 
@@ -100,12 +100,12 @@ def _fwd(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_routed
         y_shared, y_routed = torch.empty(T, H, **bf), torch.empty(MB, H, **bf)
         keep.append(_ptr_array(combine_buffer_ptrs))
         a.combine_ptrs_host = keep[1]
-    work = [torch.empty(MB, H, **bf), *_q(MB, H, dev), torch.empty(MB, I, **bf), torch.empty(MB, I, **bf), *_q(MB, I, dev)]
+    work = [torch.empty(MB, H, **bf), *_q(MB, H, dev), *_q(MB, I, dev)]
     (a.x_fp8_t, a.x_sc_t, a.gate_shared, a.up_shared, a.hidden_shared, a.gate_fp8, a.gate_sc, a.up_fp8, a.up_sc,
      a.hidden_fp8_t, a.hidden_sc_t, a.y_shared, a.y_routed) = map(_p, (
         x_fp8_t, x_sc_t, gate_shared, up_shared, hidden_shared, gate_fp8, gate_sc, up_fp8, up_sc, hidden_fp8_t,
         hidden_sc_t, y_shared, y_routed))
-    (a.x_routed, a.x_fp8, a.x_sc, a.gate_bf16, a.up_bf16, a.hidden_fp8, a.hidden_sc) = map(_p, work)
+    (a.x_routed, a.x_fp8, a.x_sc, a.hidden_fp8, a.hidden_sc) = map(_p, work)
     a.skip_down_combine = 1 if skip else 0
     _ck(lib.mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(ctypes.byref(a), _stream()))
     return (x_fp8_t, x_sc_t, gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc, hidden_shared, hidden_fp8_t,
@@ -182,9 +182,9 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
      a.partials) = map(_p, work)
     if a.schedule_capacity > MB:      # later macrobatches are replayed: forward weights and the forward's work buffers
         replay = [w_routed_gate, w_routed_gate_sc, w_routed_up, w_routed_up_sc, torch.empty(MB, H, **bf), *_q(MB, H, dev),
-                  torch.empty(MB, I, **bf), torch.empty(MB, I, **bf), *_q(MB, I, dev)]
-        (a.w_routed_gate, a.w_routed_gate_sc, a.w_routed_up, a.w_routed_up_sc, a.x_routed, a.x_fp8, a.x_sc, a.gate_bf16,
-         a.up_bf16, a.hidden_fp8, a.hidden_sc) = map(_p, replay)
+                  *_q(MB, I, dev)]
+        (a.w_routed_gate, a.w_routed_gate_sc, a.w_routed_up, a.w_routed_up_sc, a.x_routed, a.x_fp8, a.x_sc,
+         a.hidden_fp8, a.hidden_sc) = map(_p, replay)
     _ck(lib.mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(ctypes.byref(a), _stream()))
     return (d_x_shared, d_x_routed, d_gate_shared, d_gate_fp8, d_gate_sc, d_up_shared, d_up_fp8, d_up_sc,
             d_hidden_shared, d_hidden_routed, d_y_fp8, d_y_sc, d_w_shared_gate, d_w_routed_gate, d_w_shared_up,

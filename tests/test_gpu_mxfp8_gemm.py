@@ -80,6 +80,49 @@ def test_mxfp8_gemm_dual_b():
         assert_close("up", (Ad[s:e] @ Ud[gi].T).to(torch.bfloat16), D2[s:e], GEMM_TOL)
 
 
+@pytest.mark.parametrize("limit", [None, 0.5])
+def test_mxfp8_gemm_gate_up_swiglu_quant_equals_the_unfused_sequence(limit):
+    """Mode 3 (SwiGLU + quantisation in the gate/up epilogue) against mode 1 followed by the quantiser: gate and up
+    byte-exact; hidden (computed with the fast division) within one E4M3 step of quantising the bf16 SwiGLU of the
+    same gate / up; scale layouts as the quantiser emits them."""
+    from mok import _C, ops
+    rows_per_group, N, K = [512, 256, 768], 384, 256
+    offs, gob, rows = groups(rows_per_group)
+    g = torch.Generator().manual_seed(33)
+    A = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    Wg = (torch.randn(3, N, K, generator=g) * 0.15).to(torch.bfloat16)
+    Wu = (torch.randn(3, N, K, generator=g) * 0.15).to(torch.bfloat16)
+    Aq, As, _ = quant(A)
+    Gq, Gs, _ = quant(Wg)
+    Uq, Us, _ = quant(Wu)
+    gate = torch.empty(rows, N, dtype=torch.bfloat16, device="cuda")
+    up = torch.empty(rows, N, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm_mxfp8(1, Aq, As, Gq, Gs, gate, group_of_block=gob, G=3, N=N, K=K, B2=Uq, B2_sc=Us, D2=up)
+    u8 = dict(dtype=torch.uint8, device="cuda")
+    outs = [torch.zeros(rows, N, **u8), torch.zeros(rows // 128, N // 128, 32, 16, **u8),
+            torch.zeros(rows, N, **u8), torch.zeros(rows // 128, N // 128, 32, 16, **u8),
+            torch.zeros(rows, N, **u8), torch.zeros(rows // 128, N // 128, 32, 16, **u8),
+            torch.zeros(N, rows, **u8), torch.zeros(N // 128, rows // 128, 32, 16, **u8)]
+    _C.grouped_gemm_mxfp8(3, Aq, As, Gq, Gs, None, group_of_block=gob, G=3, N=N, K=K, B2=Uq, B2_sc=Us,
+                          quantised_outputs=outs, t_rows=rows, swiglu_limit=limit)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0
+    gq, gs, _, _ = ops.mxfp8_quantize(gate, True, False)
+    uq, us, _, _ = ops.mxfp8_quantize(up, True, False)
+    assert torch.equal(outs[0], gq.view(torch.uint8)) and torch.equal(outs[1], gs)
+    assert torch.equal(outs[2], uq.view(torch.uint8)) and torch.equal(outs[3], us)
+    hidden = _C.swiglu_fwd(gate, up, limit)
+    hq, hs, hqt, hst = ops.mxfp8_quantize(hidden, True, True)
+    f8 = torch.float8_e4m3fn
+    for name, got_q, got_s, ref_q, ref_s in (("hidden", outs[4], outs[5], hq, hs), ("hidden^T", outs[6], outs[7], hqt, hst)):
+        same = (got_q == ref_q.view(torch.uint8)).float().mean().item()
+        assert same > 0.995, (name, same)                                   # a different division rounds a few values differently
+        a = O.dequantize(got_q.view(f8).cpu(), got_s.cpu())
+        b = O.dequantize(ref_q.cpu(), ref_s.cpu())
+        assert_close(name, b, a, (0.05, 2e-3))
+        assert (got_s != ref_s).float().mean().item() < 0.01, name
+
+
 @pytest.mark.parametrize("cols_per_group,M,N", [([256], 128, 256), ([512, 0, 256], 256, 384), ([256, 1024], 384, 512)])
 def test_mxfp8_gemm_wgrad(cols_per_group, M, N):
     from mok import _C
