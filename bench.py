@@ -308,6 +308,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--minibatch", type=int, default=0, help="override the workload's minibatch_size (overlap window)")
+    ap.add_argument("--comm-sms", type=int, default=0, help="override fwd/bwd_num_comm_sms (each SM's worth = 8 blocks of the comm kernels)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-mxfp8", action="store_true", help="skip the MXFP8 leg (reported under the key \"mxfp8\")")
     ap.add_argument("--no-torch-baseline", action="store_true",
@@ -342,6 +343,9 @@ def main():
     E_l = E // world
     MB = int(math.ceil((T * K + E_l * 256) / mb) * mb)
     cfg = F.MoKConfig(minibatch_size=mb, macrobatch_size=MB, schedule_capacity_multiplier=mult)
+    if args.comm_sms:
+        cfg = F.MoKConfig(minibatch_size=mb, macrobatch_size=MB, schedule_capacity_multiplier=mult,
+                          fwd_num_comm_sms=args.comm_sms, bwd_num_comm_sms=args.comm_sms)
 
     # ---- synthetic inputs: per-step tensors in pinned host memory + device copies; weights on the device
     g = torch.Generator().manual_seed(1000 + rank)
