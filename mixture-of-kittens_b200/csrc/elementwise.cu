@@ -106,45 +106,68 @@ __global__ void swiglu_bwd_kernel(const uint4* __restrict__ gate, const uint4* _
     }
 }
 
+template <int W>
+__device__ __forceinline__ void ld_words(const uint32_t* p, uint32_t (&v)[W]) {
+    if (W == 8) {
+        asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]),
+                     "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "l"(p));
+    } else {
+        const uint4 q = *reinterpret_cast<const uint4*>(p);
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    }
+}
+template <int W>
+__device__ __forceinline__ void st_words(uint32_t* p, const uint32_t (&v)[W]) {
+    if (W == 8) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+                     "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+    } else {
+        *reinterpret_cast<uint4*>(p) = make_uint4(v[0], v[1], v[2], v[3]);
+    }
+}
+
 // out[t] = bf16(shared[t] + sum_k w[t,k] * routed[t*K+k]), fp32, k ascending
 // (reference: csrc/utils.cuh:43-95 and 140-176; WEIGHTED=false is the backward epilogue).
-template <bool WEIGHTED>
-__global__ void epilogue_kernel(const uint4* __restrict__ shared, const uint4* __restrict__ routed,
-                                const float* __restrict__ weights, uint4* __restrict__ out,
-                                int64_t tokens, int vec_per_row, int topk) {
-    const int64_t n = tokens * vec_per_row;
+// One thread per W packed bf16 pairs of a token (W = 8: 32-byte accesses); the routed rows of up to eight
+// routes are requested before the first one is used, so a thread keeps up to 256 bytes in flight.
+template <bool WEIGHTED, int W>
+__global__ void __launch_bounds__(256, 2) epilogue_kernel(const uint32_t* __restrict__ shared, const uint32_t* __restrict__ routed,
+                                const float* __restrict__ weights, uint32_t* __restrict__ out,
+                                int64_t tokens, int items_per_row, int topk) {
+    const int64_t n = tokens * items_per_row;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int64_t row_words = static_cast<int64_t>(items_per_row) * W;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const int64_t t = i / vec_per_row;
-        const int v = static_cast<int>(i - t * vec_per_row);
-        const uint4 s = shared[i];
-        float acc[8];
-        {
-            const uint32_t* sp = reinterpret_cast<const uint32_t*>(&s);
+        const int64_t t = i / items_per_row;
+        const int v = static_cast<int>(i - t * items_per_row);
+        uint32_t s[W];
+        ld_words<W>(shared + i * W, s);
+        float acc[2 * W];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float2 f = unpack_bf16(sp[k]);
-                acc[2 * k] = f.x;
-                acc[2 * k + 1] = f.y;
-            }
+        for (int k = 0; k < W; ++k) {
+            const float2 f = unpack_bf16(s[k]);
+            acc[2 * k] = f.x;
+            acc[2 * k + 1] = f.y;
         }
-        const uint4* rrow = routed + (t * topk) * vec_per_row + v;
-        for (int k0 = 0; k0 < topk; k0 += 4) {
-            uint4 r[4];
+        const uint32_t* rrow = routed + (t * topk) * row_words + static_cast<int64_t>(v) * W;
+        for (int k0 = 0; k0 < topk; k0 += 8) {
+            uint32_t r[8][W];
+            float w[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (k0 + u < topk) r[u] = rrow[static_cast<int64_t>(k0 + u) * vec_per_row];
+            for (int u = 0; u < 8; ++u)
+                if (k0 + u < topk) {
+                    ld_words<W>(rrow + static_cast<int64_t>(k0 + u) * row_words, r[u]);
+                    w[u] = WEIGHTED ? __ldg(weights + t * topk + k0 + u) : 1.0f;
+                }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 if (k0 + u >= topk) continue;
-                const float w = WEIGHTED ? __ldg(weights + t * topk + k0 + u) : 1.0f;
-                const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r[u]);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float2 f = unpack_bf16(rp[k]);
+                for (int k = 0; k < W; ++k) {
+                    const float2 f = unpack_bf16(r[u][k]);
                     if (WEIGHTED) {
-                        acc[2 * k] = acc[2 * k] + f.x * w;      // mul then add, as the reference does
-                        acc[2 * k + 1] = acc[2 * k + 1] + f.y * w;
+                        acc[2 * k] = acc[2 * k] + f.x * w[u];      // k ascending, as the reference does
+                        acc[2 * k + 1] = acc[2 * k + 1] + f.y * w[u];
                     } else {
                         acc[2 * k] += f.x;
                         acc[2 * k + 1] += f.y;
@@ -152,12 +175,31 @@ __global__ void epilogue_kernel(const uint4* __restrict__ shared, const uint4* _
                 }
             }
         }
-        uint4 o;
-        uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+        uint32_t o[W];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) op[k] = pack_bf16(acc[2 * k], acc[2 * k + 1]);
-        out[i] = o;
+        for (int k = 0; k < W; ++k) o[k] = pack_bf16(acc[2 * k], acc[2 * k + 1]);
+        st_words<W>(out + i * W, o);
     }
+}
+
+template <bool WEIGHTED>
+int launch_epilogue(const void* shared, const void* routed, const float* weights, void* out, int64_t tokens, int64_t hidden, int topk,
+                    cudaStream_t stream) {
+    const bool wide = hidden % 16 == 0 && ((reinterpret_cast<uintptr_t>(shared) | reinterpret_cast<uintptr_t>(routed) |
+                                            reinterpret_cast<uintptr_t>(out)) & 31) == 0;
+    const int items = static_cast<int>(hidden / (wide ? 16 : 8));
+    const int64_t work = tokens * items;
+    int64_t blocks = (work + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    const uint32_t* sp = static_cast<const uint32_t*>(shared);
+    const uint32_t* rp = static_cast<const uint32_t*>(routed);
+    uint32_t* op = static_cast<uint32_t*>(out);
+    if (wide) epilogue_kernel<WEIGHTED, 8><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(sp, rp, weights, op, tokens, items, topk);
+    else epilogue_kernel<WEIGHTED, 4><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(sp, rp, weights, op, tokens, items, topk);
+    MOKB_CUDA(cudaGetLastError());
+    note_launch();
+    return MOKB_OK;
 }
 
 int grid_for(int64_t work_items, int threads) {
@@ -209,13 +251,8 @@ extern "C" int mokb_fwd_epilogue(const void* y_shared, const void* combine_buffe
     TraceScope trace(static_cast<cudaStream_t>(stream), "fwd_epilogue");
     MOKB_REQUIRE(y_shared && combine_buffer && topk_weights && output, "fwd_epilogue: null pointer");
     MOKB_REQUIRE(num_local_tokens > 0 && hidden > 0 && hidden % 8 == 0 && topk > 0 && topk <= 255, "fwd_epilogue: bad sizes");
-    const int vec = static_cast<int>(hidden / 8);
-    epilogue_kernel<true><<<grid_for(num_local_tokens * vec, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(y_shared), static_cast<const uint4*>(combine_buffer), topk_weights,
-        static_cast<uint4*>(output), num_local_tokens, vec, topk);
-    MOKB_CUDA(cudaGetLastError());
-    note_launch();
-    return MOKB_OK;
+    return launch_epilogue<true>(y_shared, combine_buffer, topk_weights, output, num_local_tokens, hidden, topk,
+                                 static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mokb_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* d_x,
@@ -223,11 +260,6 @@ extern "C" int mokb_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_
     TraceScope trace(static_cast<cudaStream_t>(stream), "bwd_epilogue");
     MOKB_REQUIRE(d_x_shared && d_x_routed_buffer && d_x, "bwd_epilogue: null pointer");
     MOKB_REQUIRE(num_local_tokens > 0 && hidden > 0 && hidden % 8 == 0 && topk > 0 && topk <= 255, "bwd_epilogue: bad sizes");
-    const int vec = static_cast<int>(hidden / 8);
-    epilogue_kernel<false><<<grid_for(num_local_tokens * vec, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(d_x_shared), static_cast<const uint4*>(d_x_routed_buffer), nullptr,
-        static_cast<uint4*>(d_x), num_local_tokens, vec, topk);
-    MOKB_CUDA(cudaGetLastError());
-    note_launch();
-    return MOKB_OK;
+    return launch_epilogue<false>(d_x_shared, d_x_routed_buffer, nullptr, d_x, num_local_tokens, hidden, topk,
+                                  static_cast<cudaStream_t>(stream));
 }
