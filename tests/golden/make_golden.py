@@ -140,7 +140,9 @@ def layer_worker(rank, world, ref_path, case, port, ret):
 
 
 def main():
-    ref_path = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of cursor/mixture-of-kittens>")
+    ref_path = sys.argv[1]
     torch.manual_seed(0)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29611")
     dist.init_process_group("gloo", rank=0, world_size=1)
