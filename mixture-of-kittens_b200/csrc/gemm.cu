@@ -430,8 +430,7 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
     int units = sm_count() / NCTA;                       // CTAs, or CTA pairs
     if (tiles_upper_bound < units) units = tiles_upper_bound;
     if (units < 1) return MOKB_OK;
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(units * NCTA));
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = smem;

@@ -459,8 +459,7 @@ int launch(const Maps& m, const FParams& p, int tiles_upper_bound, cudaStream_t 
     int pairs = sm_count() / 2;
     if (tiles_upper_bound < pairs) pairs = tiles_upper_bound;
     if (pairs < 1) return MOKB_OK;
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(pairs * 2));
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;

@@ -326,6 +326,15 @@ def _is_mxfp8(weights) -> bool:
     return isinstance(weights, tuple)
 
 
+def _stage(buffer: torch.Tensor, value: torch.Tensor) -> None:
+    """Copies `value` into the workspace's symmetric `buffer` (reference: mok/functional.py:509-510, 709-711, each
+    marked there as removable).  A caller that produced the value in the buffer itself (it passes `workspace.x_buffer`,
+    `workspace.d_y_buffer` or `workspace.router_weight_buffer` as the argument) pays no copy."""
+    if value.data_ptr() == buffer.data_ptr() and value.shape == buffer.shape and value.stride() == buffer.stride():
+        return
+    buffer.copy_(value)
+
+
 def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x: torch.Tensor,
             router_weights: torch.Tensor, shared_gate_weights: torch.Tensor, shared_up_weights: torch.Tensor,
             shared_down_weights: torch.Tensor, routed_gate_weights, routed_up_weights, routed_down_weights,
@@ -334,8 +343,8 @@ def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x
     [E_l, I, H] / [E_l, H, I], or (fp8, scales) pairs for MXFP8."""
     validate_inputs(config, workspace, schedule, x, router_weights)
     ws = workspace
-    ws.x_buffer.copy_(x)
-    ws.router_weight_buffer.copy_(router_weights)
+    _stage(ws.x_buffer, x)
+    _stage(ws.router_weight_buffer, router_weights)
     _barrier(ws)
     if _is_mxfp8(routed_gate_weights):
         from . import ops_mxfp8
@@ -376,7 +385,7 @@ def recompute_forward_context(config: MoKConfig, workspace: MoKWorkspace, schedu
     if _is_mxfp8(routed_gate_weights) and (len(routed_gate_weights) != 2 or len(routed_up_weights) != 2):
         raise ValueError("MXFP8 routed gate and up weights must be data/scale pairs")
     ws = workspace
-    ws.x_buffer.copy_(x)
+    _stage(ws.x_buffer, x)
     _barrier(ws)
     if _is_mxfp8(routed_gate_weights):
         from . import ops_mxfp8
@@ -414,9 +423,9 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
     if not isinstance(forward_context, MoKForwardContext):
         raise TypeError("forward_context must be a MoKForwardContext")
     ws = workspace
-    ws.d_y_buffer.copy_(grad_output)
-    ws.x_buffer.copy_(x)
-    ws.router_weight_buffer.copy_(router_weights)
+    _stage(ws.d_y_buffer, grad_output)
+    _stage(ws.x_buffer, x)
+    _stage(ws.router_weight_buffer, router_weights)
     _barrier(ws)
     ctx = forward_context
     if _is_mxfp8(routed_gate_weights):

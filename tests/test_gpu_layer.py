@@ -149,3 +149,23 @@ def test_launch_timeline_records_every_phase_in_order():
     first = {t: min(r[3] for r in recs if r[0] == t) for t in set(tags)}
     assert first["schedule"] < first["dispatch"] < first["combine"] < first["fwd_epilogue"] < first["dispatch_scaled"] < first["bwd_epilogue"]
     assert _C.trace_end() == []              # recording has stopped
+
+
+def test_inputs_already_in_the_workspace_buffers_skip_the_staging_copies_and_change_nothing():
+    from mok import _C, functional as F
+    ranks = O.make_inputs(R=1, T=512, H=256, I=256, E=4, K=2, seed=9, routing="gaussian")
+    _, out_ref, _, _, grads_ref, _ = run_layer(ranks[0], 4)
+    group = init_single_rank_group()
+    inp = to_dev(ranks[0])
+    cfg = F.MoKConfig(minibatch_size=256, macrobatch_size=2048)
+    ws = F.get_workspace(cfg, group, device=torch.device("cuda", 0), num_local_tokens=512, hidden_size=256, topk=2)
+    ws.x_buffer.copy_(inp.x)
+    ws.router_weight_buffer.copy_(inp.router_weights)
+    ws.d_y_buffer.copy_(inp.grad_output)
+    sched = F.build_schedule(ws, cfg, inp.top_experts, num_local_experts=4)
+    w = (inp.w_shared_gate, inp.w_shared_up, inp.w_shared_down, inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down)
+    out, ctx = F.forward(cfg, ws, sched, ws.x_buffer, ws.router_weight_buffer, *w)
+    grads = F.backward(cfg, ws, sched, ctx, ws.d_y_buffer, ws.x_buffer, ws.router_weight_buffer, *w)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0
+    assert torch.equal(out, out_ref) and all(torch.equal(a, b) for a, b in zip(grads, grads_ref))
