@@ -86,6 +86,8 @@ struct Sched {
             m_blocks = (p.M + TM - 1) / TM;
             n_blocks = (p.N + BN - 1) / BN;
             total = p.G * m_blocks * n_blocks;
+            // accumulating over no rows at all (an empty macrobatch) leaves every gradient as it is: no tiles
+            if (p.accumulate && p.group_offsets[p.G] == p.group_offsets[0]) total = 0;
         } else {
             int rows = p.num_rows ? *p.num_rows : p.rows_cap;
             if (rows < 0) rows = 0;                 // the row window below never exceeds the tensors (row_end <= rows_cap)

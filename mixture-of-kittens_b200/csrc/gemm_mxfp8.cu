@@ -87,6 +87,8 @@ struct Sched {
             m_blocks = (p.M + TILE_M - 1) / TILE_M;
             n_blocks = (p.N + BN - 1) / BN;
             total = p.G * m_blocks * n_blocks;
+            // accumulating over no token columns at all (an empty macrobatch) leaves every gradient as it is: no tiles
+            if (p.accumulate && p.group_offsets[p.G] == p.group_offsets[0]) total = 0;
         } else {
             int rows = p.num_rows ? *p.num_rows : p.rows_cap;
             if (rows < 0) rows = 0;                 // the row window below never exceeds the tensors (row_end <= rows_cap)
