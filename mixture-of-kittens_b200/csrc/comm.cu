@@ -12,13 +12,34 @@
 namespace mokb {
 namespace {
 
-__device__ __forceinline__ uint4 ld_v4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
 __device__ __forceinline__ void st_v4(void* p, uint4 v) {
     asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// W 32-bit words per access: 4 (16 bytes) or 8 (32 bytes: one full sector, half the instructions)
+template <int W>
+struct Words {
+    uint32_t w[W];
+};
+template <int W>
+__device__ __forceinline__ Words<W> ld_words(const void* p) {
+    Words<W> v;
+    if (W == 8) {
+        asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]),
+                     "=r"(v.w[4]), "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7]) : "l"(p));
+    } else {
+        asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]) : "l"(p));
+    }
+    return v;
+}
+template <int W>
+__device__ __forceinline__ void st_words(void* p, const Words<W>& v) {
+    if (W == 8) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]),
+                     "r"(v.w[4]), "r"(v.w[5]), "r"(v.w[6]), "r"(v.w[7]) : "memory");
+    } else {
+        asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]) : "memory");
+    }
 }
 
 __global__ void all_gather_kernel(const uint4* __restrict__ src, PeerPtrs peers, int R, int rank, int64_t nvec) {
@@ -65,12 +86,12 @@ __global__ void barrier_kernel(PeerPtrs peers, int R, int rank, int32_t* target,
     }
 }
 
-// One warp per schedule row, 16-byte vectors, four loads in flight per lane.
-template <bool SCALE>
+// One warp per schedule row, 16- or 32-byte accesses, four loads in flight per lane.
+template <bool SCALE, int W>
 __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t* __restrict__ peer_rank,
                                 const int32_t* __restrict__ peer_token_idx, const int32_t* __restrict__ num_rows,
                                 int max_rows, int row_begin, int row_end, int R, int row_divisor, int vec_per_row,
-                                uint4* __restrict__ dst, float* __restrict__ row_scale_out) {
+                                Words<W>* __restrict__ dst, float* __restrict__ row_scale_out) {
     int rows = num_rows ? *num_rows : max_rows;
     rows = rows < 0 ? 0 : (rows > max_rows ? 0 : rows);
     rows = min(rows, row_end);
@@ -80,42 +101,45 @@ __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t*
     const int nwarps = gridDim.x * warps_per_block;
     for (int row = row_begin + warp; row < rows; row += nwarps) {
         const int pr = peer_rank[row];
-        uint4* out = dst + static_cast<size_t>(row) * vec_per_row;
+        Words<W>* out = dst + static_cast<size_t>(row) * vec_per_row;
         if (pr < 0 || pr >= R) {      // padding row (or a rank outside the pointer list: treated as padding, never dereferenced)
-            for (int v = lane; v < vec_per_row; v += 32) out[v] = make_uint4(0, 0, 0, 0);
+            Words<W> zero;
+#pragma unroll
+            for (int k = 0; k < W; ++k) zero.w[k] = 0u;
+            for (int v = lane; v < vec_per_row; v += 32) st_words<W>(out + v, zero);
             if (SCALE && lane == 0 && row_scale_out) row_scale_out[row] = 0.f;
             continue;
         }
         const int tok = peer_token_idx[row];
-        const uint4* in = static_cast<const uint4*>(src.p[pr]) + static_cast<size_t>(tok / row_divisor) * vec_per_row;
+        const Words<W>* in = static_cast<const Words<W>*>(src.p[pr]) + static_cast<size_t>(tok / row_divisor) * vec_per_row;
         float w = 1.f;
         if (SCALE) {
             w = static_cast<const float*>(scale_src.p[pr])[tok];
             if (lane == 0 && row_scale_out) row_scale_out[row] = w;
         }
         for (int v0 = lane; v0 < vec_per_row; v0 += 128) {
-            uint4 r[4];
+            Words<W> r[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u)
-                if (v0 + 32 * u < vec_per_row) r[u] = ld_v4(in + v0 + 32 * u);
+                if (v0 + 32 * u < vec_per_row) r[u] = ld_words<W>(in + v0 + 32 * u);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 if (v0 + 32 * u >= vec_per_row) continue;
                 if (SCALE) {
-                    uint32_t* q = reinterpret_cast<uint32_t*>(&r[u]);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const float2 f = unpack_bf16(q[k]);
-                        q[k] = pack_bf16(f.x * w, f.y * w);
+                    for (int k = 0; k < W; ++k) {
+                        const float2 f = unpack_bf16(r[u].w[k]);
+                        r[u].w[k] = pack_bf16(f.x * w, f.y * w);
                     }
                 }
-                out[v0 + 32 * u] = r[u];
+                st_words<W>(out + v0 + 32 * u, r[u]);
             }
         }
     }
 }
 
-__global__ void combine_kernel(const uint4* __restrict__ src, PeerPtrs dst, PeerPtrs val_dst,
+template <int W>
+__global__ void combine_kernel(const Words<W>* __restrict__ src, PeerPtrs dst, PeerPtrs val_dst,
                                const int32_t* __restrict__ peer_rank, const int32_t* __restrict__ peer_token_idx,
                                const int32_t* __restrict__ num_rows, int max_rows, int row_begin, int row_end, int R,
                                int vec_per_row, const float* __restrict__ row_values) {
@@ -130,19 +154,27 @@ __global__ void combine_kernel(const uint4* __restrict__ src, PeerPtrs dst, Peer
         const int pr = peer_rank[row];
         if (pr < 0 || pr >= R) continue;
         const int tok = peer_token_idx[row];
-        const uint4* in = src + static_cast<size_t>(row) * vec_per_row;
-        uint4* out = static_cast<uint4*>(dst.p[pr]) + static_cast<size_t>(tok) * vec_per_row;
+        const Words<W>* in = src + static_cast<size_t>(row) * vec_per_row;
+        Words<W>* out = static_cast<Words<W>*>(dst.p[pr]) + static_cast<size_t>(tok) * vec_per_row;
         for (int v0 = lane; v0 < vec_per_row; v0 += 128) {
-            uint4 r[4];
+            Words<W> r[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u)
-                if (v0 + 32 * u < vec_per_row) r[u] = in[v0 + 32 * u];
+                if (v0 + 32 * u < vec_per_row) r[u] = ld_words<W>(in + v0 + 32 * u);
 #pragma unroll
             for (int u = 0; u < 4; ++u)
-                if (v0 + 32 * u < vec_per_row) st_v4(out + v0 + 32 * u, r[u]);
+                if (v0 + 32 * u < vec_per_row) st_words<W>(out + v0 + 32 * u, r[u]);
         }
         if (row_values && lane == 0) static_cast<float*>(val_dst.p[pr])[tok] = row_values[row];
     }
+}
+
+// 32-byte accesses need 32-byte aligned rows everywhere: the local buffer and every peer's
+bool rows_aligned32(const void* local, const PeerPtrs& peers, int R, int64_t hidden) {
+    if (hidden % 16 != 0 || (reinterpret_cast<uintptr_t>(local) & 31) != 0) return false;
+    for (int r = 0; r < R; ++r)
+        if ((reinterpret_cast<uintptr_t>(peers.p[r]) & 31) != 0) return false;
+    return true;
 }
 
 int fill_peers(PeerPtrs* out, const uint64_t* host, int R, const char* what) {
@@ -225,17 +257,25 @@ int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t
     if (max_rows == 0 || row_begin >= max_rows) return MOKB_OK;
     const int threads = 256;
     if (blocks <= 0) blocks = sm_count() * 8;
-    const int vec = static_cast<int>(hidden / 8);
+    const bool wide = rows_aligned32(dst, src, ep_size, hidden);
+    const int vec = static_cast<int>(hidden / (wide ? 16 : 8));
     if (row_scale_ptrs_host) {
         for (int r = 0; r < ep_size; ++r) {
             MOKB_REQUIRE(row_scale_ptrs_host[r] != 0, "dispatch_rows: null scale pointer for rank %d", r);
             scale.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(row_scale_ptrs_host[r]));
         }
-        dispatch_kernel<true><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
-                                                         row_end, ep_size, row_divisor, vec, static_cast<uint4*>(dst), row_scale_out);
+        if (wide)
+            dispatch_kernel<true, 8><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
+                                                                row_end, ep_size, row_divisor, vec, static_cast<Words<8>*>(dst), row_scale_out);
+        else
+            dispatch_kernel<true, 4><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
+                                                                row_end, ep_size, row_divisor, vec, static_cast<Words<4>*>(dst), row_scale_out);
+    } else if (wide) {
+        dispatch_kernel<false, 8><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
+                                                             row_end, ep_size, row_divisor, vec, static_cast<Words<8>*>(dst), nullptr);
     } else {
-        dispatch_kernel<false><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
-                                                          row_end, ep_size, row_divisor, vec, static_cast<uint4*>(dst), nullptr);
+        dispatch_kernel<false, 4><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
+                                                             row_end, ep_size, row_divisor, vec, static_cast<Words<4>*>(dst), nullptr);
     }
     MOKB_CUDA(cudaGetLastError());
     note_launch();
@@ -261,8 +301,12 @@ int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
         }
     if (max_rows == 0 || row_begin >= max_rows) return MOKB_OK;
     if (blocks <= 0) blocks = sm_count() * 8;
-    combine_kernel<<<blocks, 256, 0, s>>>(static_cast<const uint4*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
-                                          row_begin, row_end, ep_size, static_cast<int>(hidden / 8), row_values);
+    if (rows_aligned32(src, dst, ep_size, hidden))
+        combine_kernel<8><<<blocks, 256, 0, s>>>(static_cast<const Words<8>*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
+                                                 row_begin, row_end, ep_size, static_cast<int>(hidden / 16), row_values);
+    else
+        combine_kernel<4><<<blocks, 256, 0, s>>>(static_cast<const Words<4>*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
+                                                 row_begin, row_end, ep_size, static_cast<int>(hidden / 8), row_values);
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     return MOKB_OK;
