@@ -80,6 +80,29 @@ def main():
                 mchecks[name] = [mx, rel, good]
                 ok &= good
             report["checks"]["case0_mxfp8"] = mchecks
+            # both precisions again with macrobatches of 512 rows: the forward walks several of them, the backward
+            # replays the later ones with a second round of peer pulls
+            cfg_mb = F.MoKConfig(minibatch_size=256, macrobatch_size=512, schedule_capacity_multiplier=1.0)
+            ws_mb = F.get_workspace(cfg_mb, dist.group.WORLD, device=dev, num_local_tokens=T, hidden_size=H, topk=K)
+            assert N > 512
+            for label, wts, bwd_wts, want, tol_abs, tol_rel in (
+                    ("case0_macrobatches_bf16", (inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down),
+                     (inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down), ref, O.BF16_TOLERANCE[0], O.BF16_TOLERANCE[1]),
+                    ("case0_macrobatches_mxfp8", ((qg[0], qg[1]), (qu[0], qu[1]), (qd[0], qd[1])), (qg, qu, (qd[2], qd[3])), refq, 1.0, 0.03)):
+                sched = F.build_schedule(ws_mb, cfg_mb, inp.top_experts, num_local_experts=E_l)
+                out, ctx = F.forward(cfg_mb, ws_mb, sched, inp.x, inp.router_weights, inp.w_shared_gate, inp.w_shared_up,
+                                     inp.w_shared_down, *wts, limit)
+                grads = F.backward(cfg_mb, ws_mb, sched, ctx, inp.grad_output, inp.x, inp.router_weights, inp.w_shared_gate,
+                                   inp.w_shared_up, inp.w_shared_down, *bwd_wts, limit)
+                torch.cuda.synchronize()
+                rchecks = {"status": _C.check_status()}
+                ok &= rchecks["status"] == 0
+                for name, got in zip(names, (out, *grads)):
+                    mx, rel = O.error_stats(want[name], got.cpu())
+                    good = bool(np.isfinite(mx) and mx <= tol_abs and rel <= tol_rel)
+                    rchecks[name] = [mx, rel, good]
+                    ok &= good
+                report["checks"][label] = rchecks
     report["ok"] = bool(ok)
     out_dir = os.environ.get("MOKB_TEST_OUT", "/tmp")
     with open(os.path.join(out_dir, f"multirank_rank{rank}.json"), "w") as f:
