@@ -225,10 +225,16 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
         if (m > 0)
             MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
                                         x_routed, nullptr, nullptr, comm_blocks, s_in));
-        // reverse combine: pull d_y rows, scaled by the route's router weight
-        MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
-                                    d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in));
-        if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));     // the replayed x is in place
+        // reverse combine: pull d_y rows, scaled by the route's router weight, in a few windows
+        const int bchunk = bwd_chunk_rows(hi - lo, m == 0);
+        const int nb = (hi - lo + bchunk - 1) / bchunk;
+        for (int c = 0; c < nb; ++c) {
+            const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
+            MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
+                                        d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in));
+            if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+        }
 
         if (m == 0) {
             // ---- shared expert (overlaps the dispatch above)
@@ -260,11 +266,15 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
             g.has_swiglu_limit = lim; g.swiglu_limit = limv;
             MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
         }
-        g = gemm_base(a->status);
-        g.mode = 2; g.rows_static = hi; g.row_begin = lo; g.row_end = hi;
-        g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
-        g.A = d_y_r; g.lda = H; g.B = a->w_routed_down; g.ldb = I; g.D = d_hidden_r; g.ldd = I;
-        MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+        for (int c = 0; c < nb; ++c) {       // d_hidden = d_y * W_down, window by window behind the pull
+            const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
+            if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
+            g = gemm_base(a->status);
+            g.mode = 2; g.rows_static = hi; g.row_begin = r0; g.row_end = r1;
+            g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
+            g.A = d_y_r; g.lda = H; g.B = a->w_routed_down; g.ldb = I; g.D = d_hidden_r; g.ldd = I;
+            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+        }
         MOKB_TRY(mokb_swiglu_bwd(a->gate_routed, a->up_routed, a->d_hidden_routed, a->d_gate_routed, a->d_up_routed, s.w_row, s.d_w_row,
                                  s.mb_rows + m, MB, I, lim, limv, stream));
         g = gemm_base(a->status);

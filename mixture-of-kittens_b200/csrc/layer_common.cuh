@@ -158,6 +158,14 @@ inline int chunk_rows_for(int MB, int minibatch) {
     return rows;
 }
 
+// The backward pulls d_y in a few large windows, so that the first routed GEMM can start on the rows that have
+// arrived while the rest is still in flight (macrobatch 0 only; later macrobatches are replays of small remainders).
+constexpr int kBwdWindows = 4;
+inline int bwd_chunk_rows(int rows, bool windowed) {
+    if (!windowed || rows <= 0) return rows > 0 ? rows : 256;
+    return static_cast<int>(align256((rows + kBwdWindows - 1) / kBwdWindows));
+}
+
 // Address such that element [row][0] of a [.., ld] buffer holding macrobatch rows from `first_row` on is
 // reached with the schedule's own row index: buffer row = row - first_row.
 template <class T>

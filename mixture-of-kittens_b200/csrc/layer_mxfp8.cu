@@ -262,11 +262,17 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
                                         v.x_routed, nullptr, nullptr, comm_blocks, s_in));
             MOKB_TRY(quantize_impl(v.x_routed, 1, MB, H, s.n_rows, lo, hi, v.x_fp8, v.x_sc, v.x_fp8_t, v.x_sc_t, s_in));
         }
-        // reverse combine: pull d_y rows scaled by the route's router weight, quantise them both ways
-        MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
-                                    d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in));
-        MOKB_TRY(quantize_impl(d_y_r, 1, MB, H, s.n_rows, lo, hi, d_y_fp8, d_y_sc, d_y_fp8_t, d_y_sc_t, s_in));
-        if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));     // the replayed x is in place
+        // reverse combine: pull d_y rows scaled by the route's router weight and quantise them both ways, in a few windows
+        const int bchunk = bwd_chunk_rows(hi - lo, m == 0);
+        const int nb = (hi - lo + bchunk - 1) / bchunk;
+        for (int c = 0; c < nb; ++c) {
+            const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
+            MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
+                                        d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in));
+            MOKB_TRY(quantize_impl(d_y_r, 1, MB, H, s.n_rows, r0, r1, d_y_fp8, d_y_sc, d_y_fp8_t, d_y_sc_t, s_in));
+            if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+        }
 
         if (m == 0) {
             // ---- shared expert (BF16; overlaps the dispatch above)
@@ -296,11 +302,16 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
         if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
         if (m > 0)         // replay gate|up + SwiGLU + quantisation into the context buffers
             MOKB_TRY(gate_up_swiglu(v, wgu, s, lo, hi, hi, MB, E_l, H, I, lim, limv, a->status, stream));
-        mokb_gemm_fp8_args f = fp8_base(a->status);
-        f.mode = 0; f.rows_static = hi; f.row_begin = lo; f.row_end = hi;
-        f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
-        f.A = d_y_fp8; f.A_sc = d_y_sc; f.B = a->w_routed_down_t; f.B_sc = a->w_routed_down_t_sc; f.D = d_hidden_r; f.ldd = I;
-        MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
+        mokb_gemm_fp8_args f;
+        for (int c = 0; c < nb; ++c) {       // d_hidden = d_y_q * WdT_q^T, window by window behind the pull
+            const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
+            if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
+            f = fp8_base(a->status);
+            f.mode = 0; f.rows_static = hi; f.row_begin = r0; f.row_end = r1;
+            f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
+            f.A = d_y_fp8; f.A_sc = d_y_sc; f.B = a->w_routed_down_t; f.B_sc = a->w_routed_down_t_sc; f.D = d_hidden_r; f.ldd = I;
+            MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
+        }
         MOKB_TRY(swiglu_bwd_quant_impl(v.gate_fp8, v.gate_sc, v.up_fp8, v.up_sc, d_hidden_r, MB, I, s.n_rows, lo, hi, lim, limv, w_row,
                                        d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t, d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t,
                                        partials, d_w_row, stream));
