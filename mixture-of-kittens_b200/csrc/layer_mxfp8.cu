@@ -24,7 +24,8 @@ using namespace mokb;
 //
 // Overlap: macrobatch 0 of the forward is cut into row windows (minibatch_size rows): dispatch + quantise of
 // window c+1 and the combine of window c-1 run on the side streams while the GEMMs of window c run on the
-// caller's stream.  In the backward, dispatch / combine overlap the shared expert's BF16 GEMMs and the
+// caller's stream.  In the backward the d_y pull + quantisation comes in four windows behind the shared
+// expert's BF16 GEMMs, the first routed GEMM follows it window by window, and the d_x push overlaps the
 // weight gradients.
 namespace mokb {
 namespace {
