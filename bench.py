@@ -156,11 +156,11 @@ class ClockSampler:
 
 def cpu_oracle_sample(H, I, K, threads_note=True):
     """One fwd+bwd of the CPU oracle on a bounded sample with the workload's per-token cost: K experts,
-    top-K = K (every token visits K experts + the shared one), and as many tokens as make about 10 TFLOP
+    top-K = K (every token visits K experts + the shared one), and as many tokens as make about 15 TFLOP
     (10-20 s on a 16-core host), in multiples of 512."""
     from oracle import mok_oracle as O
     Es = K
-    Ts = int(min(8192, max(512, round(1.0e13 / layer_flops(1, K, H, I) / 512) * 512)))
+    Ts = int(min(8192, max(512, round(1.5e13 / layer_flops(1, K, H, I) / 512) * 512)))
     ranks = O.make_inputs(R=1, T=Ts, H=H, I=I, E=Es, K=K, seed=0, routing="gaussian")
     t0 = time.perf_counter()
     O.layer_forward_backward(ranks)
