@@ -1,6 +1,7 @@
 """Benchmark of the MoE layer hot path: build_schedule + forward + backward per step.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c5|small]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c4|c5|c2r|small]
+                    [--trace FILE] [--comm-sms S] [--minibatch M] [--no-mxfp8] [--no-torch-baseline] [--kernel-only]
 
 For N > 1 launch under torch.distributed.run with one rank per GPU (RANK / LOCAL_RANK /
 WORLD_SIZE / MASTER_* from the environment).  Rank 0 prints ONE JSON line.
@@ -18,6 +19,10 @@ Per-GPU work is fixed as N grows (weak scaling).
              FLOPs per launch / its mean launch time (CUDA events, timed alone) over the
              measured cuBLAS BF16 burst peak of this pool (MEASURED_PEAKS.json)
   cpu_baseline  the CPU oracle (a port of the reference's PyTorch path) on a bounded sample
+  mxfp8      the same step with the routed experts in block-scaled E4M3 (+ its dominant kernel alone and
+             cuBLASLt's block-scaled GEMM measured in the same run as a reference point)
+  comm       (N > 1) dispatch and combine alone: NVLink GB/s per GPU and direction
+  torch_all_to_all  the same layer in stock PyTorch (all_to_all_single + grouped_mm + autograd), BF16
 """
 from __future__ import annotations
 
