@@ -81,25 +81,34 @@ class ClockSampler:
         self.index = index
         self.proc = None
         self.lines: list[str] = []
+        self.error = None
+        self._nvml_handle = None
 
-    def _nvml_loop(self):
-        # NVML from a thread: no process start-up, so even a 200 ms timed region gets samples
+    def _nvml_sample(self):
         import pynvml
         h = self._nvml_handle
         bits = {"hw_slowdown": pynvml.nvmlClocksEventReasonHwSlowdown,
                 "hw_thermal_slowdown": pynvml.nvmlClocksEventReasonHwThermalSlowdown,
                 "sw_thermal_slowdown": pynvml.nvmlClocksEventReasonSwThermalSlowdown,
                 "sw_power_cap": pynvml.nvmlClocksEventReasonSwPowerCap}
+        sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+        mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+        try:
+            pw = pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0
+        except Exception:
+            pw = 0.0
+        r = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+        flags = ["Active" if r & bits[n] else "Not Active" for n in
+                 ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")]
+        self.lines.append(", ".join([str(sm), str(mx), f"{pw:.1f}", *flags]))
+
+    def _nvml_loop(self):
+        # NVML from a thread: no process start-up, so even a 200 ms timed region gets samples
         while not self._stop.is_set():
             try:
-                sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
-                mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
-                pw = pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0
-                r = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
-                flags = ["Active" if r & bits[n] else "Not Active" for n in
-                         ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")]
-                self.lines.append(", ".join([str(sm), str(mx), f"{pw:.1f}", *flags]))
-            except Exception:
+                self._nvml_sample()
+            except Exception as e:
+                self.error = f"{type(e).__name__}: {e}"
                 break
             self._stop.wait(0.02)
 
@@ -114,8 +123,9 @@ class ClockSampler:
             self.thread = threading.Thread(target=self._nvml_loop, daemon=True)
             self.thread.start()
             return self
-        except Exception:
-            pass
+        except Exception as e:
+            self.error = f"{type(e).__name__}: {e}"
+            self._nvml_handle = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
@@ -132,6 +142,11 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         self._stop.set()
+        if not self.lines and self._nvml_handle is not None:
+            try:                       # the sampling thread never ran: one reading right at the end of the region
+                self._nvml_sample()
+            except Exception as e:
+                self.error = f"{type(e).__name__}: {e}"
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -155,7 +170,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "error": self.error}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
