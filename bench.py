@@ -104,12 +104,13 @@ class ClockSampler:
 
     def _nvml_loop(self):
         # NVML from a thread: no process start-up, so even a 200 ms timed region gets samples
-        while not self._stop.is_set():
+        failures = 0
+        while not self._stop.is_set() and failures < 50:
             try:
                 self._nvml_sample()
-            except Exception as e:
+            except Exception as e:          # a transient NVML error must not end the sampling
                 self.error = f"{type(e).__name__}: {e}"
-                break
+                failures += 1
             self._stop.wait(0.02)
 
     def __enter__(self):
