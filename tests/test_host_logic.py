@@ -170,3 +170,19 @@ def test_whole_layer_traces_under_fake_tensors():
             gq[0], gq[1], uq[0], uq[1], *sched, K, None, 28, MB, 256)
         assert len(bm) == 18 and tuple(bm[10].shape) == (MB, H) and bm[10].dtype == torch.float8_e4m3fn
         assert tuple(bm[13].shape) == (E_l, I, H)
+
+
+def test_stage_copies_unless_the_value_already_is_the_buffer():
+    from mok.functional import _stage
+    buf = torch.zeros(4, 8)
+    _stage(buf, buf)                                   # same tensor: nothing to do
+    assert not buf.any()
+    _stage(buf, torch.ones(4, 8))
+    assert torch.equal(buf, torch.ones(4, 8))
+    base = torch.zeros(2, 4, 8)
+    _stage(base[0], base[0])                           # a view that is the buffer
+    _stage(buf, base.view(-1)[:32].view(4, 8))         # same bytes elsewhere: copied
+    assert not buf.any()
+    wide = torch.arange(64.0).view(4, 16)
+    _stage(buf, wide[:, :8])                           # same start address but another stride: copied, not aliased
+    assert torch.equal(buf, wide[:, :8])
