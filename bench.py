@@ -175,13 +175,13 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_oracle_sample(H, I, K, threads_note=True):
+def cpu_oracle_sample(H, I, K, tokens=None):
     """One fwd+bwd of the CPU oracle on a bounded sample with the workload's per-token cost: K experts,
-    top-K = K (every token visits K experts + the shared one), and as many tokens as make about 15 TFLOP
-    (10-20 s on a 16-core host), in multiples of 512."""
+    top-K = K (every token visits K experts + the shared one).  `tokens` defaults to as many as make about
+    15 TFLOP (10-20 s on a 16-core host), in multiples of 512.  Returns (tokens, experts, seconds)."""
     from oracle import mok_oracle as O
     Es = K
-    Ts = int(min(8192, max(512, round(1.5e13 / layer_flops(1, K, H, I) / 512) * 512)))
+    Ts = tokens or int(min(8192, max(512, round(1.5e13 / layer_flops(1, K, H, I) / 512) * 512)))
     ranks = O.make_inputs(R=1, T=Ts, H=H, I=I, E=Es, K=K, seed=0, routing="gaussian")
     t0 = time.perf_counter()
     O.layer_forward_backward(ranks)
@@ -189,26 +189,46 @@ def cpu_oracle_sample(H, I, K, threads_note=True):
     return Ts, Es, dt
 
 
+def host_threads():
+    """All the host cores this process may use.  torch.distributed.run exports OMP_NUM_THREADS=1 to its workers,
+    which would make the CPU arm an order of magnitude slower than the machine allows."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def run_reference_arm(args, rank, world):
-    """The reference's CPU implementation of the path (the oracle port of its PyTorch code) on
-    the host cores: rank 0 only."""
+    """The reference's CPU implementation of the path (the oracle port of its PyTorch code) on the host cores, rank 0
+    only.  Each step is one fwd+bwd on a bounded sample of the workload (same FLOPs per token); the sample is sized
+    from a probe so that warm-up + steps end within about three minutes whatever the core count."""
     if rank != 0:
         return
+    cores = host_threads()
     T, H, I, E, K, mb, mult, routing = WORKLOADS[args.workload]
+    n_samples = args.warmup + args.steps
+    _, _, probe_s = cpu_oracle_sample(H, I, K, tokens=512)          # also pages the host libraries in
+    _, _, probe_s = cpu_oracle_sample(H, I, K, tokens=512)
+    per_sample_s = min(10.0, 180.0 / n_samples)
+    Ts = int(min(8192, max(512, round(per_sample_s / probe_s * 512 / 512) * 512)))
     times = []
-    for i in range(args.warmup + args.steps):
-        Ts, Es, dt = cpu_oracle_sample(H, I, K)
+    for i in range(n_samples):
+        Ts, Es, dt = cpu_oracle_sample(H, I, K, tokens=Ts)
         if i >= args.warmup:
             times.append(dt)
     ms = 1000.0 * sum(times) / len(times)
     value = Ts / (ms / 1000.0)
-    cores = torch.get_num_threads()
     sample = f"{Ts} tokens x top-{K} over {Es} experts + shared expert, H={H}, I={I}, fwd+bwd (same FLOPs per token as the workload)"
+    cfg = workload_config(args.workload, args.gpus)
+    cfg["sample"] = {"tokens": Ts, "experts": Es, "topk": K, "hidden": H, "intermediate": I, "ep_size": 1,
+                     "note": "the CPU arm times this bounded sample, not the full workload; tokens/s is per-token cost"}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.workload, args.gpus),
+        "config": cfg,
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -324,19 +344,196 @@ def workload_config(name, n):
             "staging": "activations are produced in the workspace's symmetric buffers (no staging copies)"}
 
 
+class Problem:
+    """One workload on this rank: inputs in pinned host memory, weights and the workspace on the device, and the
+    BF16 / MXFP8 step functions (build_schedule + forward + backward through mok.functional)."""
+
+    def __init__(self, name, args, rank, world, device, group):
+        from mok import functional as F
+        self.F, self.name, self.rank, self.world, self.device, self.group = F, name, rank, world, device, group
+        T, H, I, E, K, mb, mult, routing = WORKLOADS[name]
+        if args.minibatch:
+            mb = args.minibatch
+        assert E % world == 0
+        E_l = E // world
+        MB = int(math.ceil((T * K + E_l * 256) / mb) * mb)
+        self.T, self.H, self.I, self.E, self.K, self.mb, self.E_l, self.MB = T, H, I, E, K, mb, E_l, MB
+        kw = dict(minibatch_size=mb, macrobatch_size=MB, schedule_capacity_multiplier=mult)
+        if args.comm_sms:
+            kw.update(fwd_num_comm_sms=args.comm_sms, bwd_num_comm_sms=args.comm_sms)
+        self.cfg = F.MoKConfig(**kw)
+        g = torch.Generator().manual_seed(1000 + rank)
+        self.x_h = torch.randn(T, H, generator=g).to(torch.bfloat16).pin_memory()
+        self.gy_h = torch.randn(T, H, generator=g).to(torch.bfloat16).pin_memory()
+        logits = torch.randn(T, E, generator=g)
+        if routing == "zipf":
+            perm = torch.randperm(E, generator=torch.Generator().manual_seed(7))
+            bias = torch.empty(E)
+            bias[perm] = -1.2 * torch.log(torch.arange(1, E + 1, dtype=torch.float32))
+            logits = logits + bias
+        vals, idx = torch.topk(logits, K, dim=1)
+        self.te_h = idx.to(torch.int64).pin_memory()
+        self.rw_h = torch.softmax(vals.float(), -1).pin_memory()
+        gd = torch.Generator(device=device).manual_seed(2000 + rank)
+
+        def w(*shape):
+            t = torch.empty(*shape, dtype=torch.bfloat16, device=device)
+            t.normal_(0.0, 0.02, generator=gd)
+            return t
+        self.shared = (w(I, H), w(I, H), w(H, I))
+        self.routed = (w(E_l, I, H), w(E_l, I, H), w(E_l, H, I))
+        self.ws = F.get_workspace(self.cfg, group, device=device, num_local_tokens=T, hidden_size=H, topk=K)
+        # the step's activations live where the layer wants them: in the workspace's symmetric buffers, so
+        # functional.forward / backward skip their staging copies (the copies the reference marks as removable)
+        self.x_d, self.gy_d, self.rw_d = self.ws.x_buffer, self.ws.d_y_buffer, self.ws.router_weight_buffer
+        self.load_resident()
+        self.te_d = self.te_h.to(device)
+        self.mid = None                     # event recorded between forward and backward when set
+        self.q = None
+
+    def load_resident(self):
+        self.x_d.copy_(self.x_h)
+        self.gy_d.copy_(self.gy_h)
+        self.rw_d.copy_(self.rw_h)
+
+    def flops(self):
+        return layer_flops(self.T, self.K, self.H, self.I)
+
+    def step(self, x=None, te=None, rw=None, gy=None):
+        F = self.F
+        x, te, rw, gy = (self.x_d if x is None else x, self.te_d if te is None else te,
+                         self.rw_d if rw is None else rw, self.gy_d if gy is None else gy)
+        sched = F.build_schedule(self.ws, self.cfg, te, num_local_experts=self.E_l)
+        out, ctx = F.forward(self.cfg, self.ws, sched, x, rw, *self.shared, *self.routed)
+        if self.mid is not None:
+            self.mid.record()
+        grads = F.backward(self.cfg, self.ws, sched, ctx, gy, x, rw, *self.shared, *self.routed)
+        return sched, out, grads
+
+    def quantise_weights(self):
+        from mok import ops
+        if self.q is None:
+            self.q = tuple(ops.mxfp8_quantize(w_, True, True) for w_ in self.routed)
+        return self.q
+
+    def step_mx(self):
+        F = self.F
+        qg, qu, qd = self.quantise_weights()
+        sched = F.build_schedule(self.ws, self.cfg, self.te_d, num_local_experts=self.E_l)
+        out, ctx = F.forward(self.cfg, self.ws, sched, self.x_d, self.rw_d, *self.shared, (qg[0], qg[1]), (qu[0], qu[1]), (qd[0], qd[1]))
+        if self.mid is not None:
+            self.mid.record()
+        return F.backward(self.cfg, self.ws, sched, ctx, self.gy_d, self.x_d, self.rw_d, *self.shared, qg, qu, (qd[2], qd[3]))
+
+
+def make_timer(device):
+    """timed(fn, steps) -> (total ms, [per-step ms]): `steps` calls bracketed by a barrier + synchronize on both sides,
+    CUDA events on the launching stream after every step, each figure the maximum over ranks."""
+    def timed(fn, steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        ev[0].record()
+        for i in range(steps):
+            fn()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([ev[0].elapsed_time(ev[-1])] + [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)],
+                         dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t = t.tolist()
+        return t[0], t[1:]
+    return timed
+
+
+def fwd_bwd_split(prob, fn, reps):
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    prob.mid = ev[1]
+    f, b = [], []
+    for _ in range(reps):
+        torch.cuda.synchronize()
+        ev[0].record()
+        fn()
+        ev[2].record()
+        torch.cuda.synchronize()
+        f.append(ev[0].elapsed_time(ev[1]))
+        b.append(ev[1].elapsed_time(ev[2]))
+    prob.mid = None
+    return statistics.median(f), statistics.median(b)
+
+
+def traced_step(_C, fn):
+    torch.cuda.synchronize()
+    dist.barrier()
+    _C.trace_begin()
+    fn()
+    return _C.trace_end()
+
+
+def in_step_summary(recs, prefix, prob, real_rows, peak_tf):
+    """GEMM time inside one traced step (sum of the launch intervals of this library's GEMM launchers) and the
+    algorithmic TFLOP/s that corresponds to it; the gate/up kind (routed + shared) on its own as well."""
+    gemm = [r for r in recs if r[0].startswith(prefix)]
+    if not gemm:
+        return None
+    busy = sum(r[4] - r[3] for r in gemm)
+    span = max(r[4] for r in recs) - min(r[3] for r in recs)
+    gu = [r for r in gemm if "gate_up" in r[0]]
+    gu_ms = sum(r[4] - r[3] for r in gu)
+    gu_flops = 4.0 * real_rows * prob.H * prob.I + (4.0 * prob.T * prob.H * prob.I if prefix == "gemm_bf16" else 0.0)
+    out = {"step_ms_traced": span, "gemm_launches": len(gemm), "gemm_busy_ms": busy,
+           "gemm_tflops": prob.flops() / (busy / 1000.0) / 1e12, "gate_up_ms": gu_ms,
+           "gate_up_tflops": gu_flops / (gu_ms / 1000.0) / 1e12 if gu_ms > 0 else None,
+           "note": "algorithmic FLOPs (padding and replay not counted) over the GEMM launch intervals of one traced step"}
+    if prefix == "gemm_bf16":
+        out["gemm_frac_of_burst"] = out["gemm_tflops"] / peak_tf
+        out["gate_up_frac_of_burst"] = out["gate_up_tflops"] / peak_tf if out["gate_up_tflops"] else None
+    else:
+        out["note"] += "; the BF16 shared expert's GEMMs are not in gemm_busy_ms, its FLOPs (1/(K+1) of the layer) are"
+    return out
+
+
+def gate_up_bytes(prob, padded_rows, experts_used):
+    """Algorithmic HBM bytes of one routed gate/up + SwiGLU launch: A rows once, both weight matrices of every
+    expert that has rows once, and the three outputs."""
+    a = padded_rows * prob.H * 2
+    wts = experts_used * 2 * prob.I * prob.H * 2
+    outs = 3 * padded_rows * prob.I * 2
+    return {"a_rows": a, "weights": wts, "outputs": outs, "total": a + wts + outs}
+
+
+def run_parity_leg(rank, world, device):
+    """Small multi-rank cases against the CPU oracle on every rank, before anything is timed."""
+    from tests.parity_cases import run_parity, summarise
+    old = torch.get_num_threads()
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0)) // max(1, world)))
+    except AttributeError:
+        pass
+    rep = run_parity(rank, world, device)
+    torch.set_num_threads(old)
+    reports = [None] * world
+    dist.all_gather_object(reports, rep)
+    return summarise(reports)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--minibatch", type=int, default=0, help="override the workload's minibatch_size (overlap window)")
-    ap.add_argument("--comm-sms", type=int, default=0, help="override fwd/bwd_num_comm_sms (each SM's worth = 8 blocks of the comm kernels)")
+    ap.add_argument("--comm-sms", type=int, default=0, help="override fwd/bwd_num_comm_sms")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the parity leg (small cases against the CPU oracle on every rank)")
     ap.add_argument("--no-mxfp8", action="store_true", help="skip the MXFP8 leg (reported under the key \"mxfp8\")")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end legs (sweeps; the line then has no e2e key)")
     ap.add_argument("--no-torch-baseline", action="store_true",
                     help="skip the stock-PyTorch all-to-all + grouped_mm baseline (reported under \"torch_all_to_all\")")
+    ap.add_argument("--no-share", action="store_true", help="skip the 1-GPU leg that runs one rank's EP=8 share of config 2")
     ap.add_argument("--trace", default="", help="write the launch timeline of one BF16 and one MXFP8 step of rank 0 to this file")
     ap.add_argument("--kernel-only", action="store_true", help="time only the dominant GEMM (profiler captures)")
     args = ap.parse_args()
@@ -351,7 +548,7 @@ def main():
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
 
-    from mok import _C, functional as F
+    from mok import _C
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
@@ -359,80 +556,37 @@ def main():
     os.environ.setdefault("MASTER_PORT", "29551")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     group = dist.group.WORLD
+    timed = make_timer(device)
+    peak_tf, peak_gbs, peak_kind = measured_peaks()
 
-    T, H, I, E, K, mb, mult, routing = WORKLOADS[args.workload]
-    if args.minibatch:
-        mb = args.minibatch
-    assert E % world == 0
-    E_l = E // world
-    MB = int(math.ceil((T * K + E_l * 256) / mb) * mb)
-    cfg = F.MoKConfig(minibatch_size=mb, macrobatch_size=MB, schedule_capacity_multiplier=mult)
-    if args.comm_sms:
-        cfg = F.MoKConfig(minibatch_size=mb, macrobatch_size=MB, schedule_capacity_multiplier=mult,
-                          fwd_num_comm_sms=args.comm_sms, bwd_num_comm_sms=args.comm_sms)
+    # ---- parity first: a fast wrong answer is not a result
+    parity = None
+    if not (args.no_parity or args.kernel_only):
+        parity = run_parity_leg(rank, world, device)
+        if not parity["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "n_gpus": world, "parity": parity,
+                                  "error": "the layer's results differ from the CPU oracle's; nothing was timed"}), flush=True)
+            dist.destroy_process_group()
+            raise SystemExit(1)
+        from mok import functional as F
+        F.clear_workspace_cache()
+        torch.cuda.empty_cache()
 
-    # ---- synthetic inputs: per-step tensors in pinned host memory + device copies; weights on the device
-    g = torch.Generator().manual_seed(1000 + rank)
-    x_h = torch.randn(T, H, generator=g).to(torch.bfloat16).pin_memory()
-    gy_h = torch.randn(T, H, generator=g).to(torch.bfloat16).pin_memory()
-    logits = torch.randn(T, E, generator=g)
-    if routing == "zipf":
-        perm = torch.randperm(E, generator=torch.Generator().manual_seed(7))
-        bias = torch.empty(E)
-        bias[perm] = -1.2 * torch.log(torch.arange(1, E + 1, dtype=torch.float32))
-        logits = logits + bias
-    vals, idx = torch.topk(logits, K, dim=1)
-    te_h = idx.to(torch.int64).pin_memory()
-    rw_h = torch.softmax(vals.float(), -1).pin_memory()
-    gd = torch.Generator(device=device).manual_seed(2000 + rank)
-
-    def w(*shape):
-        t = torch.empty(*shape, dtype=torch.bfloat16, device=device)
-        t.normal_(0.0, 0.02, generator=gd)
-        return t
-    wsg, wsu, wsd = w(I, H), w(I, H), w(H, I)
-    wrg, wru, wrd = w(E_l, I, H), w(E_l, I, H), w(E_l, H, I)
-    ws = F.get_workspace(cfg, group, device=device, num_local_tokens=T, hidden_size=H, topk=K)
-    # the step's activations live where the layer wants them: in the workspace's symmetric buffers, so
-    # functional.forward / backward skip their staging copies (the copies the reference marks as removable)
-    x_d, gy_d, rw_d = ws.x_buffer, ws.d_y_buffer, ws.router_weight_buffer
-    x_d.copy_(x_h)
-    gy_d.copy_(gy_h)
-    rw_d.copy_(rw_h)
-    te_d = te_h.to(device)
-
-    marks = {}
-
-    def step(x, te, rw, gy, mark=False):
-        sched = F.build_schedule(ws, cfg, te, num_local_experts=E_l)
-        out, ctx = F.forward(cfg, ws, sched, x, rw, wsg, wsu, wsd, wrg, wru, wrd)
-        if mark:
-            marks["mid"].record()
-        grads = F.backward(cfg, ws, sched, ctx, gy, x, rw, wsg, wsu, wsd, wrg, wru, wrd)
-        return sched, out, grads
-
-    def timed(fn, steps):
-        dist.barrier()
-        torch.cuda.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            fn()
-        end.record()
-        torch.cuda.synchronize()
-        dist.barrier()
-        t = torch.tensor([start.elapsed_time(end)], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    prob = Problem(args.workload, args, rank, world, device, group)
+    T, H, I, E, K, E_l, MB = prob.T, prob.H, prob.I, prob.E, prob.K, prob.E_l, prob.MB
+    ws = prob.ws
+    x_h, gy_h, te_h, rw_h = prob.x_h, prob.gy_h, prob.te_h, prob.rw_h
+    wrg, wru, wrd = prob.routed
 
     if args.kernel_only:
-        sched = F.build_schedule(ws, cfg, te_d, num_local_experts=E_l)
+        sched = prob.F.build_schedule(ws, prob.cfg, prob.te_d, num_local_experts=E_l)
         torch.cuda.synchronize()
-        kern = time_dominant_kernel(_C, sched, x_d, wrg, wru, T, H, I, K, E_l, MB, args.steps, args.warmup, device)
+        kern = time_dominant_kernel(_C, sched, prob.x_d, wrg, wru, T, H, I, K, E_l, MB, args.steps, args.warmup, device)
         if not args.no_mxfp8:
             from mok import ops
             qg, qu = (ops.mxfp8_quantize(w_, True, False) for w_ in (wrg, wru))
-            kern["mxfp8"] = time_dominant_kernel_mxfp8(_C, ops, sched, x_d, qg, qu, T, H, I, E_l, MB, args.steps, args.warmup, device)
+            kern["mxfp8"] = time_dominant_kernel_mxfp8(_C, ops, sched, prob.x_d, qg, qu, T, H, I, E_l, MB, args.steps, args.warmup, device)
         if rank == 0:
             print(json.dumps({"kernel_only": True, **kern}), flush=True)
         dist.destroy_process_group()
@@ -440,38 +594,167 @@ def main():
 
     # ---- device-resident steps
     for _ in range(args.warmup):
-        step(x_d, te_d, rw_d, gy_d)
+        prob.step()
     torch.cuda.synchronize()
     assert _C.check_status() == 0, "device status word set during warm-up"
     launches_before = _C.launch_count()
     with ClockSampler(local_rank) as clocks:
-        total_ms = timed(lambda: step(x_d, te_d, rw_d, gy_d), args.steps)
+        total_ms, per_step = timed(prob.step, args.steps)
     launches = _C.launch_count() - launches_before
     clock_summary = clocks.summary()
     ms_per_step = total_ms / args.steps
+    fwd_ms, bwd_ms = fwd_bwd_split(prob, prob.step, max(2, args.steps // 4))
+    assert _C.check_status() == 0, "device status word set during the timed region"
 
-    # forward / backward split (one extra measured step each, events on the same stream)
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    marks["mid"] = ev[1]
-    fwd_ms, bwd_ms = [], []
-    for _ in range(max(2, args.steps // 2)):
-        torch.cuda.synchronize()
-        ev[0].record()
-        step(x_d, te_d, rw_d, gy_d, mark=True)
-        ev[2].record()
-        torch.cuda.synchronize()
-        fwd_ms.append(ev[0].elapsed_time(ev[1]))
-        bwd_ms.append(ev[1].elapsed_time(ev[2]))
-
+    sched, _, _ = prob.step()
+    real_rows = int((sched.peer_rank >= 0).sum().item())
+    padded_rows = int(sched.num_tokens.item())
+    experts_used = int((sched.tokens_per_expert > 0).sum().item())
     trace_lines = []
-    if args.trace:
-        torch.cuda.synchronize()
-        dist.barrier()
-        _C.trace_begin()
-        step(x_d, te_d, rw_d, gy_d)
-        trace_lines += [("bf16",) + rec for rec in _C.trace_end()]
+    rec_bf16 = traced_step(_C, prob.step)
+    trace_lines += [("bf16",) + rec for rec in rec_bf16]
+    in_step = {"bf16": in_step_summary(rec_bf16, "gemm_bf16", prob, real_rows, peak_tf)}
 
     # ---- end to end: inputs start in pinned host memory, result checksums come back to the host
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(prob, timed, args.steps, _C)
+        prob.load_resident()              # the device-resident legs below read the symmetric buffers again
+
+    # ---- roofline of the dominant kernel
+    kern = time_dominant_kernel(_C, sched, prob.x_d, wrg, wru, T, H, I, K, E_l, MB, 5, 2, device)
+    model = gate_up_bytes(prob, padded_rows, experts_used)
+    traffic, traffic_note = None, None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            tj = json.load(f)
+        ratio = tj.get("gate_up_gemm_dram_over_algorithmic_bytes")
+        if ratio:
+            traffic = ratio * model["total"]
+            traffic_note = (f"algorithmic bytes of this launch x {ratio} = DRAM bytes / algorithmic bytes that ncu measured "
+                            "for this kernel on the 'small' workload (profiles/traffic.json); not a capture of this launch")
+    roofline = {"bound": "tensor", "kernel": "grouped_gemm_kernel<MODE_SWIGLU> (routed gate/up + SwiGLU)",
+                "achieved": kern["tflops"], "peak": peak_tf, "unit": "TFLOP/s", "frac": kern["tflops"] / peak_tf,
+                "peak_source": f"{peak_kind} cuBLAS bf16 burst", "traffic": traffic, "traffic_source": traffic_note,
+                "algorithmic_bytes": model, "launch_ms": kern["ms"], "flops_per_launch": kern["flops_per_launch"],
+                "rows": real_rows, "padded_rows": padded_rows,
+                "tflops_on_padded_rows": kern["tflops"] * padded_rows / max(real_rows, 1)}
+
+    # ---- the communication phases alone: dispatch (row pull) and combine (row push) over all scheduled rows,
+    # every rank at once, CUDA events, max over ranks.  Bytes over NVLink = rows whose home is another rank.
+    comm = None
+    if world > 1:
+        remote = int(((sched.peer_rank >= 0) & (sched.peer_rank != rank)).sum().item())
+        buf = torch.empty(MB, H, dtype=torch.bfloat16, device=device)
+        comm = {"remote_rows": remote, "rows": padded_rows, "nvlink_peak_gbs_per_direction": 900.0, "measured_peer_copy_gbs": 770.0}
+        for name, fn in (
+            ("dispatch", lambda: _C.dispatch_rows(ws.x_buffer_ptrs, sched.peer_rank, sched.peer_token_idx, sched.num_tokens,
+                                                  MB, K, H, buf)),
+            ("combine", lambda: _C.combine_rows(buf, ws.combine_buffer_ptrs, sched.peer_rank, sched.peer_token_idx,
+                                                sched.num_tokens, MB, H)),
+        ):
+            fn()
+            ms = timed(fn, 5)[0] / 5
+            gbs = remote * H * 2 / (ms / 1000.0) / 1e9
+            comm[name] = {"ms": ms, "nvlink_gbs": gbs, "frac_of_900": gbs / 900.0, "frac_of_measured_770": gbs / 770.0}
+        del buf
+
+    # ---- the same step with the routed experts in MXFP8 (weights pre-quantised outside the step, as the reference does)
+    mx = None
+    if not args.no_mxfp8:
+        from mok import ops
+        mx = run_mxfp8_leg(prob, timed, args, _C, ops, sched, real_rows, peak_tf, trace_lines, in_step, rank, device)
+
+    # ---- baseline: the same layer with stock PyTorch ops (all_to_all_single + grouped_mm + autograd), BF16
+    tb = None
+    if not args.no_torch_baseline:
+        try:
+            tb_steps = max(2, min(args.steps, 5))
+            tb_ms = time_torch_all_to_all(group, lambda fn, n: timed(fn, n)[0], tb_steps, 2, prob.x_d, prob.te_d, prob.rw_d, prob.gy_d,
+                                          (*prob.shared, *prob.routed))
+            tb = {"value": T * world / (tb_ms / 1000.0), "unit": "tokens/s", "ms_per_step": tb_ms, "steps": tb_steps,
+                  "tflops_per_gpu": prob.flops() / (tb_ms / 1000.0) / 1e12,
+                  "note": "all_to_all_single (NCCL) + torch._grouped_mm + autograd, BF16, same inputs and weights"}
+        except Exception as e:      # a library baseline must not take the benchmark down
+            tb = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+        torch.cuda.empty_cache()
+
+    # ---- 1 GPU only: one rank's share of the EP=8 run of config 2 (32 local experts), the honest anchor for 1 -> 8 scaling
+    share = None
+    if world == 1 and args.workload == "c2" and not args.no_share:
+        prob.q = None
+        del prob, wrg, wru, wrd, sched, ws, kern
+        torch.cuda.empty_cache()
+        sp = Problem("c2r", args, rank, world, device, group)
+        for _ in range(3):
+            sp.step()
+        s_ms = timed(sp.step, max(5, args.steps // 2))[1]
+        share = {"workload": "c2r: config 2 with 32 routed experts (what one rank holds at EP=8), no NVLink",
+                 "ms_per_step": statistics.median(s_ms), "tflops_per_gpu": sp.flops() / (statistics.median(s_ms) / 1000.0) / 1e12}
+        if not args.no_mxfp8:
+            for _ in range(3):
+                sp.step_mx()
+            m_ms = timed(sp.step_mx, max(5, args.steps // 2))[1]
+            share["mxfp8_ms_per_step"] = statistics.median(m_ms)
+            share["mxfp8_tflops_per_gpu"] = sp.flops() / (statistics.median(m_ms) / 1000.0) / 1e12
+        assert _C.check_status() == 0, "device status word set during the EP=8-share leg"
+        del sp
+        torch.cuda.empty_cache()
+
+    if rank == 0 and args.trace:
+        with open(args.trace, "w") as f:
+            f.write("# leg tag first_row stream begin_ms end_ms\n")
+            for rec in trace_lines:
+                f.write(" ".join(str(v) for v in rec) + "\n")
+
+    if rank == 0:
+        tokens = T * world
+        flops = layer_flops(T, K, H, I)
+        line = {
+            "metric": METRIC, "value": tokens / (ms_per_step / 1000.0), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args.workload, world),
+            "median_ms_per_step": statistics.median(per_step),
+            "tokens_per_s_per_gpu": T / (ms_per_step / 1000.0),
+            "tflops_per_gpu": flops / (ms_per_step / 1000.0) / 1e12,
+            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "roofline": roofline,
+            "in_step": in_step,
+            "gpu_launches": int(launches),
+            "clocks": clock_summary,
+        }
+        if parity is not None:
+            line["parity"] = parity
+        if e2e is not None:
+            line["e2e"] = {k: (tokens / (v / 1000.0) if k == "value" else v) for k, v in e2e.items()}
+        if mx is not None:
+            line["mxfp8"] = mx
+        if comm is not None:
+            line["comm"] = comm
+        if tb is not None:
+            line["torch_all_to_all"] = tb
+        if share is not None:
+            line["ep8_share_1gpu"] = share
+        if world == 1 and not args.no_cpu_baseline:
+            cores = host_threads()
+            Ts, Es, dt = cpu_oracle_sample(H, I, K)
+            line["cpu_baseline"] = {
+                "value": Ts / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+                "sample": f"{Ts} tokens x top-{K} over {Es} experts + shared expert, H={H}, I={I}, one fwd+bwd of the CPU oracle "
+                          f"({dt:.1f} s; same FLOPs per token as the workload)"}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
+def run_e2e(prob, timed, steps, _C):
+    """The step through mok.functional with the four inputs in pinned HOST memory: host -> device copies (straight into
+    the workspace's symmetric buffers) and a device -> host read of two checksums inside the timed region.  Returns
+    {"value": ms per step (converted to tokens/s by the caller), ...}."""
+    device = prob.device
+    x_h, gy_h, te_h, rw_h = prob.x_h, prob.gy_h, prob.te_h, prob.rw_h
+    ws = prob.ws
     x_e, gy_e, rw_e = ws.x_buffer, ws.d_y_buffer, ws.router_weight_buffer        # host -> symmetric buffers directly
     te_e = torch.empty_like(te_h, device=device)
     res_h = torch.empty(2, dtype=torch.float32).pin_memory()
@@ -481,15 +764,15 @@ def main():
         te_e.copy_(te_h, non_blocking=True)
         rw_e.copy_(rw_h, non_blocking=True)
         gy_e.copy_(gy_h, non_blocking=True)
-        _, out, grads = step(x_e, te_e, rw_e, gy_e)
+        _, out, grads = prob.step(x_e, te_e, rw_e, gy_e)
         res = torch.stack([out.float().sum(), grads[0].float().sum()])
         res_h.copy_(res, non_blocking=True)
         torch.cuda.current_stream().synchronize()     # the caller consumes the result on the host
     for _ in range(2):
         e2e_step()
-    e2e_ms = timed(e2e_step, args.steps) / args.steps
+    e2e_ms = timed(e2e_step, steps)[0] / steps
     h2d = sum(t.numel() * t.element_size() for t in (x_h, te_h, rw_h, gy_h))
-    assert _C.check_status() == 0, "device status word set during the timed region"
+    assert _C.check_status() == 0, "device status word set during the end-to-end steps"
 
     # the same with an input prefetcher: step i+1's inputs cross PCIe on a copy stream into a second set of device
     # tensors while step i computes (one host->device copy of all four inputs per step, as above; functional then
@@ -509,7 +792,7 @@ def main():
         slot = pipe["i"] & 1
         torch.cuda.current_stream().wait_event(ready[slot])
         x_s, te_s, rw_s, gy_s = stage[slot]
-        _, out, grads = step(x_s, te_s, rw_s, gy_s)
+        _, out, grads = prob.step(x_s, te_s, rw_s, gy_s)
         prefetch(slot ^ 1)
         res = torch.stack([out.float().sum(), grads[0].float().sum()])
         res_h.copy_(res, non_blocking=True)
@@ -518,148 +801,48 @@ def main():
     prefetch(0)
     for _ in range(2):
         e2e_prefetch_step()
-    e2e_prefetch_ms = timed(e2e_prefetch_step, args.steps) / args.steps
+    e2e_prefetch_ms = timed(e2e_prefetch_step, steps)[0] / steps
     copy_stream.synchronize()
-    x_d.copy_(x_h)              # the device-resident legs below read the symmetric buffers again
-    gy_d.copy_(gy_h)
-    rw_d.copy_(rw_h)
     assert _C.check_status() == 0, "device status word set during the prefetching end-to-end steps"
+    tokens = prob.T * prob.world
+    return {"value": e2e_ms, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8, "ms_per_step": e2e_ms,
+            "with_input_prefetch": {"value": tokens / (e2e_prefetch_ms / 1000.0), "ms_per_step": e2e_prefetch_ms,
+                                    "note": "next step's host->device copies on a copy stream while this step computes"}}
 
-    # ---- roofline of the dominant kernel
-    sched, _, _ = step(x_d, te_d, rw_d, gy_d)
-    kern = time_dominant_kernel(_C, sched, x_d, wrg, wru, T, H, I, K, E_l, MB, 5, 2, device)
-    peak_tf, peak_gbs, peak_kind = measured_peaks()
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            tj = json.load(f)
-        per_flop = tj.get("gate_up_gemm_dram_bytes_per_algorithmic_flop")
-        if per_flop:
-            traffic = per_flop * kern["flops_per_launch"]
-    roofline = {"bound": "tensor", "kernel": "grouped_gemm_kernel<MODE_SWIGLU> (routed gate/up + SwiGLU)",
-                "achieved": kern["tflops"], "peak": peak_tf, "unit": "TFLOP/s", "frac": kern["tflops"] / peak_tf,
-                "peak_source": f"{peak_kind} cuBLAS bf16 burst", "traffic": traffic,
-                "launch_ms": kern["ms"], "flops_per_launch": kern["flops_per_launch"]}
 
-    # ---- the communication phases alone: dispatch (row pull) and combine (row push) over all scheduled rows,
-    # every rank at once, CUDA events, max over ranks.  Bytes over NVLink = rows whose home is another rank.
-    comm = None
-    if world > 1:
-        n_rows = int(sched.num_tokens.item())
-        remote = int(((sched.peer_rank >= 0) & (sched.peer_rank != rank)).sum().item())
-        buf = torch.empty(MB, H, dtype=torch.bfloat16, device=device)
-        comm = {"remote_rows": remote, "rows": n_rows, "nvlink_peak_gbs_per_direction": 900.0, "measured_peer_copy_gbs": 770.0}
-        for name, fn in (
-            ("dispatch", lambda: _C.dispatch_rows(ws.x_buffer_ptrs, sched.peer_rank, sched.peer_token_idx, sched.num_tokens,
-                                                  MB, K, H, buf)),
-            ("combine", lambda: _C.combine_rows(buf, ws.combine_buffer_ptrs, sched.peer_rank, sched.peer_token_idx,
-                                                sched.num_tokens, MB, H)),
-        ):
-            fn()
-            ms = timed(fn, 5) / 5
-            comm[name] = {"ms": ms, "nvlink_gbs": remote * H * 2 / (ms / 1000.0) / 1e9,
-                          "frac_of_900": remote * H * 2 / (ms / 1000.0) / 1e9 / 900.0}
-        del buf
-
-    # ---- the same step with the routed experts in MXFP8 (weights pre-quantised outside the step, as the reference does)
-    mx = None
-    if not args.no_mxfp8:
-        from mok import ops
-        qg, qu, qd = (ops.mxfp8_quantize(w_, True, True) for w_ in (wrg, wru, wrd))
-
-        def step_mx(mark=False):
-            sched = F.build_schedule(ws, cfg, te_d, num_local_experts=E_l)
-            out, ctx = F.forward(cfg, ws, sched, x_d, rw_d, wsg, wsu, wsd, (qg[0], qg[1]), (qu[0], qu[1]), (qd[0], qd[1]))
-            if mark:
-                marks["mid"].record()
-            return F.backward(cfg, ws, sched, ctx, gy_d, x_d, rw_d, wsg, wsu, wsd, qg, qu, (qd[2], qd[3]))
-        for _ in range(args.warmup):
-            step_mx()
-        torch.cuda.synchronize()
-        mx_ms = timed(step_mx, args.steps) / args.steps
-        mx_f, mx_b = [], []
-        for _ in range(2):
-            torch.cuda.synchronize()
-            ev[0].record()
-            step_mx(mark=True)
-            ev[2].record()
-            torch.cuda.synchronize()
-            mx_f.append(ev[0].elapsed_time(ev[1]))
-            mx_b.append(ev[1].elapsed_time(ev[2]))
-        assert _C.check_status() == 0, "device status word set during the MXFP8 steps"
-        if args.trace:
-            torch.cuda.synchronize()
-            dist.barrier()
-            _C.trace_begin()
-            step_mx()
-            trace_lines += [("mxfp8",) + rec for rec in _C.trace_end()]
-        mx = {"value": T * world / (mx_ms / 1000.0), "unit": "tokens/s", "ms_per_step": mx_ms,
-              "tflops_per_gpu": layer_flops(T, K, H, I) / (mx_ms / 1000.0) / 1e12,
-              "fwd_ms": statistics.median(mx_f), "bwd_ms": statistics.median(mx_b),
-              "note": "routed experts in block-scaled E4M3 (tcgen05 mxf8f6f4), shared expert BF16; inputs resident in HBM"}
-        mx["dominant_kernel"] = time_dominant_kernel_mxfp8(_C, ops, sched, x_d, qg, qu, T, H, I, E_l, MB, 5, 2, device)
-        del qg, qu, qd
-        if rank == 0:
-            lib = cublaslt_mxfp8_tflops(device)
-            if isinstance(lib, tuple):
-                mx["cublaslt_mxfp8_tflops"] = {"burst": lib[0], "sustained": lib[1],
-                                               "note": "8192^3 torch._scaled_mm with E8M0 block scales, measured in this run"}
-            else:
-                mx["cublaslt_mxfp8_tflops"] = {"unavailable": lib}
-
-    # ---- baseline: the same layer with stock PyTorch ops (all_to_all_single + grouped_mm + autograd), BF16
-    tb = None
-    if not args.no_torch_baseline:
-        try:
-            tb_steps = max(2, min(args.steps, 5))
-            tb_ms = time_torch_all_to_all(group, timed, tb_steps, 2, x_d, te_d, rw_d, gy_d, (wsg, wsu, wsd, wrg, wru, wrd))
-            tb = {"value": T * world / (tb_ms / 1000.0), "unit": "tokens/s", "ms_per_step": tb_ms, "steps": tb_steps,
-                  "tflops_per_gpu": layer_flops(T, K, H, I) / (tb_ms / 1000.0) / 1e12,
-                  "note": "all_to_all_single (NCCL) + torch._grouped_mm + autograd, BF16, same inputs and weights"}
-        except Exception as e:      # a library baseline must not take the benchmark down
-            tb = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
-        torch.cuda.empty_cache()
-
-    if rank == 0 and args.trace:
-        with open(args.trace, "w") as f:
-            f.write("# leg tag first_row stream begin_ms end_ms\n")
-            for rec in trace_lines:
-                f.write(" ".join(str(v) for v in rec) + "\n")
-
+def run_mxfp8_leg(prob, timed, args, _C, ops, sched, real_rows, peak_tf, trace_lines, in_step, rank, device):
+    T, H, I, K, E_l, MB = prob.T, prob.H, prob.I, prob.K, prob.E_l, prob.MB
+    for _ in range(args.warmup):
+        prob.step_mx()
+    torch.cuda.synchronize()
+    total, per_step = timed(prob.step_mx, args.steps)
+    mx_ms = total / args.steps
+    mx_f, mx_b = fwd_bwd_split(prob, prob.step_mx, 2)
+    assert _C.check_status() == 0, "device status word set during the MXFP8 steps"
+    rec = traced_step(_C, prob.step_mx)
+    trace_lines += [("mxfp8",) + r for r in rec]
+    in_step["mxfp8"] = in_step_summary(rec, "gemm_mxfp8", prob, real_rows, peak_tf)
+    mx = {"value": T * prob.world / (mx_ms / 1000.0), "unit": "tokens/s", "ms_per_step": mx_ms,
+          "median_ms_per_step": statistics.median(per_step),
+          "tflops_per_gpu": prob.flops() / (mx_ms / 1000.0) / 1e12, "fwd_ms": mx_f, "bwd_ms": mx_b,
+          "note": "routed experts in block-scaled E4M3 (tcgen05 mxf8f6f4), shared expert BF16; inputs resident in HBM"}
+    qg, qu, _ = prob.quantise_weights()
+    mx["dominant_kernel"] = time_dominant_kernel_mxfp8(_C, ops, sched, prob.x_d, qg, qu, T, H, I, E_l, MB, 5, 2, device)
+    prob.q = None
+    del qg, qu
+    torch.cuda.empty_cache()
     if rank == 0:
-        tokens = T * world
-        flops = layer_flops(T, K, H, I)
-        line = {
-            "metric": METRIC, "value": tokens / (ms_per_step / 1000.0), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(args.workload, world),
-            "tokens_per_s_per_gpu": T / (ms_per_step / 1000.0),
-            "tflops_per_gpu": flops / (ms_per_step / 1000.0) / 1e12,
-            "fwd_ms": statistics.median(fwd_ms), "bwd_ms": statistics.median(bwd_ms),
-            "roofline": roofline,
-            "e2e": {"value": tokens / (e2e_ms / 1000.0), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": 8, "ms_per_step": e2e_ms,
-                    "with_input_prefetch": {"value": tokens / (e2e_prefetch_ms / 1000.0), "ms_per_step": e2e_prefetch_ms,
-                                            "note": "next step's host->device copies on a copy stream while this step computes"}},
-            "gpu_launches": int(launches),
-            "clocks": clock_summary,
-        }
-        if mx is not None:
-            line["mxfp8"] = mx
-        if comm is not None:
-            line["comm"] = comm
-        if tb is not None:
-            line["torch_all_to_all"] = tb
-        if world == 1 and not args.no_cpu_baseline:
-            Ts, Es, dt = cpu_oracle_sample(H, I, K)
-            line["cpu_baseline"] = {
-                "value": Ts / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                "sample": f"{Ts} tokens x top-{K} over {Es} experts + shared expert, H={H}, I={I}, one fwd+bwd of the CPU oracle "
-                          f"({dt:.1f} s; same FLOPs per token as the workload)"}
-        print(json.dumps(line), flush=True)
-    dist.destroy_process_group()
+        lib = cublaslt_mxfp8_tflops(device)
+        if isinstance(lib, tuple):
+            mx["cublaslt_mxfp8_tflops"] = {"burst": lib[0], "sustained": lib[1],
+                                           "note": "8192^3 torch._scaled_mm with E8M0 block scales, measured in this run"}
+            mx["roofline"] = {"bound": "tensor", "kernel": mx["dominant_kernel"]["kernel"], "achieved": mx["dominant_kernel"]["tflops"],
+                              "peak": lib[0], "unit": "TFLOP/s", "frac": mx["dominant_kernel"]["tflops"] / lib[0],
+                              "peak_source": "cuBLASLt block-scaled E4M3 8192^3 GEMM (torch._scaled_mm), burst of 20 calls, measured in "
+                                             "this run: MEASURED_PEAKS.json has no FP8 figure"}
+        else:
+            mx["cublaslt_mxfp8_tflops"] = {"unavailable": lib}
+    return mx
 
 
 def time_dominant_kernel(_C, sched, x, wrg, wru, T, H, I, K, E_l, MB, steps, warmup, device):

@@ -12,7 +12,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "mok", "libmok_b200.so")
-SOURCES = ["host.cu", "schedule.cu", "comm.cu", "elementwise.cu", "quantize.cu", "gemm.cu", "gemm_mxfp8.cu", "layer.cu", "layer_mxfp8.cu", "noalloc.cu"]
+SOURCES = ["host.cu", "schedule.cu", "comm.cu", "elementwise.cu", "quantize.cu", "gemm.cu", "gemm_mxfp8.cu", "layer.cu", "layer_mxfp8.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "--warn-on-spills"]
 
@@ -22,7 +22,11 @@ def nvcc() -> str:
 
 
 def sources() -> list[str]:
-    return [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
+    paths = [os.path.join(CSRC, s) for s in SOURCES]
+    missing = [p for p in paths if not os.path.exists(p)]
+    if missing:
+        raise FileNotFoundError(f"build.py lists sources that do not exist: {missing}")
+    return paths
 
 
 def stale() -> bool:

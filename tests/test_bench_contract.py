@@ -30,3 +30,38 @@ def test_reference_arm_runs_on_rank_zero_only():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1"],
                        capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
     assert r.returncode == 0 and not [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+
+
+def test_reference_arm_uses_all_host_cores_under_a_launcher_that_pins_one_thread():
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm must not inherit that
+    env = dict(os.environ, RANK="0", WORLD_SIZE="2", LOCAL_RANK="0", OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+                        "--warmup", "3", "--workload", "c1"], capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    d = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][0])
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+    sample = d["config"]["sample"]
+    assert sample["tokens"] % 512 == 0 and sample["tokens"] >= 512 and sample["hidden"] == 1024 and sample["ep_size"] == 1
+    assert d["n_gpus"] == 2
+
+
+def test_parity_summary_and_byte_model():
+    import types
+    sys.path.insert(0, ROOT)
+    import bench
+    from tests.parity_cases import summarise
+    good = {"rank": 0, "ok": True, "checks": {"case0_gaussian_bf16": {"status": 0, "schedule_exact": True, "output": [0.1, 1e-3, True]},
+                                               "case0_gaussian_mxfp8": {"status": 0, "output": [0.3, 2e-2, True]}}}
+    bad = {"rank": 1, "ok": False, "checks": {"case0_gaussian_bf16": {"status": 0, "schedule_exact": False, "output": [0.7, 2e-3, False]}}}
+    s = summarise([good])
+    assert s["ok"] and s["cases"] == 2 and s["worst"]["output"] == [0.1, 1e-3] and s["worst"]["output_mxfp8"] == [0.3, 2e-2]
+    s = summarise([good, bad])
+    assert not s["ok"] and s["ranks"] == 2 and s["worst"]["output"][0] == 0.7
+    assert set(s["failed"]) == {"rank1/case0_gaussian_bf16/schedule_exact", "rank1/case0_gaussian_bf16/output"}
+    prob = types.SimpleNamespace(H=2048, I=1024, T=4096, K=4, flops=lambda: 18.0 * 4096 * 5 * 2048 * 1024)
+    m = bench.gate_up_bytes(prob, 20224, 32)
+    assert m["total"] == 20224 * 2048 * 2 + 32 * 2 * 1024 * 2048 * 2 + 3 * 20224 * 1024 * 2
+    recs = [("gemm_bf16_gate_up_swiglu", 0, 0, 0.0, 1.0), ("dispatch", 0, 1, 0.0, 0.5), ("gemm_bf16_nt", 0, 0, 1.0, 2.0)]
+    ins = bench.in_step_summary(recs, "gemm_bf16", prob, 16384, 1000.0)
+    assert ins["gemm_launches"] == 2 and ins["gemm_busy_ms"] == 2.0 and ins["gate_up_ms"] == 1.0 and ins["step_ms_traced"] == 2.0
+    assert abs(ins["gate_up_tflops"] - 4.0 * (16384 + 4096) * 2048 * 1024 / 1e-3 / 1e12) < 1e-6

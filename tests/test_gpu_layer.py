@@ -50,7 +50,9 @@ def run_layer(inp_cpu, E_l, *, limit=None, MB=None, mb=256, recompute=False, mul
     dict(T=1024, H=1024, I=512, E=8, K=2, routing="router", limit=None),     # config 1 of the benchmark
     dict(T=512, H=512, I=384, E=6, K=3, routing="gaussian", limit=2.0),      # I not a multiple of 256, clamped
     dict(T=512, H=256, I=128, E=16, K=1, routing="zipf", limit=None, mult=9.0, MB=4608),   # mostly padding, top-1
-], ids=["min", "c1", "i384_clamp", "zipf_top1"])
+    dict(T=512, H=1280, I=1408, E=8, K=6, routing="gaussian", limit=None),   # config 5's expert width (11 * 128) and top-6
+    dict(T=512, H=1024, I=1536, E=16, K=8, routing="zipf", limit=None, mult=1.0),   # config 4: Zipf routing, multiplier 1.0
+], ids=["min", "c1", "i384_clamp", "zipf_top1", "c5_width", "c4_zipf"])
 def test_layer_bf16_vs_oracle(shape):
     shape = dict(shape)
     limit, mult, MB = shape.pop("limit"), shape.pop("mult", 0.5), shape.pop("MB", None)

@@ -14,13 +14,13 @@ GRAD_KEYS = ("d_x", "d_router_weights", "d_w_routed_gate", "d_w_routed_up", "d_w
              "d_w_shared_gate", "d_w_shared_up", "d_w_shared_down")
 
 
-def run_mxfp8(inp_cpu, E_l, *, limit=None, recompute=False, MB=None, mb=256):
+def run_mxfp8(inp_cpu, E_l, *, limit=None, recompute=False, MB=None, mb=256, mult=0.5):
     from mok import _C, functional as F, ops
     group = init_single_rank_group()
     inp = to_dev(inp_cpu)
     T, H = inp.x.shape
     K = inp.top_experts.shape[1]
-    cfg = F.MoKConfig(minibatch_size=mb, macrobatch_size=MB or T * K * 2)
+    cfg = F.MoKConfig(minibatch_size=mb, macrobatch_size=MB or T * K * 2, schedule_capacity_multiplier=mult)
     ws = F.get_workspace(cfg, group, device=torch.device("cuda", 0), num_local_tokens=T, hidden_size=H, topk=K)
     sched = F.build_schedule(ws, cfg, inp.top_experts, num_local_experts=E_l)
     gq, gs, gtq, gts = ops.mxfp8_quantize(inp.w_routed_gate, True, True)
@@ -42,16 +42,18 @@ def run_mxfp8(inp_cpu, E_l, *, limit=None, recompute=False, MB=None, mb=256):
     dict(T=512, H=256, I=256, E=4, K=2, routing="router", limit=None),
     dict(T=1024, H=1024, I=512, E=8, K=2, routing="router", limit=None),      # config 3 of the benchmark (MXFP8 of config 1)
     dict(T=512, H=512, I=384, E=6, K=3, routing="gaussian", limit=2.0),
-], ids=["min", "c3", "i384_clamp"])
+    dict(T=512, H=1280, I=1408, E=8, K=6, routing="gaussian", limit=None),   # config 5's expert width (11 * 128) and top-6
+    dict(T=512, H=1024, I=1536, E=16, K=8, routing="zipf", limit=None, mult=1.0),   # config 4: Zipf routing, multiplier 1.0
+], ids=["min", "c3", "i384_clamp", "c5_width", "c4_zipf"])
 def test_layer_mxfp8_vs_oracle(shape):
     shape = dict(shape)
-    limit = shape.pop("limit")
+    limit, mult = shape.pop("limit"), shape.pop("mult", 0.5)
     ranks = O.make_inputs(R=1, seed=3, **shape)
     # the reference's tolerance is absolute; use its gradient scale (d_output ~ N(0,1) * H^-0.5, tests/utils.py:93)
     ranks[0].grad_output = (ranks[0].grad_output.float() * shape["H"] ** -0.5).to(torch.bfloat16)
     ref = O.layer_forward_backward(ranks, swiglu_limit=limit, mxfp8=True)[0]
     ref_bf16 = O.layer_forward_backward(ranks, swiglu_limit=limit)[0]
-    sched, out, ctx, _, grads, ws = run_mxfp8(ranks[0], shape["E"], limit=limit)
+    sched, out, ctx, _, grads, ws = run_mxfp8(ranks[0], shape["E"], limit=limit, mult=mult)
     N = int(ref["num_tokens"][0])
     # x_routed^T quantised along tokens: exact copy + byte-exact codec
     xq, xs, _, _ = O.mxfp8_quantize(ref["x_routed"].T.contiguous(), True, False)

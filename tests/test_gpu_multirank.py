@@ -1,4 +1,4 @@
-"""Expert parallelism over real GPUs (2, or 4 when present): launches tests/multirank_worker.py under
+"""Expert parallelism over real GPUs (2, 4 and 8 when present): launches tests/multirank_worker.py under
 torch.distributed.run and checks every rank's report.  Skipped on a single-GPU machine."""
 import json
 import os
@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_layer_over_peer_gpus(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

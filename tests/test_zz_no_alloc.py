@@ -46,6 +46,29 @@ def test_noalloc_schedule_matches_schedule_on_two_calls_in_a_row():
         assert int(got[2].item()) > 0 and int((got[0] >= 0).sum().item()) > 0
 
 
+@pytest.mark.parametrize("R,T,K,E_l,factor", [(8, 4096, 8, 128, 2), (1, 16384, 8, 1024, 4)], ids=["ep8_1024_experts", "ep1_1024_experts"])
+def test_noalloc_schedule_at_its_expert_limit_matches_the_oracle(R, T, K, E_l, factor):
+    """At 1024 experts the per-column counters of the usual geometry (2 or 8 row chunks per column) would need 8 or
+    32 MiB; the entry point falls back to fewer chunks until they fit its 4 MiB area.  The schedule must not depend
+    on that choice: it has to equal the CPU oracle's and mokb_schedule's (which keeps the usual geometry) bit for bit."""
+    from mok import _C
+    from oracle import mok_oracle as O
+    topk = G.schedule_topk(R, T, K, E_l, "random", seed=23)
+    rank = R - 1
+    C = T * K * factor
+    ref, got = both(_C, topk, E_l, C, rank)
+    want = O.schedule(topk, E_l, C, rank)
+    n = int(want[2][0])
+    for name, w, a, b in zip(("peer_rank", "peer_token_idx", "num_tokens", "tokens_per_expert"), want, ref, got):
+        assert torch.equal(a, b), f"{name} differs between mokb_schedule and mokb_schedule_noalloc"
+        w, b = torch.from_numpy(np.asarray(w)), b.cpu()
+        if name == "peer_token_idx":                    # defined on scheduled rows only (padding rows: -1 here)
+            real = torch.from_numpy(np.asarray(want[0])[:n] >= 0)
+            assert torch.equal(w[:n][real], b[:n][real]), name
+        else:
+            assert torch.equal(w.to(b.dtype), b), f"{name} differs from the oracle"
+
+
 def test_noalloc_schedule_rejects_sizes_beyond_its_limit():
     from mok import _C
     topk = torch.zeros(4, 512, 1, dtype=torch.int32, device="cuda")
