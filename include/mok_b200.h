@@ -17,10 +17,13 @@
  *     (mok/functional.py:224 of the reference);
  *   - the caller allocates every output (the reference's callee-allocates
  *     convention, csrc/megakernel/forward.cuh:345-368, lives in the Python shim);
- *   - `status` is a device int32 that kernels set to a MOKB_ST_* code instead of
- *     trapping or spinning for ever (the reference traps on schedule overflow,
- *     csrc/scheduler.cuh:86, and spins without bound, csrc/utils.cuh:274-277).
- *     It is only ever written when something went wrong; the caller zeroes it.
+ *   - `status` points to FOUR device int32 words.  Kernels set word 0 to a
+ *     MOKB_ST_* code instead of trapping or spinning for ever (the reference traps
+ *     on schedule overflow, csrc/scheduler.cuh:86, and spins without bound,
+ *     csrc/utils.cuh:274-277); after MOKB_ST_FLAG_TIMEOUT words 1..3 say which wait
+ *     ran out (1 = a GEMM on a dispatch window, 2 = a down tile on its gate/up tiles,
+ *     3 = combine on a GEMM window; the counter's index; value seen << 16 | target).
+ *     The words are only ever written when something went wrong; the caller zeroes them.
  */
 #ifndef MOK_B200_H
 #define MOK_B200_H
@@ -45,6 +48,7 @@ extern "C" {
 #define MOKB_ST_BARRIER_TIMEOUT 2     /* a peer never arrived at barrier_all */
 #define MOKB_ST_PIPELINE_TIMEOUT 3    /* an mbarrier wait inside a GEMM ran out */
 #define MOKB_ST_MACROBATCH_OVERFLOW 4 /* reserved: every layer entry point splits the rows into macrobatches */
+#define MOKB_ST_FLAG_TIMEOUT 5        /* a wait on a counter that another kernel or CTA raises ran out (2 s) */
 
 const char* mokb_last_error(void);
 /* Compute capability major*10+minor of the current device, or a negative error. */
@@ -150,7 +154,9 @@ typedef struct {
     void *gate_shared, *up_shared, *hidden_shared;   /* [T, I] */
     void *gate_routed, *up_routed, *hidden_routed;   /* [MB, I] */
     void *y_shared;                            /* [T, H] */
-    void *y_routed;                            /* [MB, H]; may be NULL when skip_down_combine */
+    void *y_routed;                            /* [MB, H], optional: the rows go to the peers' combine buffers from the down
+                                                  GEMM's epilogue; given, they are stored here as well (the reference's
+                                                  staging buffer, read by nothing afterwards) */
     /* scratch: mokb_layer_scratch_bytes() bytes, no initialisation needed */
     void* scratch;
     int32_t* status;
@@ -177,7 +183,7 @@ typedef struct {
     /* saved forward context (macrobatch 0) */
     const void *x_routed, *gate_shared, *gate_routed, *up_shared, *up_routed, *hidden_shared, *hidden_routed;
     /* outputs (ops.py:1169-1184 of the reference) */
-    void *d_x_shared, *d_x_routed;             /* [T,H] [MB,H] */
+    void *d_x_shared, *d_x_routed;             /* [T,H] [MB,H]; d_x_routed optional, as y_routed in the forward */
     void *d_gate_shared, *d_gate_routed, *d_up_shared, *d_up_routed;   /* [T,I] [MB,I] */
     void *d_hidden_shared, *d_hidden_routed;   /* [T,I] [MB,I] */
     void *d_y_routed;                          /* [MB,H] */
@@ -292,7 +298,19 @@ int mokb_struct_sizes_mxfp8(int* out, int n);
  *   mode 1: same as 0 with B = gate and B2 = up   -> D = gate, D2 = up, D3 = SwiGLU(gate, up), all [rows, N]
  *   mode 2: B [G, K, N] (N contiguous; "dgrad")   -> D [rows, N]; if A2/B2 given, D = A*B + A2*B2
  * Weight-gradient GEMM (mode 3): for each group g with rows [off[g], off[g+1]) of
- * A [rows, M] and B [rows, N]: D[g] [M, N] = A_g^T * B_g (zero if the group is empty). */
+ * A [rows, M] and B [rows, N]: D[g] [M, N] = A_g^T * B_g (zero if the group is empty).
+ *   mode 4: mode 1 followed by the down projection of the same rows, D4 [rows, N2] = D3 * B3[g]^T with B3 [G, N2, N],
+ *           in ONE persistent launch that walks the rows window by window (window_rows rows each): all gate/up tiles of
+ *           a window, then all its down tiles -- the task order of the reference's forward megakernel
+ *           (csrc/megakernel/forward.cuh:146-266).  N2 = 0 leaves the down projection out.
+ * Counters (modes 0, 1, 2, 4; device int32 arrays that the caller zeroes; the reference's barrier_wait / barrier_arrive,
+ * csrc/megakernel/utils.cuh:1-13, with a 2 s limit after which the kernel sets MOKB_ST_FLAG_TIMEOUT and exits):
+ *   win_ready[w] -- awaited (>= win_ready_target) before the first A rows of window w (counted from row_begin) are read;
+ *                   mokb_dispatch_rows_window adds 1 per block when its rows have landed;
+ *   blk_done[b]  -- mode 4, required, [rows / 256 from row_begin]: the kernel's own count of finished gate/up tiles per
+ *                   256-row block, awaited by its down tiles;
+ *   win_done[w]  -- mode 4, optional: 8 arrivals per finished down tile of window w; mokb_combine_rows_window waits
+ *                   for (rows of the window / 256) * (N2 / 256) * 8 of them before it reads D4. */
 typedef struct {
     int mode;
     int rows_static;            /* row capacity of A and D; the row count when num_rows is NULL */
@@ -310,6 +328,27 @@ typedef struct {
     float swiglu_limit;
     int accumulate;             /* mode 3: D[g] += result (read, add in fp32, round to bf16); empty groups are left alone */
     int32_t* status;
+    /* mode 4 and the counters */
+    const void* B3;
+    void* D4;
+    int N2, ldb3, ldd4;
+    int window_rows;
+    const int32_t* win_ready;
+    int win_ready_target;
+    int32_t* blk_done;
+    int32_t* win_done;
+    /* push (modes 0, 2 and the down projection of mode 4): combine without a combine kernel
+     * (dispatch_combine.cuh:152-266 of the reference pushes the rows from a staging buffer).  Row r of the result goes
+     * to row push_idx[r] of rank push_rank[r]'s buffer (leading dimension ldd, mode 4: ldd4) with plain peer stores from
+     * the GEMM's epilogue; rows whose rank is outside [0, push_ep_size) go nowhere.  With push_values, the first column
+     * tile also writes push_value_ptrs[rank][push_idx[r]] = push_values[r] (router-weight gradients).  D (mode 4: D4)
+     * may then be NULL; given, the rows are stored there as well. */
+    const uint64_t* push_ptrs_host;
+    int push_ep_size;
+    const int32_t* push_rank;
+    const int32_t* push_idx;
+    const float* push_values;
+    const uint64_t* push_value_ptrs_host;
 } mokb_gemm_args;
 int mokb_grouped_gemm_bf16(const mokb_gemm_args* args, void* stream);
 
@@ -363,6 +402,28 @@ int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
                       const int32_t* peer_rank, const int32_t* peer_token_idx,
                       const int32_t* num_rows, int max_rows, int64_t hidden,
                       const float* row_values, const uint64_t* value_ptrs_host, void* stream);
+
+/* The same two kernels on a row window [row_begin, min(row_end, *num_rows)), on `blocks` CTAs (0 = default), tied to a
+ * GEMM that runs at the same time by counters instead of launch order (dispatch_combine.cuh:1-266 runs them as tasks of
+ * the megakernel, synchronised through csrc/megakernel/utils.cuh:1-13):
+ *   done_counter  -- optional; every block of the dispatch launch adds 1 once its rows have landed.  A GEMM given this
+ *                    word as win_ready[w] with win_ready_target = the launch's block count (`blocks`, or
+ *                    mokb_comm_default_blocks() when blocks is 0) starts window w only then.
+ *   wait_counter  -- optional; the combine launch first waits (2 s at most, then MOKB_ST_FLAG_TIMEOUT in `status` and
+ *                    no row is copied) until it holds ((rows of the window) / 256) * arrivals_per_row_block arrivals:
+ *                    win_done[w] of a mode-4 GEMM with arrivals_per_row_block = (N2 / 256) * 8.  row_begin must be a
+ *                    multiple of 256. */
+int mokb_comm_default_blocks(void);
+int mokb_dispatch_rows_window(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
+                              const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin,
+                              int row_end, int row_divisor, int64_t hidden, void* dst,
+                              const uint64_t* row_scale_ptrs_host, float* row_scale_out, int blocks,
+                              int32_t* done_counter, void* stream);
+int mokb_combine_rows_window(const void* src, const uint64_t* dst_ptrs_host, int ep_size,
+                             const int32_t* peer_rank, const int32_t* peer_token_idx,
+                             const int32_t* num_rows, int max_rows, int row_begin, int row_end, int64_t hidden,
+                             const float* row_values, const uint64_t* value_ptrs_host, int blocks,
+                             const int32_t* wait_counter, int arrivals_per_row_block, int32_t* status, void* stream);
 
 /* SwiGLU forward / backward on [rows, cols] bf16 (csrc/megakernel/swiglu.cuh:38-207, 209-566).
  * Backward also emits per-row sum(d_hidden * silu(g)*u) / w (w = row_scale[i], 1/w := 0 if w <= 0)

@@ -91,7 +91,7 @@ template <bool SCALE, int W>
 __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t* __restrict__ peer_rank,
                                 const int32_t* __restrict__ peer_token_idx, const int32_t* __restrict__ num_rows,
                                 int max_rows, int row_begin, int row_end, int R, int row_divisor, int vec_per_row,
-                                Words<W>* __restrict__ dst, float* __restrict__ row_scale_out) {
+                                Words<W>* __restrict__ dst, float* __restrict__ row_scale_out, int32_t* done_counter) {
     int rows = num_rows ? *num_rows : max_rows;
     rows = rows < 0 ? 0 : (rows > max_rows ? 0 : rows);
     rows = min(rows, row_end);
@@ -136,16 +136,34 @@ __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t*
             }
         }
     }
+    if (done_counter) {      // this block's rows of the window have landed: one arrival for whoever consumes them
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            red_release_gpu_add(done_counter, 1);
+        }
+    }
 }
 
 template <int W>
 __global__ void combine_kernel(const Words<W>* __restrict__ src, PeerPtrs dst, PeerPtrs val_dst,
                                const int32_t* __restrict__ peer_rank, const int32_t* __restrict__ peer_token_idx,
                                const int32_t* __restrict__ num_rows, int max_rows, int row_begin, int row_end, int R,
-                               int vec_per_row, const float* __restrict__ row_values) {
+                               int vec_per_row, const float* __restrict__ row_values, const int32_t* wait_counter,
+                               int arrivals_per_row_block, int32_t* status) {
     int rows = num_rows ? *num_rows : max_rows;
     rows = rows < 0 ? 0 : (rows > max_rows ? 0 : rows);
     rows = min(rows, row_end);
+    if (wait_counter) {
+        // the rows come from a GEMM that is still running: wait (bounded) until every tile of this window is stored
+        __shared__ int go;
+        if (threadIdx.x == 0) {
+            const int expected = ((rows - row_begin) / 256) * arrivals_per_row_block;
+            go = expected <= 0 || flag_wait(wait_counter, expected, nullptr, status, kWaitWindowDone, row_begin / 256);
+        }
+        __syncthreads();
+        if (!go) return;
+    }
     const int lane = threadIdx.x & 31;
     const int warps_per_block = blockDim.x >> 5;
     const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -241,10 +259,12 @@ extern "C" int mokb_barrier_all(const uint64_t* barrier_ptrs_host, int ep_size, 
 
 namespace mokb {
 
+int comm_default_blocks() { return sm_count() * 8; }
+
 int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
                        const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                        int row_divisor, int64_t hidden, void* dst, const uint64_t* row_scale_ptrs_host,
-                       float* row_scale_out, int blocks, cudaStream_t s) {
+                       float* row_scale_out, int blocks, cudaStream_t s, int32_t* done_counter) {
     TraceScope trace(s, row_scale_ptrs_host ? "dispatch_scaled" : "dispatch", row_begin);
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "dispatch_rows: bad ep_size");
     MOKB_REQUIRE(peer_rank && peer_token_idx && dst, "dispatch_rows: null pointer");
@@ -256,9 +276,13 @@ int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t
     for (int r = 0; r < kPeerMax; ++r) scale.p[r] = nullptr;
     if (max_rows == 0 || row_begin >= max_rows) return MOKB_OK;
     const int threads = 256;
-    if (blocks <= 0) blocks = sm_count() * 8;
+    if (blocks <= 0) blocks = comm_default_blocks();
     const bool wide = rows_aligned32(dst, src, ep_size, hidden);
     const int vec = static_cast<int>(hidden / (wide ? 16 : 8));
+    share_sms_with_gemm(dispatch_kernel<true, 8>);
+    share_sms_with_gemm(dispatch_kernel<true, 4>);
+    share_sms_with_gemm(dispatch_kernel<false, 8>);
+    share_sms_with_gemm(dispatch_kernel<false, 4>);
     if (row_scale_ptrs_host) {
         for (int r = 0; r < ep_size; ++r) {
             MOKB_REQUIRE(row_scale_ptrs_host[r] != 0, "dispatch_rows: null scale pointer for rank %d", r);
@@ -266,16 +290,16 @@ int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t
         }
         if (wide)
             dispatch_kernel<true, 8><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
-                                                                row_end, ep_size, row_divisor, vec, static_cast<Words<8>*>(dst), row_scale_out);
+                                                                row_end, ep_size, row_divisor, vec, static_cast<Words<8>*>(dst), row_scale_out, done_counter);
         else
             dispatch_kernel<true, 4><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
-                                                                row_end, ep_size, row_divisor, vec, static_cast<Words<4>*>(dst), row_scale_out);
+                                                                row_end, ep_size, row_divisor, vec, static_cast<Words<4>*>(dst), row_scale_out, done_counter);
     } else if (wide) {
         dispatch_kernel<false, 8><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
-                                                             row_end, ep_size, row_divisor, vec, static_cast<Words<8>*>(dst), nullptr);
+                                                             row_end, ep_size, row_divisor, vec, static_cast<Words<8>*>(dst), nullptr, done_counter);
     } else {
         dispatch_kernel<false, 4><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
-                                                             row_end, ep_size, row_divisor, vec, static_cast<Words<4>*>(dst), nullptr);
+                                                             row_end, ep_size, row_divisor, vec, static_cast<Words<4>*>(dst), nullptr, done_counter);
     }
     MOKB_CUDA(cudaGetLastError());
     note_launch();
@@ -284,8 +308,11 @@ int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t
 
 int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_size, const int32_t* peer_rank,
                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
-                      int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s) {
+                      int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s,
+                      const int32_t* wait_counter, int arrivals_per_row_block, int32_t* status) {
     TraceScope trace(s, "combine", row_begin);
+    MOKB_REQUIRE(wait_counter == nullptr || (arrivals_per_row_block > 0 && status != nullptr && row_begin % 256 == 0),
+                 "combine_rows: a wait counter needs arrivals_per_row_block, a status word and a window that starts on a 256-row block");
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "combine_rows: bad ep_size");
     MOKB_REQUIRE(src && peer_rank && peer_token_idx, "combine_rows: null pointer");
     MOKB_REQUIRE(max_rows >= 0 && hidden > 0 && hidden % 8 == 0, "combine_rows: bad sizes");
@@ -300,13 +327,17 @@ int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
             val.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(value_ptrs_host[r]));
         }
     if (max_rows == 0 || row_begin >= max_rows) return MOKB_OK;
-    if (blocks <= 0) blocks = sm_count() * 8;
+    if (blocks <= 0) blocks = comm_default_blocks();
+    share_sms_with_gemm(combine_kernel<8>);
+    share_sms_with_gemm(combine_kernel<4>);
     if (rows_aligned32(src, dst, ep_size, hidden))
         combine_kernel<8><<<blocks, 256, 0, s>>>(static_cast<const Words<8>*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
-                                                 row_begin, row_end, ep_size, static_cast<int>(hidden / 16), row_values);
+                                                 row_begin, row_end, ep_size, static_cast<int>(hidden / 16), row_values, wait_counter,
+                                                 arrivals_per_row_block, status);
     else
         combine_kernel<4><<<blocks, 256, 0, s>>>(static_cast<const Words<4>*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
-                                                 row_begin, row_end, ep_size, static_cast<int>(hidden / 8), row_values);
+                                                 row_begin, row_end, ep_size, static_cast<int>(hidden / 8), row_values, wait_counter,
+                                                 arrivals_per_row_block, status);
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     return MOKB_OK;
@@ -319,7 +350,18 @@ extern "C" int mokb_dispatch_rows(const uint64_t* src_ptrs_host, int ep_size, co
                                   int row_divisor, int64_t hidden, void* dst,
                                   const uint64_t* row_scale_ptrs_host, float* row_scale_out, void* stream) {
     return dispatch_rows_impl(src_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, 0, max_rows, row_divisor,
-                              hidden, dst, row_scale_ptrs_host, row_scale_out, 0, static_cast<cudaStream_t>(stream));
+                              hidden, dst, row_scale_ptrs_host, row_scale_out, 0, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+extern "C" int mokb_comm_default_blocks(void) { return comm_default_blocks(); }
+
+extern "C" int mokb_dispatch_rows_window(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
+                                         const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin,
+                                         int row_end, int row_divisor, int64_t hidden, void* dst,
+                                         const uint64_t* row_scale_ptrs_host, float* row_scale_out, int blocks,
+                                         int32_t* done_counter, void* stream) {
+    return dispatch_rows_impl(src_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, row_divisor,
+                              hidden, dst, row_scale_ptrs_host, row_scale_out, blocks, static_cast<cudaStream_t>(stream), done_counter);
 }
 
 extern "C" int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_size,
@@ -327,5 +369,15 @@ extern "C" int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host,
                                  const int32_t* num_rows, int max_rows, int64_t hidden,
                                  const float* row_values, const uint64_t* value_ptrs_host, void* stream) {
     return combine_rows_impl(src, dst_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, 0, max_rows, hidden,
-                             row_values, value_ptrs_host, 0, static_cast<cudaStream_t>(stream));
+                             row_values, value_ptrs_host, 0, static_cast<cudaStream_t>(stream), nullptr, 0, nullptr);
+}
+
+extern "C" int mokb_combine_rows_window(const void* src, const uint64_t* dst_ptrs_host, int ep_size,
+                                        const int32_t* peer_rank, const int32_t* peer_token_idx,
+                                        const int32_t* num_rows, int max_rows, int row_begin, int row_end, int64_t hidden,
+                                        const float* row_values, const uint64_t* value_ptrs_host, int blocks,
+                                        const int32_t* wait_counter, int arrivals_per_row_block, int32_t* status, void* stream) {
+    return combine_rows_impl(src, dst_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, hidden,
+                             row_values, value_ptrs_host, blocks, static_cast<cudaStream_t>(stream), wait_counter,
+                             arrivals_per_row_block, status);
 }

@@ -32,6 +32,18 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
     do { int _r = (expr); if (_r != MOKB_OK) return _r; } while (0)
 
 int sm_count();
+
+// Kernels that run on the side streams beside a GEMM ask for the same shared-memory / L1 split as the GEMM (all
+// shared memory).  An SM changes its split only when it is empty: blocks of a kernel with the default split that sit
+// on every SM -- above all blocks that WAIT for the GEMM -- would keep its 197 KB CTAs from ever being placed.
+template <class Kernel>
+inline void share_sms_with_gemm(Kernel kernel) {
+    static bool done = false;       // one flag per kernel type
+    if (!done) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, static_cast<int>(cudaSharedmemCarveoutMaxShared));
+        done = true;
+    }
+}
 // Launch timeline (diagnostic, off unless mokb_trace_begin was called): an object of this class in a launcher
 // brackets everything the launcher enqueues on `stream` with two timing events.
 class TraceScope {
@@ -51,13 +63,18 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t in
 
 // Row-window forms of dispatch / combine used by the layer to overlap them with the GEMMs:
 // rows [row_begin, min(row_end, *num_rows)) only, on `blocks` CTAs of 256 threads (0 = default).
+// `done_counter`: every block adds 1 (release) once its rows of the window have landed, so a GEMM that is already
+// running can start on them.  `wait_counter`: the rows are still being written by a running GEMM; the kernel first
+// waits (bounded) for ((rows of the window) / 256) * arrivals_per_row_block arrivals.
+int comm_default_blocks();
 int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
                        const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                        int row_divisor, int64_t hidden, void* dst, const uint64_t* row_scale_ptrs_host,
-                       float* row_scale_out, int blocks, cudaStream_t s);
+                       float* row_scale_out, int blocks, cudaStream_t s, int32_t* done_counter = nullptr);
 int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_size, const int32_t* peer_rank,
                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
-                      int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s);
+                      int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s,
+                      const int32_t* wait_counter = nullptr, int arrivals_per_row_block = 0, int32_t* status = nullptr);
 
 // MXFP8 codec launchers (quantize.cu).  Rows [row_begin, min(row_end, *num_rows)) are processed (row_end = 0: all
 // M / rows_cap rows; `num_rows` is a device pointer, optional).  Row numbers are the caller's: a buffer holding only
@@ -141,6 +158,55 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (i > kWaitLimit) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// ---- counters between kernels (and between CTAs of one kernel): the producer of some rows adds to a global
+// counter with release semantics after its stores, the consumer polls it with acquire loads.  The reference's
+// barrier_wait / barrier_arrive (csrc/megakernel/utils.cuh:1-13) with a time limit: a consumer that waits longer
+// than kFlagWaitNs records MOKB_ST_FLAG_TIMEOUT, raises the CTA's abort flag (if it has one) and gives up.
+constexpr unsigned long long kFlagWaitNs = 2ull * 1000 * 1000 * 1000;
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// makes writes that other threads made through ordinary stores (and that this thread has acquired) visible to
+// the TMA reads this thread issues next
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+// `kind` / `index` say which counter it was (status words 1..3, for diagnosis: kind, index, value seen << 16 | target)
+enum { kWaitWindowReady = 1, kWaitBlockDone = 2, kWaitWindowDone = 3 };
+
+__device__ __forceinline__ bool flag_wait(const int* flag, int target, volatile int* abort_flag, int* status, int kind, int index) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        const int seen = ld_acquire_gpu(flag);
+        if (seen >= target) return true;
+        if (i >= 32) __nanosleep(i < 1024 ? 100 : 500);
+        if ((i & 127u) == 127u) {
+            if (abort_flag && *abort_flag) return false;
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > kFlagWaitNs) {
+                if (abort_flag) *abort_flag = 1;
+                if (status && atomicCAS(status, 0, MOKB_ST_FLAG_TIMEOUT) == 0) {
+                    status[1] = kind;
+                    status[2] = index;
+                    status[3] = (seen << 16) | (target & 0xFFFF);
+                }
                 return false;
             }
         }

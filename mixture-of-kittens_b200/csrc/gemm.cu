@@ -25,7 +25,18 @@
 //   MODE_SWIGLU  gate,up = A * Wg[g]^T, A * Wu[g]^T; hidden = SwiGLU  (one 128+128 column tile)
 //   MODE_NN      D[rows,N] = A[rows,K] * W[g][K,N] (+ A2 * W2[g])    (input gradients)
 //   MODE_WGRAD   D[g][M,N] = A[rows_g,M]^T * B[rows_g,N]             (weight gradients)
+//   MODE_FWD     MODE_SWIGLU tiles and the MODE_NT (down) tiles of the same rows in ONE persistent launch,
+//                window by window (a window = the rows one dispatch launch pulls): the task loop of the
+//                reference's forward megakernel (csrc/megakernel/forward.cuh:146-266) with its global-memory
+//                counters (csrc/megakernel/utils.cuh:1-13), every wait bounded.
 // Expert segments are multiples of 256 rows, so a tile never straddles two experts.
+//
+// Counters (row-tiled modes, all optional): `win_ready[w]` is raised by the dispatch blocks of window w and
+// awaited by the TMA producer before it loads the first A rows of that window; MODE_FWD also counts the
+// epilogue warps that finished the gate/up tiles of a 256-row block (`blk_done`, awaited before a down tile
+// loads `hidden`) and those that finished the down tiles of a window (`win_done`, awaited by the combine
+// kernel).  Producers publish with a release at GPU scope after their stores; the consumer acquires and then
+// orders the generic-proxy writes before its own TMA reads with a proxy fence.
 #include <stdlib.h>
 #include <string.h>
 
@@ -41,7 +52,7 @@ constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_ROWS = 1024;                // rows per raster super-group
 
-enum { MODE_NT = 0, MODE_SWIGLU = 1, MODE_NN = 2, MODE_WGRAD = 3 };
+enum { MODE_NT = 0, MODE_SWIGLU = 1, MODE_NN = 2, MODE_WGRAD = 3, MODE_FWD = 4 };
 
 template <int NCTA>
 struct Geo {
@@ -69,18 +80,41 @@ struct KParams {
     int has_limit;
     float limit;
     int accumulate;                  // MODE_WGRAD: add to the stored bf16 result instead of overwriting it
+    // counters (see the top of the file)
+    int window_rows;                 // rows per window, a multiple of 256; 0 = one window
+    const int32_t* win_ready;        // [windows from row_begin], optional
+    int win_ready_target;
+    // MODE_FWD: the down projection that follows gate/up + SwiGLU
+    int N2, K2;                      // down: N2 = hidden columns (multiple of 256; 0 = no down tiles), K2 = contraction
+    int b3_rows_per_group;
+    __nv_bfloat16* D4;
+    int ldd4;
+    int32_t* blk_done;               // [256-row blocks from row_begin]
+    int32_t* win_done;               // [windows from row_begin], optional
+    // push (MODE_NT, MODE_NN, the down tiles of MODE_FWD): row r of the result goes to row push_idx[r] of rank
+    // push_rank[r]'s buffer (rows with a rank outside [0, push_ranks) go nowhere) -- combine without a combine kernel
+    int push, push_ranks, push_wide;
+    const int32_t* push_rank;
+    const int32_t* push_idx;
+    const float* push_values;        // optional: push_val[rank][idx] = push_values[r], written with the first column tile
     int32_t* status;
+    PeerPtrs push_dst, push_val;
 };
 
 struct Tile {
     int m_blk, n_blk, group, k_iters, k_row0;
+    int phase;                       // MODE_FWD: 0 = gate/up + SwiGLU tile, 1 = down tile
+    int window;                      // window of the tile's rows, counted from row_begin
 };
 
 template <int MODE, int NCTA>
 struct Sched {
     int m_blocks, n_blocks, total, m_first;
+    int n_gu, n_nt, win_blocks;      // MODE_FWD: column tiles of the two phases; row tiles per window (all row-tiled modes)
     __device__ Sched(const KParams& p) {
         m_first = 0;
+        n_gu = n_nt = 0;
+        win_blocks = 1 << 30;
         constexpr int TM = Geo<NCTA>::TILE_M;
         if (MODE == MODE_WGRAD) {
             m_blocks = (p.M + TM - 1) / TM;
@@ -96,6 +130,12 @@ struct Sched {
             m_blocks = (hi - lo) / TM;
             n_blocks = MODE == MODE_SWIGLU ? p.N / 128 : (p.N + BN - 1) / BN;
             total = m_blocks * n_blocks;
+            if (p.window_rows > 0) win_blocks = p.window_rows / TM;
+            if (MODE == MODE_FWD) {
+                n_gu = p.N / 128;
+                n_nt = p.N2 / BN;
+                total = m_blocks * (n_gu + n_nt);
+            }
         }
     }
     __device__ Tile get(const KParams& p, int t) const {
@@ -110,6 +150,30 @@ struct Sched {
             ti.m_blk = rem - ti.n_blk * m_blocks;
             ti.k_row0 = p.group_offsets[ti.group];
             ti.k_iters = (p.group_offsets[ti.group + 1] - ti.k_row0) / BK;
+        } else if (MODE == MODE_FWD) {
+            // window by window: all gate/up tiles of the window's rows, then all their down tiles; inside a phase,
+            // super-groups of 1024 rows x every column tile
+            const int wb = min(win_blocks, m_blocks);
+            const int per_win = wb * (n_gu + n_nt);
+            const int n_win = (m_blocks + wb - 1) / wb;
+            const int w = min(t / per_win, n_win - 1);
+            int local = t - w * per_win;
+            const int blk0 = w * wb;
+            const int wc = min(wb, m_blocks - blk0);
+            ti.phase = local >= wc * n_gu ? 1 : 0;
+            if (ti.phase) local -= wc * n_gu;
+            const int nb = ti.phase ? n_nt : n_gu;
+            const int per = GM * nb;
+            const int sg = local / per;
+            const int first = sg * GM;
+            const int gsize = min(GM, wc - first);
+            const int in = local - sg * per;
+            ti.n_blk = in / gsize;
+            ti.m_blk = m_first + blk0 + first + (in - ti.n_blk * gsize);
+            ti.window = w;
+            ti.group = p.group_of_block ? p.group_of_block[ti.m_blk * (TM / 128)] : 0;
+            ti.k_row0 = 0;
+            ti.k_iters = (ti.phase ? p.K2 : p.K) / BK;
         } else {
             const int per = GM * n_blocks;
             const int sg = t / per;
@@ -121,6 +185,8 @@ struct Sched {
             ti.group = p.group_of_block ? p.group_of_block[ti.m_blk * (TM / 128)] : 0;
             ti.k_row0 = 0;
             ti.k_iters = (p.K / BK) * (p.dual ? 2 : 1);
+            ti.phase = 0;
+            ti.window = (ti.m_blk - m_first) / win_blocks;
         }
         return ti;
     }
@@ -158,7 +224,7 @@ template <int MODE, int NCTA>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                    const KParams p) {
+                    const __grid_constant__ CUtensorMap tmB3, const KParams p) {
     using G = Geo<NCTA>;
     constexpr int STAGES = G::STAGES;
     constexpr int STAGE_BYTES = G::STAGE_BYTES;
@@ -197,9 +263,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
-        if (MODE == MODE_SWIGLU || (MODE == MODE_NN && p.dual)) {
+        if (MODE == MODE_SWIGLU || MODE == MODE_FWD || (MODE == MODE_NN && p.dual)) {
             tma_prefetch_desc(&tmB2);
             if (MODE == MODE_NN) tma_prefetch_desc(&tmA2);
+        }
+        if (MODE == MODE_FWD && p.N2 > 0) {
+            tma_prefetch_desc(&tmA2);
+            tma_prefetch_desc(&tmB3);
         }
     }
     if (warp == 1) {
@@ -226,9 +296,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t ph = 0;
             bool ok = true;
             const int kh = p.K / BK;
+            int waited_window = -1;
             for (int t = tile_id0; ok && t < sched.total; t += tile_stride) {
                 const Tile ti = sched.get(p, t);
                 const int row0 = ti.m_blk * G::TILE_M + static_cast<int>(cta) * 128;    // this CTA's rows of A / D
+                if (MODE != MODE_WGRAD) {
+                    // rows that another kernel (or, for a down tile, other CTAs of this one) is still producing
+                    bool fenced = false;
+                    if (p.win_ready && ti.phase == 0 && ti.window > waited_window) {
+                        if (!flag_wait(p.win_ready + ti.window, p.win_ready_target, abort_flag, p.status, kWaitWindowReady, ti.window)) { ok = false; break; }
+                        waited_window = ti.window;
+                        fenced = true;
+                    }
+                    if (MODE == MODE_FWD && ti.phase == 1) {
+                        if (!flag_wait(p.blk_done + (ti.m_blk - sched.m_first), sched.n_gu * 4 * NCTA, abort_flag, p.status, kWaitBlockDone, ti.m_blk - sched.m_first)) { ok = false; break; }
+                        fenced = true;
+                    }
+                    if (fenced) fence_proxy_async_global();
+                }
                 for (int it = 0; it < ti.k_iters; ++it) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
                     const uint32_t fb_local = full_bar(s);
@@ -240,7 +325,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (MODE == MODE_NT) {
                         tma_tile<NCTA>(a_dst, &tmA, fb, it * BK, row0);
                         tma_tile<NCTA>(b_dst, &tmB, fb, it * BK, ti.group * p.b_rows_per_group + bcol0);
-                    } else if (MODE == MODE_SWIGLU) {
+                    } else if (MODE == MODE_FWD && ti.phase == 1) {
+                        tma_tile<NCTA>(a_dst, &tmA2, fb, it * BK, row0);
+                        tma_tile<NCTA>(b_dst, &tmB3, fb, it * BK, ti.group * p.b3_rows_per_group + bcol0);
+                    } else if (MODE == MODE_SWIGLU || MODE == MODE_FWD) {
                         tma_tile<NCTA>(a_dst, &tmA, fb, it * BK, row0);
                         const int brow = ti.group * p.b_rows_per_group + ti.n_blk * 128;
                         if (NCTA == 2) {      // leader stages the gate columns, its peer the up columns
@@ -331,7 +419,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
             const bool empty_k = ti.k_iters == 0;
             const int row_in_tile = static_cast<int>(cta) * 128 + row_in_cta;
-            if (MODE == MODE_SWIGLU) {
+            if (MODE == MODE_SWIGLU || (MODE == MODE_FWD && ti.phase == 0)) {
                 const size_t row = static_cast<size_t>(ti.m_blk) * G::TILE_M + row_in_tile;
                 const size_t off = row * p.ldd + static_cast<size_t>(ti.n_blk) * 128;
 #pragma unroll 1
@@ -367,8 +455,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 } else {
                     row = static_cast<size_t>(tile_row);
                 }
-                __nv_bfloat16* dst = p.D + row * p.ldd + static_cast<size_t>(ti.n_blk) * BN;
-                const int cols_left = p.N - ti.n_blk * BN;
+                __nv_bfloat16* const base = MODE == MODE_FWD ? p.D4 : p.D;
+                const size_t ld_out = MODE == MODE_FWD ? p.ldd4 : p.ldd;
+                __nv_bfloat16* dst = base + row * ld_out + static_cast<size_t>(ti.n_blk) * BN;
+                if (base == nullptr) row_ok = false;          // pushed only
+                __nv_bfloat16* pdst = nullptr;                // this row's place in its home rank's buffer
+                if ((MODE == MODE_NT || MODE == MODE_NN || MODE == MODE_FWD) && p.push) {
+                    const int pr = p.push_rank[tile_row];
+                    if (pr >= 0 && pr < p.push_ranks) {
+                        const size_t slot = static_cast<size_t>(p.push_idx[tile_row]);
+                        pdst = static_cast<__nv_bfloat16*>(p.push_dst.p[pr]) + slot * ld_out + static_cast<size_t>(ti.n_blk) * BN;
+                        if (p.push_values && ti.n_blk == 0) static_cast<float*>(p.push_val.p[pr])[slot] = p.push_values[tile_row];
+                    }
+                }
+                const int cols_left = (MODE == MODE_FWD ? p.N2 : p.N) - ti.n_blk * BN;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     if (c * 32 >= cols_left) break;
@@ -396,6 +496,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         }
                     }
                     if (row_ok) store_row32(dst + c * 32, r, p.wide_stores);
+                    if (pdst) store_row32(pdst + c * 32, r, p.push_wide);
                 }
             }
             tc_fence_before();
@@ -403,6 +504,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (lane == 0) {
                 if (NCTA == 2) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
                 else mbar_arrive(tempty_bar(acc));
+                if (MODE == MODE_FWD) {
+                    // this warp's rows of the tile are stored: count it for whoever reads them next
+                    int32_t* counter = ti.phase == 0 ? p.blk_done + (ti.m_blk - sched.m_first) : (p.win_done ? p.win_done + ti.window : nullptr);
+                    if (counter) red_release_gpu_add(counter, 1);
+                }
             }
         }
     }
@@ -425,8 +531,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 template <int MODE, int NCTA>
-int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2, const KParams& p,
-           int tiles_upper_bound, cudaStream_t stream) {
+int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2, const CUtensorMap& b3,
+           const KParams& p, int tiles_upper_bound, cudaStream_t stream) {
     constexpr size_t smem = Geo<NCTA>::SMEM_BYTES;
     MOKB_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<MODE, NCTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int units = sm_count() / NCTA;                       // CTAs, or CTA pairs
@@ -444,7 +550,7 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    MOKB_CUDA(cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<MODE, NCTA>, a, b, a2, b2, p));
+    MOKB_CUDA(cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<MODE, NCTA>, a, b, a2, b2, b3, p));
     note_launch();
     return MOKB_OK;
 }
@@ -462,7 +568,7 @@ int ctas_per_tile() {
 template <int MODE>
 int dispatch_launch(int ncta, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2,
                     const KParams& p, int tiles, cudaStream_t stream) {
-    return ncta == 2 ? launch<MODE, 2>(a, b, a2, b2, p, tiles, stream) : launch<MODE, 1>(a, b, a2, b2, p, tiles, stream);
+    return ncta == 2 ? launch<MODE, 2>(a, b, a2, b2, b, p, tiles, stream) : launch<MODE, 1>(a, b, a2, b2, b, p, tiles, stream);
 }
 
 }  // namespace
@@ -473,14 +579,16 @@ using namespace mokb;
 extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     MOKB_REQUIRE(g != nullptr, "grouped_gemm: null args");
-    MOKB_REQUIRE(g->mode >= 0 && g->mode <= 3, "grouped_gemm: unknown mode %d", g->mode);
-    static const char* const kTags[4] = {"gemm_bf16_nt", "gemm_bf16_gate_up_swiglu", "gemm_bf16_nn", "gemm_bf16_wgrad"};
+    MOKB_REQUIRE(g->mode >= 0 && g->mode <= 4, "grouped_gemm: unknown mode %d", g->mode);
+    static const char* const kTags[5] = {"gemm_bf16_nt", "gemm_bf16_gate_up_swiglu", "gemm_bf16_nn", "gemm_bf16_wgrad", "gemm_bf16_fwd_routed"};
     TraceScope trace(stream, kTags[g->mode], g->row_begin);
-    MOKB_REQUIRE(g->A && g->B && g->D && g->status, "grouped_gemm: null pointer");
+    MOKB_REQUIRE(g->A && g->B && g->status, "grouped_gemm: null pointer");
+    MOKB_REQUIRE(g->D || (g->push_ptrs_host && g->mode != MODE_FWD), "grouped_gemm: D may only be left out when the result is pushed to peers");
     MOKB_REQUIRE(g->G >= 1, "grouped_gemm: G must be >= 1");
     MOKB_REQUIRE(g->rows_static >= 0 && g->rows_static % 128 == 0, "grouped_gemm: rows must be a multiple of 128");
     // row tiles of 256 need row counts in multiples of 256 (true for every tensor of the layer)
-    const int ncta = (ctas_per_tile() == 2 && g->rows_static % 256 == 0) ? 2 : 1;
+    const int ncta = (g->mode == MODE_FWD || (ctas_per_tile() == 2 && g->rows_static % 256 == 0)) ? 2 : 1;
+    MOKB_REQUIRE(g->mode != MODE_FWD || g->rows_static % 256 == 0, "grouped_gemm FWD: rows must be a multiple of 256");
     const int TM = 128 * ncta;
     const uint32_t b_box = static_cast<uint32_t>(BN / ncta);
     KParams p;
@@ -505,6 +613,31 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     p.limit = g->swiglu_limit;
     p.status = g->status;
     p.dual = 0;
+    if (g->push_ptrs_host) {
+        MOKB_REQUIRE(g->mode == MODE_NT || g->mode == MODE_NN || g->mode == MODE_FWD, "grouped_gemm: push is for modes 0, 2 and 4");
+        MOKB_REQUIRE(g->push_ep_size >= 1 && g->push_ep_size <= MOKB_MAX_EP && g->push_rank && g->push_idx, "grouped_gemm: push needs ranks and indices");
+        MOKB_REQUIRE((g->push_values == nullptr) == (g->push_value_ptrs_host == nullptr), "grouped_gemm: push_values and push_value_ptrs_host go together");
+        const int ld_out = g->mode == MODE_FWD ? g->ldd4 : g->ldd;
+        p.push = 1; p.push_ranks = g->push_ep_size; p.push_rank = g->push_rank; p.push_idx = g->push_idx; p.push_values = g->push_values;
+        p.push_wide = ld_out % 16 == 0;
+        for (int r = 0; r < kPeerMax; ++r) p.push_dst.p[r] = p.push_val.p[r] = nullptr;
+        for (int r = 0; r < g->push_ep_size; ++r) {
+            MOKB_REQUIRE(g->push_ptrs_host[r] != 0 && (g->push_ptrs_host[r] & 15) == 0, "grouped_gemm: push pointer of rank %d is null or not 16-byte aligned", r);
+            p.push_dst.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(g->push_ptrs_host[r]));
+            if ((g->push_ptrs_host[r] & 31) != 0) p.push_wide = 0;
+            if (g->push_value_ptrs_host) {
+                MOKB_REQUIRE(g->push_value_ptrs_host[r] != 0, "grouped_gemm: push value pointer of rank %d is null", r);
+                p.push_val.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(g->push_value_ptrs_host[r]));
+            }
+        }
+    }
+    if (g->mode != MODE_WGRAD) {
+        MOKB_REQUIRE(g->window_rows >= 0 && g->window_rows % 256 == 0, "grouped_gemm: window_rows must be a multiple of 256");
+        MOKB_REQUIRE(g->win_ready == nullptr || (g->window_rows > 0 && g->win_ready_target > 0), "grouped_gemm: win_ready needs window_rows and a target");
+        p.window_rows = g->window_rows;
+        p.win_ready = g->win_ready;
+        p.win_ready_target = g->win_ready_target;
+    }
     MOKB_REQUIRE(g->ldd % 8 == 0 && g->lda % 8 == 0 && g->ldb % 8 == 0, "grouped_gemm: leading dimensions must be multiples of 8");
     MOKB_REQUIRE((reinterpret_cast<uintptr_t>(g->D) & 15) == 0, "grouped_gemm: D not 16-byte aligned");
     if (g->rows_static == 0) return MOKB_OK;
@@ -543,6 +676,32 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
         }
         p.b_rows_per_group = g->K;
         return dispatch_launch<MODE_NN>(ncta, ta, tb, ta2, tb2, p, m_tiles * ((g->N + BN - 1) / BN), stream);
+    }
+    case MODE_FWD: {
+        MOKB_REQUIRE(g->K > 0 && g->K % BK == 0 && g->N > 0 && g->N % 128 == 0, "grouped_gemm FWD: K %% 64 and N %% 128 must be 0");
+        MOKB_REQUIRE(g->B2 && g->D2 && g->D3 && g->blk_done, "grouped_gemm FWD: B2, D2, D3 and blk_done required");
+        MOKB_REQUIRE(g->N2 >= 0 && g->N2 % BN == 0, "grouped_gemm FWD: N2 must be a multiple of 256");
+        MOKB_TRY(make_tmap_2d(&ta, g->A, 2, g->K, rows, 2ull * g->lda, 64, 128));
+        MOKB_TRY(make_tmap_2d(&tb, g->B, 2, g->K, static_cast<uint64_t>(g->G) * g->N, 2ull * g->ldb, 64, 128));
+        MOKB_TRY(make_tmap_2d(&tb2, g->B2, 2, g->K, static_cast<uint64_t>(g->G) * g->N, 2ull * g->ldb, 64, 128));
+        p.b_rows_per_group = g->N;
+        ta2 = ta;
+        CUtensorMap tb3 = tb;
+        if (g->N2 > 0) {
+            // the down projection reads the hidden rows this launch writes: A2 = D3 [rows, N], contraction over N
+            MOKB_REQUIRE(g->B3 && (g->D4 || g->push_ptrs_host) && g->ldd4 > 0 && g->ldd4 % 8 == 0 && g->ldb3 % 8 == 0,
+                         "grouped_gemm FWD: B3, D4 (or push pointers) and their leading dimensions required");
+            MOKB_REQUIRE(g->N % BK == 0, "grouped_gemm FWD: N must be a multiple of 64 for the down projection");
+            MOKB_REQUIRE((reinterpret_cast<uintptr_t>(g->D4) & 15) == 0, "grouped_gemm FWD: D4 not 16-byte aligned");
+            MOKB_TRY(make_tmap_2d(&ta2, g->D3, 2, g->N, rows, 2ull * g->ldd, 64, 128));
+            MOKB_TRY(make_tmap_2d(&tb3, g->B3, 2, g->N, static_cast<uint64_t>(g->G) * g->N2, 2ull * g->ldb3, 64, 128));
+            p.N2 = g->N2; p.K2 = g->N; p.b3_rows_per_group = g->N2;
+            p.D4 = static_cast<__nv_bfloat16*>(g->D4); p.ldd4 = g->ldd4;
+            p.wide_stores = p.wide_stores && g->ldd4 % 16 == 0 && (reinterpret_cast<uintptr_t>(g->D4) & 31) == 0;
+        }
+        p.blk_done = g->blk_done;
+        p.win_done = g->win_done;
+        return launch<MODE_FWD, 2>(ta, tb, ta2, tb2, tb3, p, m_tiles * (g->N / 128 + g->N2 / BN), stream);
     }
     default: {
         MOKB_REQUIRE(g->M > 0 && g->M % 128 == 0 && g->N > 0 && g->N % 64 == 0, "grouped_gemm WGRAD: M %% 128 and N %% 64 must be 0");

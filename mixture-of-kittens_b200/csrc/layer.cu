@@ -1,21 +1,25 @@
-// The fused MoE layer, forward and backward (BF16): the sequence of dispatch,
-// grouped GEMMs, SwiGLU and combine that replaces the reference's persistent
-// kernels (csrc/megakernel/forward.cuh:1-291, backward.cuh:1-443).
+// The fused MoE layer, forward and backward (BF16): dispatch, grouped GEMMs, SwiGLU and combine, the work of
+// the reference's persistent kernels (csrc/megakernel/forward.cuh:1-291, backward.cuh:1-443).
 //
-// Nothing here synchronises the host: the number of routed rows is read on the
-// device by every kernel (forward.cuh:20 does the same).  Communication overlaps
-// computation the way the reference's communication CTAs do, but with stream
-// ordering instead of in-kernel counters: dispatch and combine run on two side
-// streams of this library, in row windows of `minibatch_size` rows, on
-// `num_comm_sms` SMs' worth of threads, and are tied to the GEMM launches on the
-// caller's stream by events (fork after the prologue, join before returning):
+// Nothing here synchronises the host: the number of routed rows is read on the device by every kernel
+// (forward.cuh:20 does the same).
 //
-//   forward   side 1: dispatch(c0) dispatch(c1) ...
-//             caller: prologue | shared gate/up, shared down | gate/up(c0) down(c0) gate/up(c1) down(c1) ...
-//             side 2:                                                   combine(c0)          combine(c1) ...
-//   backward  side 1: scaled dispatch of d_y
-//             caller: prologue | shared backward (6 launches) | routed dgrads | routed wgrads
-//             side 2:                                                          combine of d_x + router grads
+//   forward   side stream: dispatch(w0) dispatch(w1) ...                      each raises win_ready[w] when its rows have landed
+//             caller     : prologue | shared gate/up, shared down | ONE routed launch: for every window w
+//                          { wait win_ready[w]; gate/up + SwiGLU tiles; down tiles, each after the gate/up tiles of its
+//                            256 rows (blk_done); the down epilogue stores every row into its home rank's combine buffer }
+//   backward  side stream: scaled dispatch of d_y in four windows, raising win_ready[w]
+//             caller     : prologue | shared backward (6 launches) | d_hidden = d_y * W_down (one launch, window by window)
+//                          | SwiGLU backward | d_x = d_gate * W_gate + d_up * W_up, whose epilogue stores every row and its
+//                            router-weight gradient into the home rank's buffers | three weight gradients
+//
+// The counters are the reference's (csrc/megakernel/utils.cuh:1-13, types.cuh:126-130): global-memory words added to
+// with release semantics by whoever produced some rows and polled with acquire loads by whoever consumes them.  Who may
+// wait is restricted so that nothing can starve: only CTAs of the persistent GEMM wait, either for dispatch blocks (which
+// never wait and therefore always finish) or for other CTAs of the same GEMM, whose tiles come earlier in the one order
+// that every CTA walks; kernels that run beside the GEMM never wait for it, because blocks that sit on an SM waiting
+// would keep the GEMM's own CTAs (one per SM, nearly all of its shared memory and a third of its registers) from
+// being placed.  Every wait is bounded (2 s, then MOKB_ST_FLAG_TIMEOUT and the kernel drains and exits).
 //
 // Macrobatches (csrc/megakernel/types.cuh:86-106, forward.cuh:89-131, backward.cuh:286-329 of the
 // reference): the routed buffers hold `macrobatch_size` rows; when the schedule has more, the rows
@@ -24,9 +28,8 @@
 // for macrobatch 0, and for every later one replays dispatch + gate/up + SwiGLU first.  Weight
 // gradients of later macrobatches are added to the stored bf16 gradient in macrobatch order, which
 // keeps results bit-reproducible.  How many macrobatches are non-empty is only known on the
-// device: all ceil(capacity / MB) are enqueued and the empty ones find no rows.
-//
-// No kernel waits on another kernel; MOKB_OVERLAP=0 puts everything on the caller's stream.
+// device: all ceil(capacity / MB) are enqueued and the empty ones find no rows.  Only macrobatch 0 is cut into
+// windows; later ones are ordered by events.  MOKB_OVERLAP=0 puts everything on the caller's stream.
 #include "layer_common.cuh"
 
 namespace mokb {
@@ -78,14 +81,14 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_arg
                  "fwd_bf16: null output");
     const bool with_down = !a->skip_down_combine;
     if (with_down)
-        MOKB_REQUIRE(a->combine_ptrs_host && a->w_shared_down && a->w_routed_down && a->y_shared && a->y_routed, "fwd_bf16: null down/combine pointer");
+        MOKB_REQUIRE(a->combine_ptrs_host && a->w_shared_down && a->w_routed_down && a->y_shared, "fwd_bf16: null down/combine pointer");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
     const int C = a->schedule_capacity;
     const Scratch s = carve(a->scratch, C, E_l, MB);
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
-    cudaStream_t s_in = overlap ? as->s1 : stream, s_out = overlap ? as->s2 : stream;
+    cudaStream_t s_in = overlap ? as->s1 : stream;
     const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
     // recompute only rebuilds macrobatch 0 (the saved context); the forward walks all of them, last first
     const int n_macro = with_down ? macrobatches(C, MB) : 1;
@@ -100,24 +103,26 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_arg
         // only macrobatch 0 (the one that is always populated) is cut into overlap windows
         const int chunk = m == 0 ? chunk_rows_for(MB, a->minibatch_size) : MB;
         const int nchunks = (hi - lo + chunk - 1) / chunk;
+        // windows of macrobatch 0 are tied to the GEMM launch by counters: the GEMM is ONE persistent launch that
+        // starts window w when the dispatch blocks of w have arrived
+        const bool flags = overlap && m == 0;
         void* x_routed = rebase(a->x_routed, lo, 2ull * H);
         void* gate_r = rebase(a->gate_routed, lo, 2ull * I);
         void* up_r = rebase(a->up_routed, lo, 2ull * I);
         void* hidden_r = rebase(a->hidden_routed, lo, 2ull * I);
-        void* y_r = with_down ? rebase(a->y_routed, lo, 2ull * H) : nullptr;
+        void* y_r = (with_down && a->y_routed) ? rebase(a->y_routed, lo, 2ull * H) : nullptr;
 
         if (overlap) {     // everything enqueued so far (previous macrobatch included) precedes this one's side work
             MOKB_CUDA(cudaEventRecord(as->fork, stream));
             MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
-            if (with_down) MOKB_CUDA(cudaStreamWaitEvent(s_out, as->fork, 0));
         }
         // dispatch: pull every scheduled row from its home rank, window by window
         for (int c = 0; c < nchunks; ++c) {
             const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
             MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
-                                        x_routed, nullptr, nullptr, comm_blocks, s_in));
-            if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+                                        x_routed, nullptr, nullptr, comm_blocks, s_in, flags ? s.win_ready + c : nullptr));
         }
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
 
         if (!shared_done) {
             // shared expert: gate/up + SwiGLU in one pass, then down (independent of the dispatch)
@@ -136,35 +141,27 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_arg
             }
         }
 
-        // routed experts, window by window behind the dispatch
-        for (int c = 0; c < nchunks; ++c) {
-            const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
-            if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
-            mokb_gemm_args g = gemm_base(a->status);
-            g.mode = 1; g.rows_static = hi; g.row_begin = r0; g.row_end = r1;
-            g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
-            g.A = x_routed; g.lda = H; g.B = a->w_routed_gate; g.B2 = a->w_routed_up; g.ldb = H;
-            g.D = gate_r; g.D2 = up_r; g.D3 = hidden_r; g.ldd = I;
-            g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
-            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-            if (!with_down) continue;
-            g = gemm_base(a->status);
-            g.mode = 0; g.rows_static = hi; g.row_begin = r0; g.row_end = r1;
-            g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = H; g.K = I;
-            g.A = hidden_r; g.lda = I; g.B = a->w_routed_down; g.ldb = I; g.D = y_r; g.ldd = H;
-            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-            // combine: push the window's rows back to slot t*K+k of their home ranks
-            if (overlap) {
-                MOKB_CUDA(cudaEventRecord(as->ev_out[c], stream));
-                MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[c], 0));
-            }
-            MOKB_TRY(combine_rows_impl(y_r, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1,
-                                       H, nullptr, nullptr, comm_blocks, s_out));
+        // routed experts: gate/up + SwiGLU and the down projection of every window in one launch
+        if (overlap && !flags) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
+        mokb_gemm_args g = gemm_base(a->status);
+        g.mode = 4; g.rows_static = hi; g.row_begin = lo; g.row_end = hi;
+        g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
+        g.A = x_routed; g.lda = H; g.B = a->w_routed_gate; g.B2 = a->w_routed_up; g.ldb = H;
+        g.D = gate_r; g.D2 = up_r; g.D3 = hidden_r; g.ldd = I;
+        g.has_swiglu_limit = a->has_swiglu_limit; g.swiglu_limit = a->swiglu_limit;
+        g.window_rows = chunk;
+        g.blk_done = s.blk_done + lo / 256;
+        if (flags) { g.win_ready = s.win_ready; g.win_ready_target = comm_blocks; }
+        if (with_down) {
+            // combine: the epilogue of every down tile stores its rows straight into slot t*K+k of their home ranks'
+            // combine buffers (y_routed, when the caller wants it, gets a copy)
+            g.B3 = a->w_routed_down; g.ldb3 = I; g.D4 = y_r; g.ldd4 = H; g.N2 = H;
+            g.push_ptrs_host = a->combine_ptrs_host; g.push_ep_size = a->ep_size;
+            g.push_rank = a->peer_rank; g.push_idx = a->peer_token_idx;
         }
-        if (overlap && with_down) {    // the next macrobatch overwrites y_routed: the combine must be done with it
-            MOKB_CUDA(cudaEventRecord(as->join2, s_out));
-            MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
-        }
+        MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+        // the next macrobatch (or the caller) reuses x_routed: the side stream must be done with it
+        if (flags) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
     }
     return MOKB_OK;
 }
@@ -177,7 +174,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
     MOKB_REQUIRE(a->w_shared_gate && a->w_shared_up && a->w_shared_down && a->w_routed_gate && a->w_routed_up && a->w_routed_down, "bwd_bf16: null weight");
     MOKB_REQUIRE(a->x_routed && a->gate_shared && a->gate_routed && a->up_shared && a->up_routed && a->hidden_shared && a->hidden_routed,
                  "bwd_bf16: null forward context");
-    MOKB_REQUIRE(a->d_x_shared && a->d_x_routed && a->d_gate_shared && a->d_gate_routed && a->d_up_shared && a->d_up_routed &&
+    MOKB_REQUIRE(a->d_x_shared && a->d_gate_shared && a->d_gate_routed && a->d_up_shared && a->d_up_routed &&
                  a->d_hidden_shared && a->d_hidden_routed && a->d_y_routed && a->d_w_shared_gate && a->d_w_routed_gate &&
                  a->d_w_shared_up && a->d_w_routed_up && a->d_w_shared_down && a->d_w_routed_down, "bwd_bf16: null output");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
@@ -186,7 +183,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
-    cudaStream_t s_in = overlap ? as->s1 : stream, s_out = overlap ? as->s2 : stream;
+    cudaStream_t s_in = overlap ? as->s1 : stream;
     const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
     const int lim = a->has_swiglu_limit;
     const float limv = a->swiglu_limit;
@@ -213,7 +210,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
         void* d_hidden_r = rebase(a->d_hidden_routed, lo, 2ull * I);
         void* d_gate_r = rebase(a->d_gate_routed, lo, 2ull * I);
         void* d_up_r = rebase(a->d_up_routed, lo, 2ull * I);
-        void* d_x_r = rebase(a->d_x_routed, lo, 2ull * H);
+        void* d_x_r = a->d_x_routed ? rebase(a->d_x_routed, lo, 2ull * H) : nullptr;
         float* w_row = rebase(s.w_row, lo, 4);
         float* d_w_row = rebase(s.d_w_row, lo, 4);
 
@@ -226,15 +223,17 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
             MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
                                         x_routed, nullptr, nullptr, comm_blocks, s_in));
         if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));     // the replayed x is in place
-        // reverse combine: pull d_y rows, scaled by the route's router weight, in a few windows
+        // reverse combine: pull d_y rows, scaled by the route's router weight, in a few windows; in macrobatch 0 the
+        // first routed GEMM is one launch that starts each window when the window's dispatch blocks have arrived
+        const bool flags = overlap && m == 0;
         const int bchunk = bwd_chunk_rows(hi - lo, m == 0);
         const int nb = (hi - lo + bchunk - 1) / bchunk;
         for (int c = 0; c < nb; ++c) {
             const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
             MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
-                                        d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in));
-            if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+                                        d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in, flags ? s.win_ready + c : nullptr));
         }
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[0], s_in));
 
         if (m == 0) {
             // ---- shared expert (overlaps the dispatch above)
@@ -266,36 +265,33 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
             g.has_swiglu_limit = lim; g.swiglu_limit = limv;
             MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
         }
-        for (int c = 0; c < nb; ++c) {       // d_hidden = d_y * W_down, window by window behind the pull
-            const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
-            if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
-            g = gemm_base(a->status);
-            g.mode = 2; g.rows_static = hi; g.row_begin = r0; g.row_end = r1;
-            g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
-            g.A = d_y_r; g.lda = H; g.B = a->w_routed_down; g.ldb = I; g.D = d_hidden_r; g.ldd = I;
-            MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-        }
+        // d_hidden = d_y * W_down, window by window behind the pull
+        if (overlap && !flags) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[0], 0));
+        g = gemm_base(a->status);
+        g.mode = 2; g.rows_static = hi; g.row_begin = lo; g.row_end = hi;
+        g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = I; g.K = H;
+        g.A = d_y_r; g.lda = H; g.B = a->w_routed_down; g.ldb = I; g.D = d_hidden_r; g.ldd = I;
+        if (flags) { g.window_rows = bchunk; g.win_ready = s.win_ready; g.win_ready_target = comm_blocks; }
+        MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
+        // (the pulls have all arrived once that GEMM is through its last window; the event makes it formal)
+        if (flags) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[0], 0));
         MOKB_TRY(mokb_swiglu_bwd(a->gate_routed, a->up_routed, a->d_hidden_routed, a->d_gate_routed, a->d_up_routed, s.w_row, s.d_w_row,
                                  s.mb_rows + m, MB, I, lim, limv, stream));
+        // d_x = d_gate * W_gate + d_up * W_up; the epilogue stores every row straight into slot t*K+k of its home rank's
+        // d_x_routed buffer, and the route's router-weight gradient with it (the reverse dispatch)
         g = gemm_base(a->status);
         g.mode = 2; g.rows_static = hi; g.row_begin = lo; g.row_end = hi;
         g.num_rows = s.n_rows; g.group_of_block = s.group_of_block; g.G = E_l; g.N = H; g.K = I;
         g.A = d_gate_r; g.B = a->w_routed_gate; g.A2 = d_up_r; g.B2 = a->w_routed_up; g.lda = I; g.ldb = H;
         g.D = d_x_r; g.ldd = H;
+        g.push_ptrs_host = a->d_x_routed_ptrs_host; g.push_ep_size = a->ep_size;
+        g.push_rank = a->peer_rank; g.push_idx = a->peer_token_idx;
+        g.push_values = d_w_row; g.push_value_ptrs_host = a->d_router_weight_ptrs_host;
         MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
-        // reverse dispatch: push d_x rows and the per-route router-weight gradient home (overlaps the weight gradients)
-        if (overlap) {
-            MOKB_CUDA(cudaEventRecord(as->ev_out[0], stream));
-            MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[0], 0));
-        }
-        MOKB_TRY(combine_rows_impl(d_x_r, a->d_x_routed_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi,
-                                   H, d_w_row, a->d_router_weight_ptrs_host, comm_blocks, s_out));
-        if (overlap) MOKB_CUDA(cudaEventRecord(as->join2, s_out));
         const int32_t* offs = s.mb_offsets + static_cast<size_t>(m) * (E_l + 1);
         MOKB_TRY(wgrad(d_y_r, H, hidden_r, I, a->d_w_routed_down, E_l, hi, offs, m > 0));
         MOKB_TRY(wgrad(d_gate_r, I, x_routed, H, a->d_w_routed_gate, E_l, hi, offs, m > 0));
         MOKB_TRY(wgrad(d_up_r, I, x_routed, H, a->d_w_routed_up, E_l, hi, offs, m > 0));
-        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
     }
     return MOKB_OK;
 }

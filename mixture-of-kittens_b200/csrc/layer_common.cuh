@@ -23,16 +23,23 @@ struct Scratch {
     int32_t* group_of_block;   // [capacity / 128]
     float* w_row;              // [MB] router weight of each routed row of the current macrobatch (backward)
     float* d_w_row;            // [MB] router-weight gradient of each routed row (backward)
+    // counters between kernels that run at the same time (zeroed by the prologue of every call)
+    int32_t* win_ready;        // [kMaxChunks] blocks of the dispatch launch of window w that have finished
+    int32_t* win_done;         // [kMaxChunks] epilogue warps that have stored a down tile of window w
+    int32_t* blk_done;         // [capacity / 256] epilogue warps that have stored a gate/up tile of a 256-row block
 };
 
 inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
 inline int macrobatches(int capacity, int MB) { return (capacity + MB - 1) / MB; }
 
+constexpr int kMaxChunks = 32;     // windows per macrobatch (side-stream events, counters)
+
 inline size_t scratch_bytes(int capacity, int E_l, int MB) {
     const size_t nm = macrobatches(capacity, MB);
     return align256((E_l + 1) * 4) + 512 + align256(nm * 4) + align256(nm * (E_l + 1) * 4) +
-           align256(static_cast<size_t>(capacity / 128) * 4) + 2 * align256(static_cast<size_t>(MB) * 4);
+           align256(static_cast<size_t>(capacity / 128) * 4) + 2 * align256(static_cast<size_t>(MB) * 4) +
+           2 * align256(kMaxChunks * 4) + align256(static_cast<size_t>(capacity / 256) * 4);
 }
 
 inline Scratch carve(void* base, int capacity, int E_l, int MB) {
@@ -46,7 +53,10 @@ inline Scratch carve(void* base, int capacity, int E_l, int MB) {
     s.mb_offsets = reinterpret_cast<int32_t*>(p); p += align256(nm * (E_l + 1) * 4);
     s.group_of_block = reinterpret_cast<int32_t*>(p); p += align256(static_cast<size_t>(capacity / 128) * 4);
     s.w_row = reinterpret_cast<float*>(p); p += align256(static_cast<size_t>(MB) * 4);
-    s.d_w_row = reinterpret_cast<float*>(p);
+    s.d_w_row = reinterpret_cast<float*>(p); p += align256(static_cast<size_t>(MB) * 4);
+    s.win_ready = reinterpret_cast<int32_t*>(p); p += align256(kMaxChunks * 4);
+    s.win_done = reinterpret_cast<int32_t*>(p); p += align256(kMaxChunks * 4);
+    s.blk_done = reinterpret_cast<int32_t*>(p);
     return s;
 }
 
@@ -98,6 +108,8 @@ __global__ void prologue_kernel(const int32_t* __restrict__ tokens_per_expert, c
         }
         s.group_of_block[b] = g;
     }
+    for (int i = threadIdx.x; i < kMaxChunks; i += blockDim.x) s.win_ready[i] = s.win_done[i] = 0;
+    for (int i = threadIdx.x; i < capacity / 256; i += blockDim.x) s.blk_done[i] = 0;
 }
 
 inline int run_prologue(const int32_t* tpe, const int32_t* num_tokens, int E_l, int C, int MB, int T, const Scratch& s, int32_t* status, cudaStream_t stream) {
@@ -136,7 +148,6 @@ int check_common(const A* a, const char* who) {
 }  // namespace
 
 // ---- side streams and events, one set per device, created on first use (defined in layer.cu)
-constexpr int kMaxChunks = 32;
 
 struct Async {
     bool ready = false;

@@ -261,6 +261,7 @@ int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int
     if (row_begin == row_end) return MOKB_OK;
     MOKB_REQUIRE(E <= 65535 && M / 128 <= 65535, "mxfp8_quantize: tensor too large for one launch");
     const dim3 grid(static_cast<unsigned>(N / 128), static_cast<unsigned>((row_end - row_begin) / 128), static_cast<unsigned>(E));
+    share_sms_with_gemm(quantize_kernel);
     quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), M, N, RowWindow{num_rows, row_begin, row_end},
                                               static_cast<uint8_t*>(x_fp8), static_cast<uint8_t*>(x_sc),
                                               static_cast<uint8_t*>(x_fp8_t), static_cast<uint8_t*>(x_sc_t));
@@ -287,6 +288,7 @@ int swiglu_bwd_quant_impl(const void* gate_q, const void* gate_sc, const void* u
     MOKB_CUDA(cudaFuncSetAttribute(swiglu_bwd_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const RowWindow win{num_rows, row_begin, row_end};
     const dim3 grid(static_cast<unsigned>(I / 128), static_cast<unsigned>((row_end - row_begin) / 128));
+    share_sms_with_gemm(swiglu_bwd_quant_kernel);
     swiglu_bwd_quant_kernel<<<grid, 256, smem, stream>>>(
         static_cast<const uint8_t*>(gate_q), static_cast<const uint8_t*>(gate_sc), static_cast<const uint8_t*>(up_q),
         static_cast<const uint8_t*>(up_sc), static_cast<const __nv_bfloat16*>(d_hidden), rows_cap, I, win, Clamp{has_limit, limit},

@@ -25,13 +25,14 @@ lib = ctypes.CDLL(_LIB_PATH)
 c_int, c_i64, c_f32, c_vp, c_sz = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
 c_u64p = ctypes.POINTER(ctypes.c_uint64)
 
-ST_OK, ST_SCHEDULE_OVERFLOW, ST_BARRIER_TIMEOUT, ST_PIPELINE_TIMEOUT, ST_MACROBATCH_OVERFLOW = range(5)
+ST_OK, ST_SCHEDULE_OVERFLOW, ST_BARRIER_TIMEOUT, ST_PIPELINE_TIMEOUT, ST_MACROBATCH_OVERFLOW, ST_FLAG_TIMEOUT = range(6)
 STATUS_TEXT = {
     ST_OK: "ok",
     ST_SCHEDULE_OVERFLOW: "the padded routed rows exceed schedule_capacity",
     ST_BARRIER_TIMEOUT: "a rank did not arrive at barrier_all in time",
     ST_PIPELINE_TIMEOUT: "a pipeline wait inside a GEMM kernel ran out",
     ST_MACROBATCH_OVERFLOW: "the padded routed rows exceed macrobatch_size",
+    ST_FLAG_TIMEOUT: "a wait on a counter raised by another kernel or CTA ran out",
 }
 
 
@@ -71,7 +72,11 @@ class GemmArgs(ctypes.Structure):
                 ("group_offsets", c_vp), ("G", c_int), ("M", c_int), ("N", c_int), ("K", c_int),
                 ("A", c_vp), ("B", c_vp), ("A2", c_vp), ("B2", c_vp), ("lda", c_int), ("ldb", c_int),
                 ("D", c_vp), ("D2", c_vp), ("D3", c_vp), ("ldd", c_int), ("has_swiglu_limit", c_int),
-                ("swiglu_limit", c_f32), ("accumulate", c_int), ("status", c_vp)]
+                ("swiglu_limit", c_f32), ("accumulate", c_int), ("status", c_vp),
+                ("B3", c_vp), ("D4", c_vp), ("N2", c_int), ("ldb3", c_int), ("ldd4", c_int), ("window_rows", c_int),
+                ("win_ready", c_vp), ("win_ready_target", c_int), ("blk_done", c_vp), ("win_done", c_vp),
+                ("push_ptrs_host", c_u64p), ("push_ep_size", c_int), ("push_rank", c_vp), ("push_idx", c_vp),
+                ("push_values", c_vp), ("push_value_ptrs_host", c_u64p)]
 
 
 class GemmFp8Args(ctypes.Structure):
@@ -114,6 +119,11 @@ _sig("mokb_grouped_gemm_bf16", c_int, ctypes.POINTER(GemmArgs), c_vp)
 _sig("mokb_grouped_gemm_mxfp8", c_int, ctypes.POINTER(GemmFp8Args), c_vp)
 _sig("mokb_dispatch_rows", c_int, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_i64, c_vp, c_u64p, c_vp, c_vp)
 _sig("mokb_combine_rows", c_int, c_vp, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_vp, c_u64p, c_vp)
+_sig("mokb_comm_default_blocks", c_int)
+_sig("mokb_dispatch_rows_window", c_int, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_i64, c_vp, c_u64p, c_vp, c_int,
+     c_vp, c_vp)
+_sig("mokb_combine_rows_window", c_int, c_vp, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_i64, c_vp, c_u64p, c_int, c_vp,
+     c_int, c_vp, c_vp)
 _sig("mokb_swiglu_fwd", c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_f32, c_vp)
 _sig("mokb_swiglu_bwd", c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_f32, c_vp)
 
@@ -124,6 +134,7 @@ EXPORTED = [
     "mokb_mxfp8_quantize", "mokb_fwd_epilogue", "mokb_bwd_epilogue", "mokb_layer_scratch_bytes",
     "mokb_dispatch_mlp_swiglu_combine_fwd_bf16", "mokb_dispatch_mlp_swiglu_combine_bwd_bf16",
     "mokb_grouped_gemm_bf16", "mokb_grouped_gemm_mxfp8", "mokb_dispatch_rows", "mokb_combine_rows", "mokb_swiglu_fwd", "mokb_swiglu_bwd",
+    "mokb_comm_default_blocks", "mokb_dispatch_rows_window", "mokb_combine_rows_window",
 ]
 
 
@@ -161,6 +172,12 @@ class MokError(RuntimeError):
     pass
 
 
+# The BF16 layer sends the rows of y_routed / d_x_routed to their home ranks from the epilogue of the GEMM that computes
+# them, so those two outputs (staging buffers in the reference, read by nothing afterwards) stay unwritten unless this
+# is set: MOKB_KEEP_STAGING_ROWS=1 in the environment, or the attribute at run time.
+KEEP_STAGING_ROWS = os.environ.get("MOKB_KEEP_STAGING_ROWS", "0") == "1"
+
+
 def _ck(rc: int) -> None:
     if rc != 0:
         raise MokError(f"mok_b200 error {rc}: {_last_error().decode(errors='replace')}")
@@ -186,7 +203,7 @@ def status_tensor(device: torch.device | None = None) -> torch.Tensor:
     idx = torch.cuda.current_device() if device is None or device.index is None else device.index
     t = _STATUS.get(idx)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        t = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))      # code + three words of detail
         _STATUS[idx] = t
     return t
 
@@ -194,10 +211,20 @@ def status_tensor(device: torch.device | None = None) -> torch.Tensor:
 def check_status(device: torch.device | None = None, *, reset: bool = True) -> int:
     """Reads the status word (synchronises the host: for tests and debugging, never called by the layer)."""
     t = status_tensor(device)
-    code = int(t.item())
+    words = t.tolist()
+    code = int(words[0])
+    _LAST_DETAIL[:] = words
     if reset and code:
         t.zero_()
     return code
+
+
+_LAST_DETAIL = [0, 0, 0, 0]
+
+
+def status_detail() -> list[int]:
+    """The four status words as the last check_status() read them: [code, kind, index, value seen << 16 | target]."""
+    return list(_LAST_DETAIL)
 
 
 def raise_for_status(device: torch.device | None = None) -> None:
@@ -347,7 +374,9 @@ def _fwd_bf16(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_r
     a.x_routed = _p(x_routed)
     a.gate_shared, a.up_shared, a.hidden_shared = _p(gate_shared), _p(up_shared), _p(hidden_shared)
     a.gate_routed, a.up_routed, a.hidden_routed = _p(gate_routed), _p(up_routed), _p(hidden_routed)
-    a.y_shared, a.y_routed = _p(y_shared), _p(y_routed)
+    # y_routed is the reference's staging buffer of the combine (its rows go to the peers from there); here the rows
+    # go to the peers from the GEMM's epilogue and the tensor is only filled on request
+    a.y_shared, a.y_routed = _p(y_shared), (_p(y_routed) if KEEP_STAGING_ROWS else None)
     a.skip_down_combine = 1 if skip_down_combine else 0
     _ck(lib.mokb_dispatch_mlp_swiglu_combine_fwd_bf16(ctypes.byref(a), _stream()))
     return x_routed, gate_shared, gate_routed, up_shared, up_routed, hidden_shared, hidden_routed, y_shared, y_routed
@@ -404,7 +433,7 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(d_y_buffer, d_y_buffer_ptrs, d_x_routed
     d_w_shared_down = torch.empty(H, I, **bf)
     d_w_routed_gate, d_w_routed_up = torch.empty(E_l, I, H, **bf), torch.empty(E_l, I, H, **bf)
     d_w_routed_down = torch.empty(E_l, H, I, **bf)
-    a.d_x_shared, a.d_x_routed = _p(d_x_shared), _p(d_x_routed)
+    a.d_x_shared, a.d_x_routed = _p(d_x_shared), (_p(d_x_routed) if KEEP_STAGING_ROWS else None)
     a.d_gate_shared, a.d_gate_routed, a.d_up_shared, a.d_up_routed = (_p(d_gate_shared), _p(d_gate_routed),
                                                                      _p(d_up_shared), _p(d_up_routed))
     a.d_hidden_shared, a.d_hidden_routed, a.d_y_routed = _p(d_hidden_shared), _p(d_hidden_routed), _p(d_y_routed)
@@ -422,8 +451,25 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(d_y_buffer, d_y_buffer_ptrs, d_x_routed
 # ----------------------------------------------------------------------------
 def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None, group_offsets=None, G=1,
                  M=0, N=0, K=0, A2=None, B2=None, D2=None, D3=None, lda=None, ldb=None, ldd=None, swiglu_limit=None,
-                 row_begin=0, row_end=0, accumulate=False):
+                 row_begin=0, row_end=0, accumulate=False, B3=None, D4=None, N2=0, window_rows=0, win_ready=None,
+                 win_ready_target=0, blk_done=None, win_done=None, push_ptrs=None, push_rank=None, push_idx=None,
+                 push_values=None, push_value_ptrs=None, N2_ld=None):
+    """Modes 0-3 as in the header; mode 4 = gate/up + SwiGLU (B, B2 -> D, D2, D3) and the down projection
+    (D3, B3 -> D4 [rows, N2]) in one launch, with the optional window counters."""
     g = GemmArgs()
+    g.B3, g.D4, g.N2 = _p(B3), _p(D4), N2
+    g.ldb3 = B3.shape[-1] if B3 is not None else 0
+    g.ldd4 = D4.shape[-1] if D4 is not None else (N2_ld or N2)
+    keep = []
+    if push_ptrs is not None:
+        keep.append(_ptr_array(push_ptrs))
+        g.push_ptrs_host, g.push_ep_size = keep[-1], len(push_ptrs)
+        g.push_rank, g.push_idx, g.push_values = _p(push_rank), _p(push_idx), _p(push_values)
+        if push_value_ptrs is not None:
+            keep.append(_ptr_array(push_value_ptrs))
+            g.push_value_ptrs_host = keep[-1]
+    g.window_rows, g.win_ready, g.win_ready_target = window_rows, _p(win_ready), win_ready_target
+    g.blk_done, g.win_done = _p(blk_done), _p(win_done)
     g.mode = mode
     g.accumulate = 1 if accumulate else 0
     g.row_begin, g.row_end = row_begin, row_end
@@ -434,7 +480,7 @@ def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None
     g.lda = A.shape[-1] if lda is None else lda
     g.ldb = B.shape[-1] if ldb is None else ldb
     g.D, g.D2, g.D3 = _p(D), _p(D2), _p(D3)
-    g.ldd = D.shape[-1] if ldd is None else ldd
+    g.ldd = (D.shape[-1] if D is not None else N) if ldd is None else ldd
     g.has_swiglu_limit = 0 if swiglu_limit is None else 1
     g.swiglu_limit = 0.0 if swiglu_limit is None else float(swiglu_limit)
     g.status = _p(status_tensor(A.device))
@@ -477,6 +523,26 @@ def combine_rows(src, dst_ptrs, peer_rank, peer_token_idx, num_rows, max_rows, h
     _ck(lib.mokb_combine_rows(_p(src), _ptr_array(dst_ptrs), len(dst_ptrs), _p(peer_rank), _p(peer_token_idx),
                               _p(num_rows), max_rows, hidden, _p(row_values),
                               None if value_ptrs is None else _ptr_array(value_ptrs), _stream()))
+
+
+def comm_default_blocks() -> int:
+    return int(lib.mokb_comm_default_blocks())
+
+
+def dispatch_rows_window(src_ptrs, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, row_divisor, hidden, dst,
+                         row_scale_ptrs=None, row_scale_out=None, blocks=0, done_counter=None):
+    _ck(lib.mokb_dispatch_rows_window(_ptr_array(src_ptrs), len(src_ptrs), _p(peer_rank), _p(peer_token_idx), _p(num_rows),
+                                      max_rows, row_begin, row_end, row_divisor, hidden, _p(dst),
+                                      None if row_scale_ptrs is None else _ptr_array(row_scale_ptrs), _p(row_scale_out),
+                                      blocks, _p(done_counter), _stream()))
+
+
+def combine_rows_window(src, dst_ptrs, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, hidden,
+                        row_values=None, value_ptrs=None, blocks=0, wait_counter=None, arrivals_per_row_block=0):
+    _ck(lib.mokb_combine_rows_window(_p(src), _ptr_array(dst_ptrs), len(dst_ptrs), _p(peer_rank), _p(peer_token_idx),
+                                     _p(num_rows), max_rows, row_begin, row_end, hidden, _p(row_values),
+                                     None if value_ptrs is None else _ptr_array(value_ptrs), blocks, _p(wait_counter),
+                                     arrivals_per_row_block, _p(status_tensor(src.device)), _stream()))
 
 
 def swiglu_fwd(gate, up, swiglu_limit=None, num_rows=None):

@@ -37,6 +37,8 @@ def run_parity(rank: int, world: int, dev: torch.device, group=None) -> dict:
     report = {"rank": rank, "world": world, "checks": {}}
     ok = True
     for case, (T, H, I, E_l, K, routing, limit) in enumerate(CASES):
+        if world == 1:
+            E_l = max(E_l, K + 2)     # a single rank holds all experts: keep more experts than top-k choices
         E = E_l * world
         ranks = O.make_inputs(R=world, T=T, H=H, I=I, E=E, K=K, seed=40 + case, routing=routing)
         factor = max(2, world)

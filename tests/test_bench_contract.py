@@ -61,7 +61,7 @@ def test_parity_summary_and_byte_model():
     prob = types.SimpleNamespace(H=2048, I=1024, T=4096, K=4, flops=lambda: 18.0 * 4096 * 5 * 2048 * 1024)
     m = bench.gate_up_bytes(prob, 20224, 32)
     assert m["total"] == 20224 * 2048 * 2 + 32 * 2 * 1024 * 2048 * 2 + 3 * 20224 * 1024 * 2
-    recs = [("gemm_bf16_gate_up_swiglu", 0, 0, 0.0, 1.0), ("dispatch", 0, 1, 0.0, 0.5), ("gemm_bf16_nt", 0, 0, 1.0, 2.0)]
+    recs = [("gemm_bf16_fwd_routed", 0, 0, 0.0, 1.0), ("dispatch", 0, 1, 0.0, 0.5), ("gemm_bf16_nt", 0, 0, 1.0, 2.0)]
     ins = bench.in_step_summary(recs, "gemm_bf16", prob, 16384, 1000.0)
-    assert ins["gemm_launches"] == 2 and ins["gemm_busy_ms"] == 2.0 and ins["gate_up_ms"] == 1.0 and ins["step_ms_traced"] == 2.0
-    assert abs(ins["gate_up_tflops"] - 4.0 * (16384 + 4096) * 2048 * 1024 / 1e-3 / 1e12) < 1e-6
+    assert ins["gemm_launches"] == 2 and ins["gemm_busy_ms"] == 2.0 and ins["fwd_routed_ms"] == 1.0 and ins["step_ms_traced"] == 2.0
+    assert abs(ins["fwd_routed_tflops"] - 6.0 * 16384 * 2048 * 1024 / 1e-3 / 1e12) < 1e-6

@@ -31,9 +31,9 @@ def pairs_walk_three_tiles(tiles):
 
 
 # (rows per group, H, I): config 2, config 5 (I = 11 * 128), config 4
-FWD_SHAPES = [([1024, 0, 2560, 512], 7168, 2048), ([2048, 0, 3072, 512], 5120, 1408), ([512, 3584, 0, 256], 4096, 1536)]
+FWD_SHAPES = [([1024, 0, 2560, 512], 7168, 2048), ([2048, 0, 3072, 512], 5120, 1408), ([512, 4608, 0, 256], 4096, 1536)]
 DOWN_SHAPES = [([1024, 0, 2560, 512], 7168, 2048), ([2560, 0, 1024, 512], 5120, 1408), ([512, 3328, 0, 256], 4096, 1536)]
-DGRAD_SHAPES = [([2048, 0, 4608, 512], 7168, 2048), ([3072, 0, 4608, 512], 5120, 1408), ([512, 6656, 0, 1024], 4096, 1536)]
+DGRAD_SHAPES = [([2048, 0, 4608, 512], 7168, 2048), ([3072, 0, 5888, 512], 5120, 1408), ([512, 7936, 0, 1024], 4096, 1536)]
 
 
 @pytest.mark.parametrize("rows_per_group,H,I", FWD_SHAPES, ids=["c2", "c5", "c4"])

@@ -41,7 +41,7 @@ def run_layer(inp_cpu, E_l, *, limit=None, MB=None, mb=256, recompute=False, mul
     grads = F.backward(cfg, ws, sched, ctx, inp.grad_output, inp.x, inp.router_weights, inp.w_shared_gate,
                        inp.w_shared_up, inp.w_shared_down, inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down, limit)
     torch.cuda.synchronize()
-    assert _C.check_status() == 0
+    assert _C.check_status() == 0, _C.status_detail()
     return sched, out, saved, ctx2, grads, ws
 
 
@@ -143,13 +143,16 @@ def test_launch_timeline_records_every_phase_in_order():
     run_layer(ranks[0], 4)
     recs = _C.trace_end()
     tags = [r[0] for r in recs]
-    for expected in ("schedule", "dispatch", "gemm_bf16_gate_up_swiglu", "gemm_bf16_nt",
-                     "combine", "fwd_epilogue", "dispatch_scaled", "gemm_bf16_nn", "swiglu_bwd", "gemm_bf16_wgrad", "bwd_epilogue"):
+    for expected in ("schedule", "dispatch", "gemm_bf16_gate_up_swiglu", "gemm_bf16_nt", "gemm_bf16_fwd_routed",
+                     "fwd_epilogue", "dispatch_scaled", "gemm_bf16_nn", "swiglu_bwd", "gemm_bf16_wgrad", "bwd_epilogue"):
         assert expected in tags, expected
+    assert "combine" not in tags             # the rows go home from the epilogues of the GEMMs that compute them
+    assert tags.count("gemm_bf16_fwd_routed") == 1      # one persistent launch for every window of the routed forward
     assert all(0.0 <= b <= e for _, _, _, b, e in recs)
-    assert len({r[2] for r in recs}) == 3    # the caller's stream and the two side streams
+    assert len({r[2] for r in recs}) == 2    # the caller's stream and the side stream of the pulls
     first = {t: min(r[3] for r in recs if r[0] == t) for t in set(tags)}
-    assert first["schedule"] < first["dispatch"] < first["combine"] < first["fwd_epilogue"] < first["dispatch_scaled"] < first["bwd_epilogue"]
+    assert (first["schedule"] < first["dispatch"] < first["gemm_bf16_fwd_routed"] < first["fwd_epilogue"]
+            < first["dispatch_scaled"] < first["bwd_epilogue"])
     assert _C.trace_end() == []              # recording has stopped
 
 

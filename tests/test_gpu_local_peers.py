@@ -81,3 +81,65 @@ def test_dispatch_and_combine_over_local_peers(R, T, K, H, E_l):
     for r in range(R):      # every route of every home rank came back to slot t*K+k, from whichever rank owns its expert
         assert torch.equal(comb[r].view(T, K, H), x[r][:, None, :].expand(T, K, H)), f"home rank {r}: combine buffer differs"
         assert torch.equal(vals[r].cpu(), owner_row[r]), f"home rank {r}: per-route values differ"
+
+
+@pytest.mark.parametrize("R,T,K,H,I,E_l", [(4, 512, 2, 512, 256, 2), (8, 512, 4, 256, 384, 1)])
+def test_gemm_epilogue_pushes_rows_to_local_peers_like_a_combine_launch(R, T, K, H, I, E_l):
+    """The down projection (mode 0, and as the second phase of mode 4) and the dual input gradient (mode 2) with their
+    rows pushed to the home ranks' buffers from the epilogue: bit for bit what the plain GEMM followed by combine_rows
+    leaves there, including the per-route value that travels with the input gradient."""
+    from mok import _C
+    routes = make_routes(R, T, K, E_l, seed=80 + R)
+    q = R - 1                                                      # the rank whose experts we run
+    C = T * K * R
+    pr, pt, nt, tpe = O.schedule(routes, E_l, C, q)
+    N = int(nt[0])
+    prd, ptd, ntd = (torch.from_numpy(a).cuda() for a in (pr, pt, nt))
+    gob = torch.repeat_interleave(torch.arange(E_l, dtype=torch.int32), torch.from_numpy(tpe // 128).long())
+    gob = torch.cat([gob, torch.full((C // 128 - gob.numel(),), -1, dtype=torch.int32)]).cuda()
+    gd = torch.Generator(device="cuda").manual_seed(81)
+    rnd = lambda *shape, scale=1.0: (torch.randn(*shape, generator=gd, device="cuda") * scale).to(torch.bfloat16)
+    hid, Wd = rnd(C, I), rnd(E_l, H, I, scale=0.05)
+    x, Wg, Wu = rnd(C, H), rnd(E_l, I, H, scale=0.05), rnd(E_l, I, H, scale=0.05)
+    dg, du = rnd(C, I), rnd(C, I)
+    rowv = torch.arange(C, dtype=torch.float32, device="cuda") * 0.5
+    zeros = lambda: [torch.zeros(T * K, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+    ptrs = lambda ts: [t.data_ptr() for t in ts]
+
+    # reference: GEMM into a local buffer, then the combine kernel
+    y = torch.empty(C, H, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm(0, hid, Wd, y, num_rows=ntd, group_of_block=gob, G=E_l, N=H, K=I)
+    want = zeros()
+    _C.combine_rows(y, ptrs(want), prd, ptd, ntd, C, H)
+    dx = torch.empty(C, H, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm(2, dg, Wg, dx, num_rows=ntd, group_of_block=gob, G=E_l, N=H, K=I, A2=du, B2=Wu)
+    want_dx, want_val = zeros(), [torch.full((T * K,), -1.0, device="cuda") for _ in range(R)]
+    _C.combine_rows(dx, ptrs(want_dx), prd, ptd, ntd, C, H, rowv, ptrs(want_val))
+
+    # mode 0, pushed only (no local copy)
+    got = zeros()
+    _C.grouped_gemm(0, hid, Wd, None, rows=C, num_rows=ntd, group_of_block=gob, G=E_l, N=H, K=I, ldd=H,
+                    push_ptrs=ptrs(got), push_rank=prd, push_idx=ptd)
+    # mode 2 with a second operand pair, a local copy and the per-route values
+    got_dx, got_val = zeros(), [torch.full((T * K,), -1.0, device="cuda") for _ in range(R)]
+    dx2 = torch.full((C, H), 3.0, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm(2, dg, Wg, dx2, num_rows=ntd, group_of_block=gob, G=E_l, N=H, K=I, A2=du, B2=Wu,
+                    push_ptrs=ptrs(got_dx), push_rank=prd, push_idx=ptd, push_values=rowv, push_value_ptrs=ptrs(got_val))
+    # mode 4: gate/up + SwiGLU + down, the down rows pushed only
+    gate, up, hid4 = (torch.empty(C, I, dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    blk = torch.zeros(C // 256, dtype=torch.int32, device="cuda")
+    got4 = zeros()
+    _C.grouped_gemm(4, x, Wg, gate, num_rows=ntd, group_of_block=gob, G=E_l, N=I, K=H, B2=Wu, D2=up, D3=hid4, B3=Wd, N2=H,
+                    window_rows=512, blk_done=blk, push_ptrs=ptrs(got4), push_rank=prd, push_idx=ptd)
+    y4 = torch.empty(C, H, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm(0, hid4, Wd, y4, num_rows=ntd, group_of_block=gob, G=E_l, N=H, K=I)
+    want4 = zeros()
+    _C.combine_rows(y4, ptrs(want4), prd, ptd, ntd, C, H)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0
+    assert int(((torch.from_numpy(pr[:N]) >= 0) & (torch.from_numpy(pr[:N]) != q)).sum()) > 0
+    for r in range(R):
+        assert torch.equal(got[r], want[r]), f"mode 0: rank {r}'s buffer differs"
+        assert torch.equal(got_dx[r], want_dx[r]) and torch.equal(got_val[r], want_val[r]), f"mode 2: rank {r}'s buffers differ"
+        assert torch.equal(got4[r], want4[r]), f"mode 4: rank {r}'s buffer differs"
+    assert torch.equal(dx2[:N], dx[:N]) and torch.all(dx2[N:] == 3.0)
