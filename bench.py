@@ -14,7 +14,12 @@ Per-GPU work is fixed as N grows (weak scaling).
   value      tokens/s over all ranks with the step's inputs already resident in HBM
   e2e        the same through mok.functional with the inputs in pinned HOST memory: host->device
              copies of x, top_experts, router_weights, grad_output and a device->host read of
-             the result checksums are inside the timed region
+             the result checksums are inside the timed region (double-buffered over two workspaces;
+             e2e.serial: the copies on the compute stream before each step)
+  parity     small multi-rank cases against the CPU oracle on every rank, run before anything is
+             timed; a mismatch ends the run with a non-zero exit code
+  in_step    GEMM time inside one traced step and the algorithmic TFLOP/s that corresponds to it
+  ep8_share_1gpu  (1 GPU) one rank's share of the EP=8 run (32 experts), the anchor for 1 -> 8 scaling
   roofline   the dominant kernel (routed gate/up grouped GEMM with fused SwiGLU): algorithmic
              FLOPs per launch / its mean launch time (CUDA events, timed alone) over the
              measured cuBLAS BF16 burst peak of this pool (MEASURED_PEAKS.json)
@@ -348,12 +353,13 @@ class Problem:
     """One workload on this rank: inputs in pinned host memory, weights and the workspace on the device, and the
     BF16 / MXFP8 step functions (build_schedule + forward + backward through mok.functional)."""
 
-    def __init__(self, name, args, rank, world, device, group):
+    def __init__(self, name, args, rank, world, device, group, *, tokens=None, minibatch=None, host_inputs=True):
         from mok import functional as F
         self.F, self.name, self.rank, self.world, self.device, self.group = F, name, rank, world, device, group
         T, H, I, E, K, mb, mult, routing = WORKLOADS[name]
-        if args.minibatch:
-            mb = args.minibatch
+        T = tokens or T
+        if minibatch or args.minibatch:
+            mb = minibatch or args.minibatch
         assert E % world == 0
         E_l = E // world
         MB = int(math.ceil((T * K + E_l * 256) / mb) * mb)
@@ -362,18 +368,22 @@ class Problem:
         if args.comm_sms:
             kw.update(fwd_num_comm_sms=args.comm_sms, bwd_num_comm_sms=args.comm_sms)
         self.cfg = F.MoKConfig(**kw)
-        g = torch.Generator().manual_seed(1000 + rank)
-        self.x_h = torch.randn(T, H, generator=g).to(torch.bfloat16).pin_memory()
-        self.gy_h = torch.randn(T, H, generator=g).to(torch.bfloat16).pin_memory()
-        logits = torch.randn(T, E, generator=g)
+        # per-step inputs: in pinned host memory for the end-to-end legs; sweeps generate them on the device
+        gen_dev = torch.device("cpu") if host_inputs else device
+        g = torch.Generator(device=gen_dev).manual_seed(1000 + rank)
+        pin = (lambda t: t.pin_memory()) if host_inputs else (lambda t: t)
+        self.x_h = pin(torch.randn(T, H, generator=g, device=gen_dev).to(torch.bfloat16))
+        self.gy_h = pin(torch.randn(T, H, generator=g, device=gen_dev).to(torch.bfloat16))
+        logits = torch.randn(T, E, generator=g, device=gen_dev)
         if routing == "zipf":
             perm = torch.randperm(E, generator=torch.Generator().manual_seed(7))
             bias = torch.empty(E)
             bias[perm] = -1.2 * torch.log(torch.arange(1, E + 1, dtype=torch.float32))
-            logits = logits + bias
+            logits = logits + bias.to(gen_dev)
         vals, idx = torch.topk(logits, K, dim=1)
-        self.te_h = idx.to(torch.int64).pin_memory()
-        self.rw_h = torch.softmax(vals.float(), -1).pin_memory()
+        self.te_h = pin(idx.to(torch.int64))
+        self.rw_h = pin(torch.softmax(vals.float(), -1))
+        del logits
         gd = torch.Generator(device=device).manual_seed(2000 + rank)
 
         def w(*shape):
@@ -399,15 +409,16 @@ class Problem:
     def flops(self):
         return layer_flops(self.T, self.K, self.H, self.I)
 
-    def step(self, x=None, te=None, rw=None, gy=None):
+    def step(self, x=None, te=None, rw=None, gy=None, ws=None):
         F = self.F
+        ws = ws or self.ws
         x, te, rw, gy = (self.x_d if x is None else x, self.te_d if te is None else te,
                          self.rw_d if rw is None else rw, self.gy_d if gy is None else gy)
-        sched = F.build_schedule(self.ws, self.cfg, te, num_local_experts=self.E_l)
-        out, ctx = F.forward(self.cfg, self.ws, sched, x, rw, *self.shared, *self.routed)
+        sched = F.build_schedule(ws, self.cfg, te, num_local_experts=self.E_l)
+        out, ctx = F.forward(self.cfg, ws, sched, x, rw, *self.shared, *self.routed)
         if self.mid is not None:
             self.mid.record()
-        grads = F.backward(self.cfg, self.ws, sched, ctx, gy, x, rw, *self.shared, *self.routed)
+        grads = F.backward(self.cfg, ws, sched, ctx, gy, x, rw, *self.shared, *self.routed)
         return sched, out, grads
 
     def quantise_weights(self):
@@ -510,6 +521,87 @@ def gate_up_bytes(prob, padded_rows, experts_used):
     return {"a_rows": a, "weights": wts, "outputs": outs, "total": a + wts + outs}
 
 
+def fwd_routed_bytes(prob, padded_rows, experts_used):
+    """Algorithmic HBM bytes of the routed forward launch: the gate/up part plus the down weights and the y rows
+    (hidden is read back from L2 / HBM once)."""
+    m = gate_up_bytes(prob, padded_rows, experts_used)
+    m["weights"] += experts_used * prob.H * prob.I * 2
+    m["hidden_reread"] = padded_rows * prob.I * 2
+    m["outputs"] += padded_rows * prob.H * 2
+    m["total"] = m["a_rows"] + m["weights"] + m["outputs"] + m["hidden_reread"]
+    return m
+
+
+def comm_alone(prob, sched, timed, _C, rank):
+    """Dispatch (row pull) and combine (row push) kernels alone over all scheduled rows, every rank at once."""
+    remote = int(((sched.peer_rank >= 0) & (sched.peer_rank != rank)).sum().item())
+    buf = torch.empty(prob.MB, prob.H, dtype=torch.bfloat16, device=prob.device)
+    ws, out = prob.ws, {"remote_rows": remote}
+    for name, fn in (
+        ("dispatch", lambda: _C.dispatch_rows(ws.x_buffer_ptrs, sched.peer_rank, sched.peer_token_idx, sched.num_tokens,
+                                              prob.MB, prob.K, prob.H, buf)),
+        ("combine", lambda: _C.combine_rows(buf, ws.combine_buffer_ptrs, sched.peer_rank, sched.peer_token_idx,
+                                            sched.num_tokens, prob.MB, prob.H)),
+    ):
+        fn()
+        ms = timed(fn, 5)[0] / 5
+        gbs = remote * prob.H * 2 / (ms / 1000.0) / 1e9
+        out[name] = {"ms": ms, "nvlink_gbs": gbs, "frac_of_900": gbs / 900.0, "frac_of_measured_770": gbs / 770.0}
+    return out
+
+
+def run_sweep(args, rank, world, device, group, timed, _C):
+    """Config 4 (Zipf routing, multiplier 1.0) and the config-5 grid (tokens per rank x minibatch) at EP = world, BF16
+    and MXFP8: ms per step, tokens/s/GPU, TFLOP/s/GPU and the NVLink rate of the communication phases.  One JSON
+    line per cell on rank 0 (and in --sweep-out), inputs generated on the device."""
+    from mok import functional as F
+    cells = [("c4", None, None)] + [("c5", T, mb) for T in (4096, 16384, 65536) for mb in (2048, 8192, 16384)]
+    if args.sweep != "all":
+        cells = [c for c in cells if c[0] == args.sweep]
+    lines = []
+    last_T = None
+    for name, T, mb in cells:
+        if last_T is not None and T != last_T:
+            F.clear_workspace_cache()
+            torch.cuda.empty_cache()
+        last_T = T
+        prob = Problem(name, args, rank, world, device, group, tokens=T, minibatch=mb, host_inputs=False)
+        cell = {"sweep": name, "n_gpus": world, "tokens_per_rank": prob.T, "minibatch_size": prob.mb, "hidden": prob.H,
+                "intermediate": prob.I, "experts": prob.E, "topk": prob.K, "macrobatch_size": prob.MB}
+        for label, fn in (("bf16", prob.step), ("mxfp8", prob.step_mx)):
+            if label == "mxfp8" and args.no_mxfp8:
+                continue
+            for _ in range(3):
+                fn()
+            ms = statistics.median(timed(fn, args.steps)[1])
+            cell[label] = {"ms_per_step": ms, "tokens_per_s_per_gpu": prob.T / (ms / 1000.0),
+                           "tflops_per_gpu": prob.flops() / (ms / 1000.0) / 1e12}
+        status = _C.check_status()
+        cell["status"] = status
+        sched, _, _ = prob.step()
+        rows = int(sched.num_tokens.item())
+        ranks_rows = torch.tensor([rows], dtype=torch.int64, device=device)
+        allr = [torch.zeros_like(ranks_rows) for _ in range(world)]
+        dist.all_gather(allr, ranks_rows)
+        cell["padded_rows_per_rank"] = [int(t.item()) for t in allr]
+        if world > 1:
+            comm = comm_alone(prob, sched, timed, _C, rank)
+            # bytes that cross NVLink in one step (forward pull + push, backward pull + push) over the step time
+            step_bytes = 4.0 * comm["remote_rows"] * prob.H * 2
+            comm["in_step_gbs_bf16"] = step_bytes / (cell["bf16"]["ms_per_step"] / 1000.0) / 1e9
+            cell["comm"] = comm
+        prob.q = None
+        del prob, sched
+        torch.cuda.empty_cache()
+        lines.append(cell)
+        if rank == 0:
+            print(json.dumps(cell), flush=True)
+    if rank == 0 and args.sweep_out:
+        with open(args.sweep_out, "a") as f:
+            for cell in lines:
+                f.write(json.dumps(cell) + "\n")
+
+
 def run_parity_leg(rank, world, device):
     """Small multi-rank cases against the CPU oracle on every rank, before anything is timed."""
     from tests.parity_cases import run_parity, summarise
@@ -543,6 +635,9 @@ def main():
     ap.add_argument("--no-share", action="store_true", help="skip the 1-GPU leg that runs one rank's EP=8 share of config 2")
     ap.add_argument("--trace", default="", help="write the launch timeline of one BF16 and one MXFP8 step of rank 0 to this file")
     ap.add_argument("--kernel-only", action="store_true", help="time only the dominant GEMM (profiler captures)")
+    ap.add_argument("--sweep", default="", choices=["", "c4", "c5", "all"],
+                    help="instead of the benchmark line: config 4 and / or the config-5 grid (tokens x minibatch) at EP = --gpus")
+    ap.add_argument("--sweep-out", default="", help="append the sweep's JSON lines to this file")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if not args.kernel_only else args.warmup
 
@@ -580,6 +675,11 @@ def main():
         F.clear_workspace_cache()
         torch.cuda.empty_cache()
 
+    if args.sweep:
+        run_sweep(args, rank, world, device, group, timed, _C)
+        dist.destroy_process_group()
+        return
+
     prob = Problem(args.workload, args, rank, world, device, group)
     T, H, I, E, K, E_l, MB = prob.T, prob.H, prob.I, prob.E, prob.K, prob.E_l, prob.MB
     ws = prob.ws
@@ -589,7 +689,7 @@ def main():
     if args.kernel_only:
         sched = prob.F.build_schedule(ws, prob.cfg, prob.te_d, num_local_experts=E_l)
         torch.cuda.synchronize()
-        kern = time_dominant_kernel(_C, sched, prob.x_d, wrg, wru, T, H, I, K, E_l, MB, args.steps, args.warmup, device)
+        kern = time_dominant_kernel(_C, sched, prob.x_d, wrg, wru, T, H, I, K, E_l, MB, args.steps, args.warmup, device, wrd=wrd)
         if not args.no_mxfp8:
             from mok import ops
             qg, qu = (ops.mxfp8_quantize(w_, True, False) for w_ in (wrg, wru))
@@ -603,7 +703,7 @@ def main():
     for _ in range(args.warmup):
         prob.step()
     torch.cuda.synchronize()
-    assert _C.check_status() == 0, "device status word set during warm-up"
+    assert _C.check_status() == 0, f"device status word set during warm-up: {_C.status_detail()}"
     launches_before = _C.launch_count()
     with ClockSampler(local_rank) as clocks:
         total_ms, per_step = timed(prob.step, args.steps)
@@ -611,7 +711,7 @@ def main():
     clock_summary = clocks.summary()
     ms_per_step = total_ms / args.steps
     fwd_ms, bwd_ms = fwd_bwd_split(prob, prob.step, max(2, args.steps // 4))
-    assert _C.check_status() == 0, "device status word set during the timed region"
+    assert _C.check_status() == 0, f"device status word set during the timed region: {_C.status_detail()}"
 
     sched, _, _ = prob.step()
     real_rows = int((sched.peer_rank >= 0).sum().item())
@@ -629,8 +729,9 @@ def main():
         prob.load_resident()              # the device-resident legs below read the symmetric buffers again
 
     # ---- roofline of the dominant kernel
-    kern = time_dominant_kernel(_C, sched, prob.x_d, wrg, wru, T, H, I, K, E_l, MB, 5, 2, device)
-    model = gate_up_bytes(prob, padded_rows, experts_used)
+    kern = time_dominant_kernel(_C, sched, prob.x_d, wrg, wru, T, H, I, K, E_l, MB, 5, 2, device, wrd=wrd)
+    kern_gu = time_dominant_kernel(_C, sched, prob.x_d, wrg, wru, T, H, I, K, E_l, MB, 5, 2, device)
+    model = fwd_routed_bytes(prob, padded_rows, experts_used)
     traffic, traffic_note = None, None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
@@ -641,31 +742,22 @@ def main():
             traffic = ratio * model["total"]
             traffic_note = (f"algorithmic bytes of this launch x {ratio} = DRAM bytes / algorithmic bytes that ncu measured "
                             "for this kernel on the 'small' workload (profiles/traffic.json); not a capture of this launch")
-    roofline = {"bound": "tensor", "kernel": "grouped_gemm_kernel<MODE_SWIGLU> (routed gate/up + SwiGLU)",
+    roofline = {"bound": "tensor", "kernel": "grouped_gemm_kernel<MODE_FWD> (routed gate/up + SwiGLU + down, one persistent launch)",
                 "achieved": kern["tflops"], "peak": peak_tf, "unit": "TFLOP/s", "frac": kern["tflops"] / peak_tf,
                 "peak_source": f"{peak_kind} cuBLAS bf16 burst", "traffic": traffic, "traffic_source": traffic_note,
                 "algorithmic_bytes": model, "launch_ms": kern["ms"], "flops_per_launch": kern["flops_per_launch"],
                 "rows": real_rows, "padded_rows": padded_rows,
-                "tflops_on_padded_rows": kern["tflops"] * padded_rows / max(real_rows, 1)}
+                "tflops_on_padded_rows": kern["tflops"] * padded_rows / max(real_rows, 1),
+                "gate_up_launch_alone": {"ms": kern_gu["ms"], "tflops": kern_gu["tflops"], "frac": kern_gu["tflops"] / peak_tf,
+                                         "note": "the gate/up + SwiGLU launch (mode 1) on the same rows: last round's dominant kernel"}}
 
     # ---- the communication phases alone: dispatch (row pull) and combine (row push) over all scheduled rows,
     # every rank at once, CUDA events, max over ranks.  Bytes over NVLink = rows whose home is another rank.
     comm = None
     if world > 1:
-        remote = int(((sched.peer_rank >= 0) & (sched.peer_rank != rank)).sum().item())
-        buf = torch.empty(MB, H, dtype=torch.bfloat16, device=device)
-        comm = {"remote_rows": remote, "rows": padded_rows, "nvlink_peak_gbs_per_direction": 900.0, "measured_peer_copy_gbs": 770.0}
-        for name, fn in (
-            ("dispatch", lambda: _C.dispatch_rows(ws.x_buffer_ptrs, sched.peer_rank, sched.peer_token_idx, sched.num_tokens,
-                                                  MB, K, H, buf)),
-            ("combine", lambda: _C.combine_rows(buf, ws.combine_buffer_ptrs, sched.peer_rank, sched.peer_token_idx,
-                                                sched.num_tokens, MB, H)),
-        ):
-            fn()
-            ms = timed(fn, 5)[0] / 5
-            gbs = remote * H * 2 / (ms / 1000.0) / 1e9
-            comm[name] = {"ms": ms, "nvlink_gbs": gbs, "frac_of_900": gbs / 900.0, "frac_of_measured_770": gbs / 770.0}
-        del buf
+        comm = {"rows": padded_rows, "nvlink_peak_gbs_per_direction": 900.0, "measured_peer_copy_gbs": 770.0,
+                **comm_alone(prob, sched, timed, _C, rank)}
+        comm["in_step_gbs_bf16"] = 4.0 * comm["remote_rows"] * H * 2 / (ms_per_step / 1000.0) / 1e9
 
     # ---- the same step with the routed experts in MXFP8 (weights pre-quantised outside the step, as the reference does)
     mx = None
@@ -705,7 +797,7 @@ def main():
             m_ms = timed(sp.step_mx, max(5, args.steps // 2))[1]
             share["mxfp8_ms_per_step"] = statistics.median(m_ms)
             share["mxfp8_tflops_per_gpu"] = sp.flops() / (statistics.median(m_ms) / 1000.0) / 1e12
-        assert _C.check_status() == 0, "device status word set during the EP=8-share leg"
+        assert _C.check_status() == 0, f"device status word set during the EP=8-share leg: {_C.status_detail()}"
         del sp
         torch.cuda.empty_cache()
 
@@ -779,27 +871,33 @@ def run_e2e(prob, timed, steps, _C):
         e2e_step()
     e2e_ms = timed(e2e_step, steps)[0] / steps
     h2d = sum(t.numel() * t.element_size() for t in (x_h, te_h, rw_h, gy_h))
-    assert _C.check_status() == 0, "device status word set during the end-to-end steps"
+    assert _C.check_status() == 0, f"device status word set during the end-to-end steps: {_C.status_detail()}"
 
-    # the same with an input prefetcher: step i+1's inputs cross PCIe on a copy stream into a second set of device
-    # tensors while step i computes (one host->device copy of all four inputs per step, as above; functional then
-    # stages them into the symmetric buffers with device copies).  Reported beside the serial number, not instead of it.
+    # the same with double-buffered inputs: two workspaces used alternately; step i+1's four inputs cross PCIe on a copy
+    # stream straight into the other workspace's symmetric buffers while step i computes (one host->device copy of all
+    # four inputs and one device->host read of the checksums per step, as above; no device-side staging copy)
+    F = prob.F
+    ws2 = F.create_workspace(prob.cfg, prob.group, device=device, num_local_tokens=prob.T, hidden_size=prob.H, topk=prob.K)
+    spaces = [ws, ws2]
+    te_slots = [te_e, torch.empty_like(te_e)]
     copy_stream = torch.cuda.Stream(device=device)
-    stage = [tuple(torch.empty_like(t, device=device) for t in (x_h, te_h, rw_h, gy_h)) for _ in range(2)]
     ready = [torch.cuda.Event(), torch.cuda.Event()]
     pipe = {"i": 0}
 
     def prefetch(slot):
+        w_ = spaces[slot]
         with torch.cuda.stream(copy_stream):     # the slot's last consumer finished two steps ago (each step ends with a synchronize)
-            for d_, h_ in zip(stage[slot], (x_h, te_h, rw_h, gy_h)):
-                d_.copy_(h_, non_blocking=True)
+            w_.x_buffer.copy_(x_h, non_blocking=True)
+            te_slots[slot].copy_(te_h, non_blocking=True)
+            w_.router_weight_buffer.copy_(rw_h, non_blocking=True)
+            w_.d_y_buffer.copy_(gy_h, non_blocking=True)
             ready[slot].record(copy_stream)
 
     def e2e_prefetch_step():
         slot = pipe["i"] & 1
         torch.cuda.current_stream().wait_event(ready[slot])
-        x_s, te_s, rw_s, gy_s = stage[slot]
-        _, out, grads = prob.step(x_s, te_s, rw_s, gy_s)
+        w_ = spaces[slot]
+        _, out, grads = prob.step(w_.x_buffer, te_slots[slot], w_.router_weight_buffer, w_.d_y_buffer, ws=w_)
         prefetch(slot ^ 1)
         res = torch.stack([out.float().sum(), grads[0].float().sum()])
         res_h.copy_(res, non_blocking=True)
@@ -810,11 +908,15 @@ def run_e2e(prob, timed, steps, _C):
         e2e_prefetch_step()
     e2e_prefetch_ms = timed(e2e_prefetch_step, steps)[0] / steps
     copy_stream.synchronize()
-    assert _C.check_status() == 0, "device status word set during the prefetching end-to-end steps"
-    tokens = prob.T * prob.world
-    return {"value": e2e_ms, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8, "ms_per_step": e2e_ms,
-            "with_input_prefetch": {"value": tokens / (e2e_prefetch_ms / 1000.0), "ms_per_step": e2e_prefetch_ms,
-                                    "note": "next step's host->device copies on a copy stream while this step computes"}}
+    assert _C.check_status() == 0, f"device status word set during the double-buffered end-to-end steps: {_C.status_detail()}"
+    del ws2, spaces
+    return {"value": e2e_prefetch_ms, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8,
+            "ms_per_step": e2e_prefetch_ms,
+            "how": "mok.functional build_schedule + forward + backward; every step's four inputs are copied from pinned host memory "
+                   "(double-buffered: step i+1's copies run on a copy stream into a second workspace while step i computes) "
+                   "and two checksums are read back to the host",
+            "serial": {"value": prob.T * prob.world / (e2e_ms / 1000.0), "ms_per_step": e2e_ms,
+                       "note": "the same with the copies on the compute stream before each step"}}
 
 
 def run_mxfp8_leg(prob, timed, args, _C, ops, sched, real_rows, peak_tf, trace_lines, in_step, rank, device):
@@ -825,7 +927,7 @@ def run_mxfp8_leg(prob, timed, args, _C, ops, sched, real_rows, peak_tf, trace_l
     total, per_step = timed(prob.step_mx, args.steps)
     mx_ms = total / args.steps
     mx_f, mx_b = fwd_bwd_split(prob, prob.step_mx, 2)
-    assert _C.check_status() == 0, "device status word set during the MXFP8 steps"
+    assert _C.check_status() == 0, f"device status word set during the MXFP8 steps: {_C.status_detail()}"
     rec = traced_step(_C, prob.step_mx)
     trace_lines += [("mxfp8",) + r for r in rec]
     in_step["mxfp8"] = in_step_summary(rec, "gemm_mxfp8", prob, real_rows, peak_tf)
@@ -852,19 +954,27 @@ def run_mxfp8_leg(prob, timed, args, _C, ops, sched, real_rows, peak_tf, trace_l
     return mx
 
 
-def time_dominant_kernel(_C, sched, x, wrg, wru, T, H, I, K, E_l, MB, steps, warmup, device):
-    """Times the routed gate/up + SwiGLU grouped GEMM alone, on this step's real schedule."""
+def time_dominant_kernel(_C, sched, x, wrg, wru, T, H, I, K, E_l, MB, steps, warmup, device, wrd=None):
+    """Times the routed forward GEMM alone, on this step's real schedule: the one persistent launch that computes
+    gate/up + SwiGLU and the down projection of every window (mode 4; what the layer runs).  Without `wrd`: the
+    gate/up + SwiGLU launch (mode 1) only."""
     tpe = sched.tokens_per_expert
-    offs = torch.cat([torch.zeros(1, dtype=torch.int64, device=device), tpe.to(torch.int64).cumsum(0)])
     gob = torch.repeat_interleave(torch.arange(E_l, device=device, dtype=torch.int32), (tpe // 128).to(torch.int64))
     gob = torch.cat([gob, torch.full((MB // 128 - gob.numel(),), -1, dtype=torch.int32, device=device)])
     # the rows' values do not matter for the timing: local tokens repeated, not a peer gather
     x_routed = x.repeat((MB + T - 1) // T, 1)[:MB].contiguous()
     gate, up, hid = (torch.empty(MB, I, dtype=torch.bfloat16, device=device) for _ in range(3))
+    y = torch.empty(MB, H, dtype=torch.bfloat16, device=device) if wrd is not None else None
+    blk = torch.zeros(MB // 256, dtype=torch.int32, device=device)
 
     def launch():
-        _C.grouped_gemm(1, x_routed, wrg, gate, rows=MB, num_rows=sched.num_tokens, group_of_block=gob, G=E_l, N=I, K=H,
-                        B2=wru, D2=up, D3=hid)
+        if wrd is None:
+            _C.grouped_gemm(1, x_routed, wrg, gate, rows=MB, num_rows=sched.num_tokens, group_of_block=gob, G=E_l, N=I, K=H,
+                            B2=wru, D2=up, D3=hid)
+        else:
+            blk.zero_()
+            _C.grouped_gemm(4, x_routed, wrg, gate, rows=MB, num_rows=sched.num_tokens, group_of_block=gob, G=E_l, N=I, K=H,
+                            B2=wru, D2=up, D3=hid, B3=wrd, D4=y, N2=H, window_rows=8192, blk_done=blk)
     for _ in range(warmup):
         launch()
     torch.cuda.synchronize()
@@ -876,7 +986,7 @@ def time_dominant_kernel(_C, sched, x, wrg, wru, T, H, I, K, E_l, MB, steps, war
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps
     real_rows = int((sched.peer_rank >= 0).sum().item())
-    flops = 4.0 * real_rows * H * I              # 2 GEMMs x 2 * rows * H * I, padding rows not counted
+    flops = (4.0 if wrd is None else 6.0) * real_rows * H * I      # 2 (+1) GEMMs x 2 * rows * H * I, padding rows not counted
     padded = int(sched.num_tokens.item())
     return {"ms": ms, "flops_per_launch": flops, "tflops": flops / (ms / 1000.0) / 1e12,
             "rows": real_rows, "padded_rows": padded}

@@ -349,6 +349,9 @@ typedef struct {
     const int32_t* push_idx;
     const float* push_values;
     const uint64_t* push_value_ptrs_host;
+    /* mode 3, optional, device [G]: rows of group g from group_k_end[g] on (up to off[g+1]) are zero in A and B -- the
+     * padding at the end of an expert's segment -- and are left out of the contraction, in steps of 64 rows */
+    const int32_t* group_k_end;
 } mokb_gemm_args;
 int mokb_grouped_gemm_bf16(const mokb_gemm_args* args, void* stream);
 
@@ -367,7 +370,11 @@ int mokb_grouped_gemm_bf16(const mokb_gemm_args* args, void* stream);
  *           epilogue, hidden = SwiGLU(gate, up) (clamped if has_swiglu_limit), and the kernel writes gate_q, up_q,
  *           hid_q [rows, N] E4M3 with scales along columns and hid_qt [N, t_rows] with scales along tokens: what
  *           mode 1 followed by the reference's SwiGLU + quantise pass produces (grouped_gemm.cuh:295-359,
- *           swiglu.cuh:38-207).  D and D2 are not used. */
+ *           swiglu.cuh:38-207).  D and D2 are not used.
+ *   mode 4: mode 3 followed by the down projection of the same rows, D [rows, N2] = hidden * B3[g]^T with B3 [G, N2, N]
+ *           quantised along N, in ONE persistent launch, window by window -- mode 4 of mokb_grouped_gemm_bf16 in MXFP8,
+ *           with the same counters (blk_done counts 16 arrivals per gate/up tile, win_done 16 per down tile) and the
+ *           same push of the result rows to peers (modes 0 and 4; ldd is then the peers' leading dimension). */
 typedef struct {
     int mode;
     int rows_static, row_begin, row_end;     /* as in mokb_gemm_args; multiples of 256 */
@@ -383,6 +390,20 @@ typedef struct {
     int t_rows, has_swiglu_limit;
     float swiglu_limit;
     int32_t* status;
+    /* mode 4, the counters and the push: as the fields of the same names in mokb_gemm_args */
+    const void *B3, *B3_sc;
+    int N2;
+    int window_rows;
+    const int32_t* win_ready;
+    int win_ready_target;
+    int32_t* blk_done;
+    int32_t* win_done;
+    const uint64_t* push_ptrs_host;
+    int push_ep_size;
+    const int32_t* push_rank;
+    const int32_t* push_idx;
+    const float* push_values;
+    const uint64_t* push_value_ptrs_host;
 } mokb_gemm_fp8_args;
 int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* args, void* stream);
 

@@ -8,6 +8,7 @@
 //                        (reference: dispatch_combine.cuh:152-266)
 // With ep_size == 1 the same kernels run against the local pointers.
 #include "common.cuh"
+#include "mxfp8_codec.cuh"
 
 namespace mokb {
 namespace {
@@ -86,12 +87,22 @@ __global__ void barrier_kernel(PeerPtrs peers, int R, int rank, int32_t* target,
     }
 }
 
-// One warp per schedule row, 16- or 32-byte accesses, four loads in flight per lane.
-template <bool SCALE, int W>
+// Row-wise MXFP8 form of the rows a dispatch pulls (QUANT variants): E4M3 bytes [rows, H] and packed scales.
+struct RowQuant {
+    uint8_t* q;
+    uint8_t* sc;
+    int col_tiles;          // H / 128
+};
+
+// One warp per schedule row, 16- or 32-byte accesses, four loads in flight per lane.  QUANT (32-byte accesses only):
+// the row is also quantised along its columns from the registers it passes through -- a lane holds 16 consecutive
+// values, two neighbouring lanes one 32-value block (the reference quantises the tile it has just pulled,
+// csrc/megakernel/dispatch_combine.cuh:88-114; the values are those of quantize_kernel, byte for byte).
+template <bool SCALE, int W, bool QUANT>
 __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t* __restrict__ peer_rank,
                                 const int32_t* __restrict__ peer_token_idx, const int32_t* __restrict__ num_rows,
                                 int max_rows, int row_begin, int row_end, int R, int row_divisor, int vec_per_row,
-                                Words<W>* __restrict__ dst, float* __restrict__ row_scale_out, int32_t* done_counter) {
+                                Words<W>* __restrict__ dst, float* __restrict__ row_scale_out, int32_t* done_counter, RowQuant rq) {
     int rows = num_rows ? *num_rows : max_rows;
     rows = rows < 0 ? 0 : (rows > max_rows ? 0 : rows);
     rows = min(rows, row_end);
@@ -108,6 +119,14 @@ __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t*
             for (int k = 0; k < W; ++k) zero.w[k] = 0u;
             for (int v = lane; v < vec_per_row; v += 32) st_words<W>(out + v, zero);
             if (SCALE && lane == 0 && row_scale_out) row_scale_out[row] = 0.f;
+            if (QUANT) {          // a zero row: zero bytes and the scale of an all-zero block
+                float inv;
+                const uint8_t zb = static_cast<uint8_t>(scale_byte(0.f, &inv));
+                for (int v = lane; v < vec_per_row; v += 32) {
+                    asm volatile("st.global.v4.u32 [%0], {%1, %1, %1, %1};" ::"l"(rq.q + static_cast<size_t>(row) * vec_per_row * 16 + v * 16), "r"(0u) : "memory");
+                    if ((v & 1) == 0) rq.sc[scale_offset(row, v >> 1, rq.col_tiles)] = zb;
+                }
+            }
             continue;
         }
         const int tok = peer_token_idx[row];
@@ -117,22 +136,48 @@ __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t*
             w = static_cast<const float*>(scale_src.p[pr])[tok];
             if (lane == 0 && row_scale_out) row_scale_out[row] = w;
         }
-        for (int v0 = lane; v0 < vec_per_row; v0 += 128) {
+        // (every lane makes the same number of trips: the quantising variant shuffles between lanes inside)
+        for (int vb = 0; vb < vec_per_row; vb += 128) {
+            const int v0 = vb + lane;
             Words<W> r[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u)
                 if (v0 + 32 * u < vec_per_row) r[u] = ld_words<W>(in + v0 + 32 * u);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                if (v0 + 32 * u >= vec_per_row) continue;
-                if (SCALE) {
+                const bool live = v0 + 32 * u < vec_per_row;
+                if (live) {
+                    if (SCALE) {
 #pragma unroll
-                    for (int k = 0; k < W; ++k) {
-                        const float2 f = unpack_bf16(r[u].w[k]);
-                        r[u].w[k] = pack_bf16(f.x * w, f.y * w);
+                        for (int k = 0; k < W; ++k) {
+                            const float2 f = unpack_bf16(r[u].w[k]);
+                            r[u].w[k] = pack_bf16(f.x * w, f.y * w);
+                        }
+                    }
+                    st_words<W>(out + v0 + 32 * u, r[u]);
+                }
+                if (QUANT) {      // lanes 2j and 2j+1 hold one 32-value block (W = 8: 16 values per lane); whole warp
+                    uint32_t m = 0u;
+                    if (live) {
+#pragma unroll
+                        for (int k = 0; k < W; ++k) m = absmax2(m, r[u].w[k]);
+                    }
+                    float amax = fmaxf(bf16_lo(m), bf16_hi(m));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                    if (live) {
+                        float inv;
+                        const uint32_t byte = scale_byte(amax, &inv);
+                        const int v = v0 + 32 * u;
+                        uint32_t o[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            o[k] = e4m3x4(bf16_lo(r[u].w[2 * k]) * inv, bf16_hi(r[u].w[2 * k]) * inv,
+                                          bf16_lo(r[u].w[2 * k + 1]) * inv, bf16_hi(r[u].w[2 * k + 1]) * inv);
+                        asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(rq.q + static_cast<size_t>(row) * vec_per_row * 16 + v * 16),
+                                     "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                        if ((lane & 1) == 0) rq.sc[scale_offset(row, v >> 1, rq.col_tiles)] = static_cast<uint8_t>(byte);
                     }
                 }
-                st_words<W>(out + v0 + 32 * u, r[u]);
             }
         }
     }
@@ -259,13 +304,14 @@ extern "C" int mokb_barrier_all(const uint64_t* barrier_ptrs_host, int ep_size, 
 
 namespace mokb {
 
-int comm_default_blocks() { return sm_count() * 8; }
+int comm_default_blocks() { return sm_count() * 16; }
 
 int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
                        const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                        int row_divisor, int64_t hidden, void* dst, const uint64_t* row_scale_ptrs_host,
-                       float* row_scale_out, int blocks, cudaStream_t s, int32_t* done_counter) {
+                       float* row_scale_out, int blocks, cudaStream_t s, int32_t* done_counter, void* q_out, void* q_sc_out) {
     TraceScope trace(s, row_scale_ptrs_host ? "dispatch_scaled" : "dispatch", row_begin);
+    MOKB_REQUIRE((q_out == nullptr) == (q_sc_out == nullptr), "dispatch_rows: the quantised rows and their scales go together");
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "dispatch_rows: bad ep_size");
     MOKB_REQUIRE(peer_rank && peer_token_idx && dst, "dispatch_rows: null pointer");
     MOKB_REQUIRE(max_rows >= 0 && row_divisor >= 1 && hidden > 0 && hidden % 8 == 0, "dispatch_rows: bad sizes");
@@ -275,32 +321,37 @@ int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t
     MOKB_TRY(fill_peers(&src, src_ptrs_host, ep_size, "src_ptrs"));
     for (int r = 0; r < kPeerMax; ++r) scale.p[r] = nullptr;
     if (max_rows == 0 || row_begin >= max_rows) return MOKB_OK;
-    const int threads = 256;
+    // 128 threads: one warp per SM quarter, so that a block finds room beside a GEMM CTA whatever that kernel's warp count
+    const int threads = 128;
     if (blocks <= 0) blocks = comm_default_blocks();
     const bool wide = rows_aligned32(dst, src, ep_size, hidden);
     const int vec = static_cast<int>(hidden / (wide ? 16 : 8));
-    share_sms_with_gemm(dispatch_kernel<true, 8>);
-    share_sms_with_gemm(dispatch_kernel<true, 4>);
-    share_sms_with_gemm(dispatch_kernel<false, 8>);
-    share_sms_with_gemm(dispatch_kernel<false, 4>);
-    if (row_scale_ptrs_host) {
-        for (int r = 0; r < ep_size; ++r) {
-            MOKB_REQUIRE(row_scale_ptrs_host[r] != 0, "dispatch_rows: null scale pointer for rank %d", r);
-            scale.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(row_scale_ptrs_host[r]));
-        }
-        if (wide)
-            dispatch_kernel<true, 8><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
-                                                                row_end, ep_size, row_divisor, vec, static_cast<Words<8>*>(dst), row_scale_out, done_counter);
-        else
-            dispatch_kernel<true, 4><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
-                                                                row_end, ep_size, row_divisor, vec, static_cast<Words<4>*>(dst), row_scale_out, done_counter);
-    } else if (wide) {
-        dispatch_kernel<false, 8><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
-                                                             row_end, ep_size, row_divisor, vec, static_cast<Words<8>*>(dst), nullptr, done_counter);
-    } else {
-        dispatch_kernel<false, 4><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows, row_begin,
-                                                             row_end, ep_size, row_divisor, vec, static_cast<Words<4>*>(dst), nullptr, done_counter);
+    for (int r = 0; r < ep_size && row_scale_ptrs_host; ++r) {
+        MOKB_REQUIRE(row_scale_ptrs_host[r] != 0, "dispatch_rows: null scale pointer for rank %d", r);
+        scale.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(row_scale_ptrs_host[r]));
     }
+    const RowQuant rq{static_cast<uint8_t*>(q_out), static_cast<uint8_t*>(q_sc_out), static_cast<int>(hidden / 128)};
+    if (q_out) {
+        MOKB_REQUIRE(wide && hidden % 128 == 0 && (reinterpret_cast<uintptr_t>(q_out) & 15) == 0,
+                     "dispatch_rows: quantised output needs 32-byte aligned rows, hidden %% 128 == 0 and a 16-byte aligned buffer");
+    }
+#define MOKB_DISPATCH(SC, WW, QQ)                                                                                              \
+    do {                                                                                                                       \
+        share_sms_with_gemm(dispatch_kernel<SC, WW, QQ>);                                                                      \
+        dispatch_kernel<SC, WW, QQ><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows,      \
+            row_begin, row_end, ep_size, row_divisor, vec, static_cast<Words<WW>*>(dst), SC ? row_scale_out : nullptr,         \
+            done_counter, rq);                                                                                                 \
+    } while (0)
+    if (row_scale_ptrs_host) {
+        if (q_out) MOKB_DISPATCH(true, 8, true);
+        else if (wide) MOKB_DISPATCH(true, 8, false);
+        else MOKB_DISPATCH(true, 4, false);
+    } else {
+        if (q_out) MOKB_DISPATCH(false, 8, true);
+        else if (wide) MOKB_DISPATCH(false, 8, false);
+        else MOKB_DISPATCH(false, 4, false);
+    }
+#undef MOKB_DISPATCH
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     return MOKB_OK;
@@ -331,11 +382,11 @@ int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
     share_sms_with_gemm(combine_kernel<8>);
     share_sms_with_gemm(combine_kernel<4>);
     if (rows_aligned32(src, dst, ep_size, hidden))
-        combine_kernel<8><<<blocks, 256, 0, s>>>(static_cast<const Words<8>*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
+        combine_kernel<8><<<blocks, 128, 0, s>>>(static_cast<const Words<8>*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
                                                  row_begin, row_end, ep_size, static_cast<int>(hidden / 16), row_values, wait_counter,
                                                  arrivals_per_row_block, status);
     else
-        combine_kernel<4><<<blocks, 256, 0, s>>>(static_cast<const Words<4>*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
+        combine_kernel<4><<<blocks, 128, 0, s>>>(static_cast<const Words<4>*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
                                                  row_begin, row_end, ep_size, static_cast<int>(hidden / 8), row_values, wait_counter,
                                                  arrivals_per_row_block, status);
     MOKB_CUDA(cudaGetLastError());
@@ -350,7 +401,7 @@ extern "C" int mokb_dispatch_rows(const uint64_t* src_ptrs_host, int ep_size, co
                                   int row_divisor, int64_t hidden, void* dst,
                                   const uint64_t* row_scale_ptrs_host, float* row_scale_out, void* stream) {
     return dispatch_rows_impl(src_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, 0, max_rows, row_divisor,
-                              hidden, dst, row_scale_ptrs_host, row_scale_out, 0, static_cast<cudaStream_t>(stream), nullptr);
+                              hidden, dst, row_scale_ptrs_host, row_scale_out, 0, static_cast<cudaStream_t>(stream), nullptr, nullptr, nullptr);
 }
 
 extern "C" int mokb_comm_default_blocks(void) { return comm_default_blocks(); }
@@ -361,7 +412,8 @@ extern "C" int mokb_dispatch_rows_window(const uint64_t* src_ptrs_host, int ep_s
                                          const uint64_t* row_scale_ptrs_host, float* row_scale_out, int blocks,
                                          int32_t* done_counter, void* stream) {
     return dispatch_rows_impl(src_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, row_divisor,
-                              hidden, dst, row_scale_ptrs_host, row_scale_out, blocks, static_cast<cudaStream_t>(stream), done_counter);
+                              hidden, dst, row_scale_ptrs_host, row_scale_out, blocks, static_cast<cudaStream_t>(stream), done_counter,
+                              nullptr, nullptr);
 }
 
 extern "C" int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_size,

@@ -62,15 +62,18 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t in
                  uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
 
 // Row-window forms of dispatch / combine used by the layer to overlap them with the GEMMs:
-// rows [row_begin, min(row_end, *num_rows)) only, on `blocks` CTAs of 256 threads (0 = default).
+// rows [row_begin, min(row_end, *num_rows)) only, on `blocks` CTAs of 128 threads (0 = default).
 // `done_counter`: every block adds 1 (release) once its rows of the window have landed, so a GEMM that is already
 // running can start on them.  `wait_counter`: the rows are still being written by a running GEMM; the kernel first
 // waits (bounded) for ((rows of the window) / 256) * arrivals_per_row_block arrivals.
+// `q_out` / `q_sc_out` (dispatch; 32-byte aligned rows, hidden % 128 == 0): the pulled (and scaled) rows also as E4M3
+// [rows, hidden] with packed scales, quantised along the columns, addressed by schedule row like `dst`.
 int comm_default_blocks();
 int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
                        const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                        int row_divisor, int64_t hidden, void* dst, const uint64_t* row_scale_ptrs_host,
-                       float* row_scale_out, int blocks, cudaStream_t s, int32_t* done_counter = nullptr);
+                       float* row_scale_out, int blocks, cudaStream_t s, int32_t* done_counter = nullptr,
+                       void* q_out = nullptr, void* q_sc_out = nullptr);
 int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_size, const int32_t* peer_rank,
                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                       int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s,
@@ -81,8 +84,11 @@ int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
 // rows [first, first + M) is passed with every pointer moved back by `first` rows (transposed tensors: by `first`
 // bytes, scale tensors: by first / 128 tiles along the row axis), and M / rows_cap stays the buffer's own row count,
 // which is also the row stride of the transposed outputs.
+// On `blocks` CTAs (0 = as many as there are tiles, up to 16 per SM); `done_counter`: every block of the launch adds 1
+// (release) when it is through, so the window is quantised when the counter has grown by `blocks`.
 int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int32_t* num_rows, int row_begin, int row_end,
-                  void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, cudaStream_t stream);
+                  void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, cudaStream_t stream, int blocks = 0,
+                  int32_t* done_counter = nullptr);
 int swiglu_bwd_quant_impl(const void* gate_q, const void* gate_sc, const void* up_q, const void* up_sc, const void* d_hidden,
                           int64_t rows_cap, int64_t I, const int32_t* num_rows, int row_begin, int row_end, int has_limit, float limit,
                           const float* row_scale, void* dg_q, void* dg_sc, void* dg_qt, void* dg_sct,
@@ -353,6 +359,16 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, tied to the registers of a load that was left in flight across other work: nothing that reads
+// them can be scheduled above it.
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
+}
 
 // Shared-memory matrix descriptor (tcgen05), 128-byte swizzle.
 //   K-major operand : rows at 128 B pitch, 8-row groups 1024 B apart (SBO); LBO unused.

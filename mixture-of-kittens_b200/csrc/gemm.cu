@@ -62,7 +62,8 @@ struct Geo {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;    // 48 KB / 32 KB
     static constexpr int STAGES = NCTA == 2 ? 6 : 4;
     static constexpr int GROUP_M = GROUP_ROWS / TILE_M;
-    static constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    // + one 4 KB transposition buffer per epilogue warp (32 rows x 128 bytes)
+    static constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 4 * 4096;
 };
 
 struct KParams {
@@ -71,6 +72,7 @@ struct KParams {
     const int32_t* num_rows;         // device, optional
     const int32_t* group_of_block;   // device [rows/128], optional
     const int32_t* group_offsets;    // device [G+1], MODE_WGRAD
+    const int32_t* group_k_end;      // device [G], MODE_WGRAD, optional: rows of group g from here on are zero in both operands
     int G, M, N, K;
     int b_rows_per_group;            // rows of the flattened weight tensor per group
     int dual;                        // MODE_NN: second (A2, B2) pair accumulates into the same tile
@@ -98,6 +100,8 @@ struct KParams {
     const int32_t* push_idx;
     const float* push_values;        // optional: push_val[rank][idx] = push_values[r], written with the first column tile
     int32_t* status;
+    int debug;
+    int line_stores;                 // the epilogue transposes through shared memory and stores whole 128-byte lines
     PeerPtrs push_dst, push_val;
 };
 
@@ -149,7 +153,9 @@ struct Sched {
             ti.n_blk = rem / m_blocks;
             ti.m_blk = rem - ti.n_blk * m_blocks;
             ti.k_row0 = p.group_offsets[ti.group];
-            ti.k_iters = (p.group_offsets[ti.group + 1] - ti.k_row0) / BK;
+            int k_end = p.group_offsets[ti.group + 1];
+            if (p.group_k_end) k_end = min(k_end, max(p.group_k_end[ti.group], ti.k_row0));
+            ti.k_iters = (k_end - ti.k_row0 + BK - 1) / BK;      // a partial last stage reads rows that are zero
         } else if (MODE == MODE_FWD) {
             // window by window: all gate/up tiles of the window's rows, then all their down tiles; inside a phase,
             // super-groups of 1024 rows x every column tile
@@ -220,8 +226,11 @@ __device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* t, uin
     else tma_load_2d(dst, t, bar, c0, c1);
 }
 
+// 128 registers per thread at most: registers are handed out per SM quarter (16 K each), a CTA's six warps put two
+// on a quarter, and the dispatch / quantise blocks that run beside the GEMM (eight warps of 56 registers, two per
+// quarter) must still fit there -- a GEMM that waits for their rows on an SM they cannot enter would wait for ever.
 template <int MODE, int NCTA>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __maxnreg__(128)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                     const __grid_constant__ CUtensorMap tmB3, const KParams p) {
@@ -297,8 +306,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             bool ok = true;
             const int kh = p.K / BK;
             int waited_window = -1;
+            // the next tile's coordinates (integer divisions, loads of the group tables) are worked out while this
+            // tile's stages are in flight: with a short contraction the look-up would otherwise stall every tile
+            Tile next_ti = {};
+            if (tile_id0 < sched.total) next_ti = sched.get(p, tile_id0);
             for (int t = tile_id0; ok && t < sched.total; t += tile_stride) {
-                const Tile ti = sched.get(p, t);
+                const Tile ti = next_ti;
+                if (t + tile_stride < sched.total) next_ti = sched.get(p, t + tile_stride);
                 const int row0 = ti.m_blk * G::TILE_M + static_cast<int>(cta) * 128;    // this CTA's rows of A / D
                 if (MODE != MODE_WGRAD) {
                     // rows that another kernel (or, for a down tile, other CTAs of this one) is still producing
@@ -308,11 +322,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         waited_window = ti.window;
                         fenced = true;
                     }
-                    if (MODE == MODE_FWD && ti.phase == 1) {
+                    if (MODE == MODE_FWD && ti.phase == 1 && !(p.debug & 2)) {
                         if (!flag_wait(p.blk_done + (ti.m_blk - sched.m_first), sched.n_gu * 4 * NCTA, abort_flag, p.status, kWaitBlockDone, ti.m_blk - sched.m_first)) { ok = false; break; }
                         fenced = true;
                     }
-                    if (fenced) fence_proxy_async_global();
+                    if (fenced && !(p.debug & 1)) fence_proxy_async_global();
                 }
                 for (int it = 0; it < ti.k_iters; ++it) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
@@ -372,8 +386,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t ph = 0;
             bool ok = true;
             int local = 0;
+            Tile next_ti = {};
+            if (tile_id0 < sched.total) next_ti = sched.get(p, tile_id0);
             for (int t = tile_id0; ok && t < sched.total; t += tile_stride, ++local) {
-                const Tile ti = sched.get(p, t);
+                const Tile ti = next_ti;
+                if (t + tile_stride < sched.total) next_ti = sched.get(p, t + tile_stride);
                 const int acc = local & 1;
                 const uint32_t acc_ph = (local >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
@@ -469,18 +486,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                 }
                 const int cols_left = (MODE == MODE_FWD ? p.N2 : p.N) - ti.n_blk * BN;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    if (c * 32 >= cols_left) break;
-                    uint32_t r[32];
-                    if (empty_k) {
-                        if (MODE == MODE_WGRAD && p.accumulate) break;      // nothing to add: leave the stored gradient
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = 0u;
-                    } else {
-                        tmem_ld_32x32(t_addr + c * 32, r);     // whole warp, also for rows that are not stored
-                        tmem_ld_wait();
-                    }
+                const int nchunks = min(BN / 32, (cols_left + 31) / 32);
+                // one 32-column chunk from registers: (optionally add the stored gradient,) round to bf16, store locally
+                // and / or at home
+                auto put = [&](uint32_t (&r)[32], int c) {
                     if (MODE == MODE_WGRAD && p.accumulate && row_ok) {
                         const uint4* old = reinterpret_cast<const uint4*>(dst + c * 32);
 #pragma unroll
@@ -497,6 +506,81 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                     if (row_ok) store_row32(dst + c * 32, r, p.wide_stores);
                     if (pdst) store_row32(pdst + c * 32, r, p.push_wide);
+                };
+                if (empty_k) {
+                    if (!(MODE == MODE_WGRAD && p.accumulate)) {      // accumulate: nothing to add, leave the stored gradient
+                        uint32_t z[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) z[i] = 0u;
+#pragma unroll 1
+                        for (int c = 0; c < nchunks; ++c) put(z, c);
+                    }
+                } else if ((MODE == MODE_WGRAD && p.accumulate) || (nchunks & 1) || !p.line_stores) {
+                    // register path: a lane stores its own row, 32 bytes at a time.  Two register sets: the tensor-memory
+                    // load of the next chunk is in flight while this one is stored (whole warp, also for unstored rows)
+                    uint32_t ra[32], rb[32];
+                    tmem_ld_32x32(t_addr, ra);
+                    tmem_ld_wait_for(ra);
+#pragma unroll 1
+                    for (int c = 0; c < nchunks; c += 2) {
+                        const bool has_b = c + 1 < nchunks, has_next = c + 2 < nchunks;
+                        if (has_b) tmem_ld_32x32(t_addr + (c + 1) * 32, rb);
+                        put(ra, c);
+                        if (has_b) {
+                            tmem_ld_wait_for(rb);
+                            if (has_next) tmem_ld_32x32(t_addr + (c + 2) * 32, ra);
+                            put(rb, c + 1);
+                            if (has_next) tmem_ld_wait_for(ra);
+                        }
+                    }
+                } else {
+                    // line path: 64 columns (128 bytes) of the warp's 32 rows are transposed through shared memory, so
+                    // that eight lanes store one whole 128-byte line of a row and a store instruction touches 4 lines
+                    // instead of 32 sectors of 32 different lines -- what the L2 and, for rows that go to a peer, the
+                    // NVLink packets are made for.
+                    const uint32_t stage = bars + 256u + static_cast<uint32_t>(warp - 2) * 4096u;
+                    const int sub = lane >> 3, unit = lane & 7;
+                    // lane 0's row of the local output (rows of a warp are consecutive) and this lane's own row at home
+                    __nv_bfloat16* const warp_dst = base ? dst - static_cast<size_t>(lane) * ld_out : nullptr;
+                    const int warp_row0 = tile_row - lane;
+                    const unsigned long long own_home = reinterpret_cast<unsigned long long>(pdst);
+                    const int npairs = nchunks >> 1;
+#pragma unroll 1
+                    for (int cp = 0; cp < npairs; ++cp) {
+                        uint32_t w[32];           // this lane's row, 64 columns as bf16 pairs
+                        {
+                            uint32_t ra[32], rb[32];
+                            tmem_ld_32x32(t_addr + (2 * cp) * 32, ra);
+                            tmem_ld_32x32(t_addr + (2 * cp + 1) * 32, rb);
+                            tmem_ld_wait_for(ra);
+                            tmem_ld_wait_for(rb);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                w[i] = pack_bf16(__uint_as_float(ra[2 * i]), __uint_as_float(ra[2 * i + 1]));
+                                w[16 + i] = pack_bf16(__uint_as_float(rb[2 * i]), __uint_as_float(rb[2 * i + 1]));
+                            }
+                        }
+                        __syncwarp();             // the previous pair has been read out of the buffer
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)      // row `lane`, 16-byte unit u at position u ^ (lane & 7): conflict-free both ways
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 128u + static_cast<uint32_t>((u ^ (lane & 7)) << 4)),
+                                         "r"(w[4 * u]), "r"(w[4 * u + 1]), "r"(w[4 * u + 2]), "r"(w[4 * u + 3]) : "memory");
+                        __syncwarp();
+                        const int col = cp * 64 + unit * 8;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = 4 * i + sub;
+                            uint32_t v0, v1, v2, v3;
+                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                                         : "r"(stage + rr * 128u + static_cast<uint32_t>((unit ^ (rr & 7)) << 4)) : "memory");
+                            if (warp_dst && (MODE != MODE_WGRAD || warp_row0 + rr < p.M))
+                                st_global_v4(warp_dst + static_cast<size_t>(rr) * ld_out + col, v0, v1, v2, v3);
+                            if ((MODE == MODE_NT || MODE == MODE_NN || MODE == MODE_FWD) && p.push) {
+                                __nv_bfloat16* home = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, own_home, rr));
+                                if (home) st_global_v4(home + col, v0, v1, v2, v3);
+                            }
+                        }
+                    }
                 }
             }
             tc_fence_before();
@@ -533,9 +617,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 template <int MODE, int NCTA>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2, const CUtensorMap& b3,
            const KParams& p, int tiles_upper_bound, cudaStream_t stream) {
-    constexpr size_t smem = Geo<NCTA>::SMEM_BYTES;
-    MOKB_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<MODE, NCTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const size_t smem = Geo<NCTA>::SMEM_BYTES - (p.line_stores ? 0 : 4 * 4096);
+    MOKB_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<MODE, NCTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Geo<NCTA>::SMEM_BYTES));
     int units = sm_count() / NCTA;                       // CTAs, or CTA pairs
+    // a launch that waits for another kernel's rows leaves one pair of SMs to that kernel: whatever else shares the
+    // GPU, the rows it waits for can always be produced
+    if (p.win_ready && units > 2) units -= 2 / NCTA;
     if (tiles_upper_bound < units) units = tiles_upper_bound;
     if (units < 1) return MOKB_OK;
     cudaLaunchConfig_t cfg = {};
@@ -601,6 +688,7 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     p.num_rows = g->num_rows;
     p.group_of_block = g->group_of_block;
     p.group_offsets = g->group_offsets;
+    p.group_k_end = g->mode == MODE_WGRAD ? g->group_k_end : nullptr;
     p.G = g->G; p.M = g->M; p.N = g->N; p.K = g->K;
     p.D = static_cast<__nv_bfloat16*>(g->D);
     p.D2 = static_cast<__nv_bfloat16*>(g->D2);
@@ -613,6 +701,8 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     p.limit = g->swiglu_limit;
     p.status = g->status;
     p.dual = 0;
+    { const char* e = getenv("MOKB_DEBUG"); p.debug = e ? atoi(e) : 0; }
+    { const char* e = getenv("MOKB_LINE_STORES"); p.line_stores = e ? atoi(e) : 1; }
     if (g->push_ptrs_host) {
         MOKB_REQUIRE(g->mode == MODE_NT || g->mode == MODE_NN || g->mode == MODE_FWD, "grouped_gemm: push is for modes 0, 2 and 4");
         MOKB_REQUIRE(g->push_ep_size >= 1 && g->push_ep_size <= MOKB_MAX_EP && g->push_rank && g->push_idx, "grouped_gemm: push needs ranks and indices");

@@ -14,6 +14,10 @@
 //                computes hidden = SwiGLU(gate, up) and writes the MXFP8 forms the layer saves and consumes
 //                (gate, up, hidden quantised along columns; hidden also along tokens) instead of bf16 gate / up
 //                (the reference fuses the same quantisation into its gate/up epilogue, grouped_gemm.cuh:295-359)
+//   FMODE_FWD    FMODE_GATEUP_QUANT tiles and the FMODE_NT (down) tiles of the same rows in ONE persistent launch, window
+//                by window, tied by the global-memory counters described in gemm.cu (the task loop of the reference's
+//                forward megakernel, csrc/megakernel/forward.cuh:146-266); the down tiles read the E4M3 hidden rows
+//                and scales that the gate/up tiles of the same 256-row block have just written
 //
 // A CTA pair (cluster of 2, cta_group::2) computes a 256 x 256 tile; K advances 128 bytes per
 // stage (4 MMAs of K = 32).  Per stage each CTA stages 16 KB of A, 16 KB of B and three
@@ -49,7 +53,7 @@ constexpr int SF_SET_COLS = 16;                    // SFA 4 + SFB 8, padded
 constexpr int GROUP_M = 4;
 constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * (DATA_BYTES + SF_BYTES) + 1024 + 256;
 
-enum { FMODE_NT = 0, FMODE_DUALB = 1, FMODE_WGRAD = 2, FMODE_GATEUP_QUANT = 3 };
+enum { FMODE_NT = 0, FMODE_DUALB = 1, FMODE_WGRAD = 2, FMODE_GATEUP_QUANT = 3, FMODE_FWD = 4 };
 template <int MODE> constexpr bool kGateUp = MODE == FMODE_DUALB || MODE == FMODE_GATEUP_QUANT;
 
 struct FParams {
@@ -71,18 +75,35 @@ struct FParams {
     int t_rows;
     int has_limit;
     float limit;
+    // counters (row-tiled modes; see gemm.cu) and the down projection of FMODE_FWD
+    int window_rows;
+    const int32_t* win_ready;
+    int win_ready_target;
+    int N2, K2, b3_rows_per_group, a2_ktiles, b3_ktiles;     // down: N2 columns, contraction K2 = N
+    int32_t* blk_done;
+    int32_t* win_done;
+    // push (FMODE_NT and the down tiles of FMODE_FWD): row r goes to row push_idx[r] of rank push_rank[r]'s buffer
+    int push, push_ranks, push_wide;
+    const int32_t* push_rank;
+    const int32_t* push_idx;
+    const float* push_values;
     int32_t* status;
+    PeerPtrs push_dst, push_val;
 };
 
 struct Tile {
     int m_blk, n_blk, group, k_iters, k_tile0;
+    int phase, window;               // FMODE_FWD: 0 = gate/up tile, 1 = down tile; window of the rows, from row_begin
 };
 
 template <int MODE>
 struct Sched {
     int m_blocks, n_blocks, total, m_first;
+    int n_gu, n_nt, win_blocks;
     __device__ Sched(const FParams& p) {
         m_first = 0;
+        n_gu = n_nt = 0;
+        win_blocks = 1 << 30;
         if (MODE == FMODE_WGRAD) {
             m_blocks = (p.M + TILE_M - 1) / TILE_M;
             n_blocks = (p.N + BN - 1) / BN;
@@ -97,6 +118,12 @@ struct Sched {
             m_blocks = (hi - lo) / TILE_M;
             n_blocks = kGateUp<MODE> ? p.N / 128 : (p.N + BN - 1) / BN;
             total = m_blocks * n_blocks;
+            if (p.window_rows > 0) win_blocks = p.window_rows / TILE_M;
+            if (MODE == FMODE_FWD) {
+                n_gu = p.N / 128;
+                n_nt = p.N2 / BN;
+                total = m_blocks * (n_gu + n_nt);
+            }
         }
     }
     __device__ Tile get(const FParams& p, int t) const {
@@ -110,6 +137,28 @@ struct Sched {
             const int c0 = p.group_offsets[ti.group];
             ti.k_tile0 = c0 / BKB - p.k_tile_origin;
             ti.k_iters = (p.group_offsets[ti.group + 1] - c0) / BKB;
+        } else if (MODE == FMODE_FWD) {
+            const int wb = min(win_blocks, m_blocks);
+            const int per_win = wb * (n_gu + n_nt);
+            const int n_win = (m_blocks + wb - 1) / wb;
+            const int w = min(t / per_win, n_win - 1);
+            int local = t - w * per_win;
+            const int blk0 = w * wb;
+            const int wc = min(wb, m_blocks - blk0);
+            ti.phase = local >= wc * n_gu ? 1 : 0;
+            if (ti.phase) local -= wc * n_gu;
+            const int nb = ti.phase ? n_nt : n_gu;
+            const int per = GROUP_M * nb;
+            const int sg = local / per;
+            const int first = sg * GROUP_M;
+            const int gsize = min(GROUP_M, wc - first);
+            const int in = local - sg * per;
+            ti.n_blk = in / gsize;
+            ti.m_blk = m_first + blk0 + first + (in - ti.n_blk * gsize);
+            ti.window = w;
+            ti.group = p.group_of_block ? p.group_of_block[ti.m_blk * 2] : 0;
+            ti.k_tile0 = 0;
+            ti.k_iters = (ti.phase ? p.K2 : p.K) / BKB;
         } else {
             const int per = GROUP_M * n_blocks;
             const int sg = t / per;
@@ -121,6 +170,8 @@ struct Sched {
             ti.group = p.group_of_block ? p.group_of_block[ti.m_blk * 2] : 0;
             ti.k_tile0 = 0;
             ti.k_iters = (p.K / BKB) * (p.dual ? 2 : 1);
+            ti.phase = 0;
+            ti.window = (ti.m_blk - m_first) / win_blocks;
         }
         return ti;
     }
@@ -158,10 +209,13 @@ __device__ __forceinline__ void quantize_row_blocks(const uint32_t (&w)[32], uin
 struct Maps {        // by-value kernel argument
     CUtensorMap A, B, A2, B2;          // E4M3 data, 128-byte swizzle, boxes of 128 x 128
     CUtensorMap SA, SB, SA2, SB2;      // scale tiles: rows of 128 u32
+    CUtensorMap B3, SB3;               // FMODE_FWD: the down weights (A2 / SA2 are then the hidden rows)
 };
 
+// 128 registers per thread at most (see gemm.cu): ten warps put three on an SM quarter, and the blocks of the
+// dispatch and quantise kernels that this GEMM may be waiting for have to fit beside them.
 template <int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __maxnreg__(128)
 grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -197,6 +251,10 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
         tma_prefetch_desc(&tm.A); tma_prefetch_desc(&tm.B); tma_prefetch_desc(&tm.SA); tma_prefetch_desc(&tm.SB);
         if (kGateUp<MODE> || p.dual) { tma_prefetch_desc(&tm.B2); tma_prefetch_desc(&tm.SB2); }
         if (p.dual) { tma_prefetch_desc(&tm.A2); tma_prefetch_desc(&tm.SA2); }
+        if (MODE == FMODE_FWD) {
+            tma_prefetch_desc(&tm.B2); tma_prefetch_desc(&tm.SB2);
+            if (p.N2 > 0) { tma_prefetch_desc(&tm.A2); tma_prefetch_desc(&tm.SA2); tma_prefetch_desc(&tm.B3); tma_prefetch_desc(&tm.SB3); }
+        }
     }
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
@@ -217,9 +275,27 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
             uint32_t ph = 0;
             bool ok = true;
             const int kh = p.K / BKB;
+            int waited_window = -1;
+            Tile next_ti = {};         // worked out one tile ahead: the look-up would otherwise stall short tiles
+            if (tile_id0 < sched.total) next_ti = sched.get(p, tile_id0);
             for (int t = tile_id0; ok && t < sched.total; t += tile_stride) {
-                const Tile ti = sched.get(p, t);
+                const Tile ti = next_ti;
+                if (t + tile_stride < sched.total) next_ti = sched.get(p, t + tile_stride);
                 const int row0 = ti.m_blk * TILE_M + static_cast<int>(cta) * 128;     // this CTA's rows of A (and of D)
+                if (MODE != FMODE_WGRAD) {
+                    // rows that another kernel (or, for a down tile, other CTAs of this one) is still producing
+                    bool fenced = false;
+                    if (p.win_ready && ti.phase == 0 && ti.window > waited_window) {
+                        if (!flag_wait(p.win_ready + ti.window, p.win_ready_target, abort_flag, p.status, kWaitWindowReady, ti.window)) { ok = false; break; }
+                        waited_window = ti.window;
+                        fenced = true;
+                    }
+                    if (MODE == FMODE_FWD && ti.phase == 1) {
+                        if (!flag_wait(p.blk_done + (ti.m_blk - sched.m_first), sched.n_gu * 16, abort_flag, p.status, kWaitBlockDone, ti.m_blk - sched.m_first)) { ok = false; break; }
+                        fenced = true;
+                    }
+                    if (fenced) fence_proxy_async_global();
+                }
                 for (int it = 0; it < ti.k_iters; ++it) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
                     const uint32_t fb_local = full_bar(s);
@@ -236,6 +312,13 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
                         tma_load_2d_pair(sfa_dst, &tm.SA, fb, 0, (row0 / 128) * p.a_ktiles + kt);
                         tma_load_2d_pair(sfa_dst + SF_TILE, &tm.SB, fb, 0, (brow / 128) * p.b_ktiles + kt);
                         tma_load_2d_pair(sfa_dst + 2 * SF_TILE, &tm.SB, fb, 0, (brow / 128 + 1) * p.b_ktiles + kt);
+                    } else if (MODE == FMODE_FWD && ti.phase == 1) {
+                        const int brow = ti.group * p.b3_rows_per_group + ti.n_blk * BN;
+                        tma_load_2d_pair(a_dst, &tm.A2, fb, it * BKB, row0);
+                        tma_load_2d_pair(sfa_dst, &tm.SA2, fb, 0, (row0 / 128) * p.a2_ktiles + it);
+                        tma_load_2d_pair(b_dst, &tm.B3, fb, it * BKB, brow + static_cast<int>(cta) * 128);
+                        tma_load_2d_pair(sfa_dst + SF_TILE, &tm.SB3, fb, 0, (brow / 128) * p.b3_ktiles + it);
+                        tma_load_2d_pair(sfa_dst + 2 * SF_TILE, &tm.SB3, fb, 0, (brow / 128 + 1) * p.b3_ktiles + it);
                     } else {
                         const bool second = it >= kh;
                         const int kt = second ? it - kh : it;
@@ -243,7 +326,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
                         const CUtensorMap* tsa = second ? &tm.SA2 : &tm.SA;
                         tma_load_2d_pair(a_dst, ta, fb, kt * BKB, row0);
                         tma_load_2d_pair(sfa_dst, tsa, fb, 0, (row0 / 128) * p.a_ktiles + kt);
-                        if (kGateUp<MODE>) {
+                        if (kGateUp<MODE> || MODE == FMODE_FWD) {
                             const int brow = ti.group * p.b_rows_per_group + ti.n_blk * 128;
                             tma_load_2d_pair(b_dst, cta == 0 ? &tm.B : &tm.B2, fb, kt * BKB, brow);
                             tma_load_2d_pair(sfa_dst + SF_TILE, &tm.SB, fb, 0, (brow / 128) * p.b_ktiles + kt);
@@ -270,8 +353,11 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
             uint32_t ph = 0;
             bool ok = true;
             int local = 0;
+            Tile next_ti = {};
+            if (tile_id0 < sched.total) next_ti = sched.get(p, tile_id0);
             for (int t = tile_id0; ok && t < sched.total; t += tile_stride, ++local) {
-                const Tile ti = sched.get(p, t);
+                const Tile ti = next_ti;
+                if (t + tile_stride < sched.total) next_ti = sched.get(p, t + tile_stride);
                 if (!mbar_wait(tempty_bar, (local & 1) ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base;
@@ -312,7 +398,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
             const Tile ti = sched.get(p, t);
             if (!mbar_wait(tfull_bar, local & 1, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
             tc_fence_after();
-            if (MODE == FMODE_GATEUP_QUANT) {
+            if (MODE == FMODE_GATEUP_QUANT || (MODE == FMODE_FWD && ti.phase == 0)) {
                 // This warp: 32 rows (its lanes) x gate columns [64 half, +64) and the matching up columns of the tile.
                 const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
                 uint32_t gw[32], uw[32];                    // bf16 pairs: the values the bf16 path would have stored
@@ -375,6 +461,10 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
                     p.hid_sct[scale_offset(col, row_blk0 >> 5, p.t_rows >> 7)] = static_cast<uint8_t>(my_scales & 0xffu);
                     p.hid_sct[scale_offset(col + 1, row_blk0 >> 5, p.t_rows >> 7)] = static_cast<uint8_t>(my_scales >> 8);
                 }
+                if (MODE == FMODE_FWD) {      // this warp's part of the hidden rows is stored: count it for the down tiles
+                    __syncwarp();
+                    if (lane == 0) red_release_gpu_add(p.blk_done + (ti.m_blk - sched.m_first), 1);
+                }
                 continue;
             }
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * 128);
@@ -393,7 +483,17 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
                     row += static_cast<size_t>(ti.group) * p.M;
                 }
                 dst = p.D + row * p.ldd + static_cast<size_t>(ti.n_blk) * BN + half * 128;
-                cols_left = p.N - ti.n_blk * BN - half * 128;
+                cols_left = (MODE == FMODE_FWD ? p.N2 : p.N) - ti.n_blk * BN - half * 128;
+                if (p.D == nullptr) row_ok = false;        // pushed only
+            }
+            __nv_bfloat16* pdst = nullptr;                 // this row's place in its home rank's buffer
+            if ((MODE == FMODE_NT || MODE == FMODE_FWD) && p.push) {
+                const int pr = p.push_rank[tile_row];
+                if (pr >= 0 && pr < p.push_ranks) {
+                    const size_t slot = static_cast<size_t>(p.push_idx[tile_row]);
+                    pdst = static_cast<__nv_bfloat16*>(p.push_dst.p[pr]) + slot * p.ldd + static_cast<size_t>(ti.n_blk) * BN + half * 128;
+                    if (p.push_values && ti.n_blk == 0 && half == 0) static_cast<float*>(p.push_val.p[pr])[slot] = p.push_values[tile_row];
+                }
             }
             const bool add_old = MODE == FMODE_WGRAD && p.accumulate;
             if (add_old && empty_k) row_ok = false;        // nothing to add: the stored gradient stays
@@ -437,6 +537,22 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
                             st_global_v4(dst + 8 * q, packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                 }
             }
+            if (pdst) {
+                if (p.push_wide) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        if (q * 16 < cols_left) st_global_v8(pdst + 16 * q, &packed[8 * q]);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 16; ++q)
+                        if (q * 8 < cols_left)
+                            st_global_v4(pdst + 8 * q, packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+            if (MODE == FMODE_FWD && p.win_done) {
+                __syncwarp();
+                if (lane == 0) red_release_gpu_add(p.win_done + ti.window, 1);
+            }
         }
     }
 
@@ -459,6 +575,8 @@ template <int MODE>
 int launch(const Maps& m, const FParams& p, int tiles_upper_bound, cudaStream_t stream) {
     MOKB_CUDA(cudaFuncSetAttribute(grouped_gemm_mxfp8_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     int pairs = sm_count() / 2;
+    // a launch that waits for another kernel's rows leaves one pair of SMs to that kernel (see gemm.cu)
+    if (p.win_ready && pairs > 2) pairs -= 1;
     if (tiles_upper_bound < pairs) pairs = tiles_upper_bound;
     if (pairs < 1) return MOKB_OK;
     cudaLaunchConfig_t cfg = {};
@@ -493,10 +611,13 @@ using namespace mokb;
 extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     MOKB_REQUIRE(g != nullptr, "grouped_gemm_mxfp8: null args");
-    static const char* const kTags[4] = {"gemm_mxfp8_nt", "gemm_mxfp8_gate_up", "gemm_mxfp8_wgrad", "gemm_mxfp8_gate_up_swiglu_quant"};
-    TraceScope trace(stream, kTags[g->mode >= 0 && g->mode <= 3 ? g->mode : 0], g->row_begin);
-    MOKB_REQUIRE(g->mode >= 0 && g->mode <= 3, "grouped_gemm_mxfp8: unknown mode %d", g->mode);
-    MOKB_REQUIRE(g->A && g->A_sc && g->B && g->B_sc && (g->D || g->mode == FMODE_GATEUP_QUANT) && g->status, "grouped_gemm_mxfp8: null pointer");
+    static const char* const kTags[5] = {"gemm_mxfp8_nt", "gemm_mxfp8_gate_up", "gemm_mxfp8_wgrad", "gemm_mxfp8_gate_up_swiglu_quant",
+                                         "gemm_mxfp8_fwd_routed"};
+    TraceScope trace(stream, kTags[g->mode >= 0 && g->mode <= 4 ? g->mode : 0], g->row_begin);
+    MOKB_REQUIRE(g->mode >= 0 && g->mode <= 4, "grouped_gemm_mxfp8: unknown mode %d", g->mode);
+    MOKB_REQUIRE(g->A && g->A_sc && g->B && g->B_sc && g->status, "grouped_gemm_mxfp8: null pointer");
+    MOKB_REQUIRE(g->D || g->mode == FMODE_GATEUP_QUANT || g->mode == FMODE_FWD || (g->mode == FMODE_NT && g->push_ptrs_host),
+                 "grouped_gemm_mxfp8: D may only be left out when the result is pushed to peers");
     MOKB_REQUIRE(g->G >= 1 && g->ldd % 8 == 0, "grouped_gemm_mxfp8: bad G or ldd");
     MOKB_REQUIRE(g->rows_static > 0 && g->rows_static % 256 == 0, "grouped_gemm_mxfp8: rows must be a positive multiple of 256");
     FParams p;
@@ -515,6 +636,30 @@ extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream
     p.ldd = g->ldd;
     p.wide_stores = g->ldd % 16 == 0 && reinterpret_cast<uintptr_t>(g->D) % 32 == 0 && reinterpret_cast<uintptr_t>(g->D2) % 32 == 0;
     p.status = g->status;
+    if (g->push_ptrs_host) {
+        MOKB_REQUIRE(g->mode == FMODE_NT || g->mode == FMODE_FWD, "grouped_gemm_mxfp8: push is for modes 0 and 4");
+        MOKB_REQUIRE(g->push_ep_size >= 1 && g->push_ep_size <= MOKB_MAX_EP && g->push_rank && g->push_idx, "grouped_gemm_mxfp8: push needs ranks and indices");
+        MOKB_REQUIRE((g->push_values == nullptr) == (g->push_value_ptrs_host == nullptr), "grouped_gemm_mxfp8: push_values and push_value_ptrs_host go together");
+        p.push = 1; p.push_ranks = g->push_ep_size; p.push_rank = g->push_rank; p.push_idx = g->push_idx; p.push_values = g->push_values;
+        p.push_wide = g->ldd % 16 == 0;
+        for (int r = 0; r < kPeerMax; ++r) p.push_dst.p[r] = p.push_val.p[r] = nullptr;
+        for (int r = 0; r < g->push_ep_size; ++r) {
+            MOKB_REQUIRE(g->push_ptrs_host[r] != 0 && (g->push_ptrs_host[r] & 15) == 0, "grouped_gemm_mxfp8: push pointer of rank %d is null or not 16-byte aligned", r);
+            p.push_dst.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(g->push_ptrs_host[r]));
+            if ((g->push_ptrs_host[r] & 31) != 0) p.push_wide = 0;
+            if (g->push_value_ptrs_host) {
+                MOKB_REQUIRE(g->push_value_ptrs_host[r] != 0, "grouped_gemm_mxfp8: push value pointer of rank %d is null", r);
+                p.push_val.p[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(g->push_value_ptrs_host[r]));
+            }
+        }
+    }
+    if (g->mode != FMODE_WGRAD) {
+        MOKB_REQUIRE(g->window_rows >= 0 && g->window_rows % 256 == 0, "grouped_gemm_mxfp8: window_rows must be a multiple of 256");
+        MOKB_REQUIRE(g->win_ready == nullptr || (g->window_rows > 0 && g->win_ready_target > 0), "grouped_gemm_mxfp8: win_ready needs window_rows and a target");
+        p.window_rows = g->window_rows;
+        p.win_ready = g->win_ready;
+        p.win_ready_target = g->win_ready_target;
+    }
     Maps m;
     memset(&m, 0, sizeof(m));
     const uint64_t rows = static_cast<uint64_t>(g->rows_static);
@@ -540,10 +685,10 @@ extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream
     MOKB_TRY(data_map(&m.B, g->B, g->K, brows));
     MOKB_TRY(scale_map(&m.SA, g->A_sc, (rows / 128) * (g->K / 128)));
     MOKB_TRY(scale_map(&m.SB, g->B_sc, (brows / 128) * (g->K / 128)));
-    m.A2 = m.A; m.B2 = m.B; m.SA2 = m.SA; m.SB2 = m.SB;
+    m.A2 = m.A; m.B2 = m.B; m.SA2 = m.SA; m.SB2 = m.SB; m.B3 = m.B; m.SB3 = m.SB;
     p.a_ktiles = p.b_ktiles = g->K / 128;
     p.b_rows_per_group = g->N;
-    if (g->mode == FMODE_DUALB || g->mode == FMODE_GATEUP_QUANT) {
+    if (g->mode == FMODE_DUALB || g->mode == FMODE_GATEUP_QUANT || g->mode == FMODE_FWD) {
         MOKB_REQUIRE(g->B2 && g->B2_sc, "grouped_gemm_mxfp8 gate/up: B2 and B2_sc required");
         MOKB_TRY(data_map(&m.B2, g->B2, g->K, brows));
         MOKB_TRY(scale_map(&m.SB2, g->B2_sc, (brows / 128) * (g->K / 128)));
@@ -563,6 +708,24 @@ extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream
         p.t_rows = g->t_rows;
         p.has_limit = g->has_swiglu_limit;
         p.limit = g->swiglu_limit;
+        if (g->mode == FMODE_FWD) {
+            MOKB_REQUIRE(g->blk_done != nullptr, "grouped_gemm_mxfp8 mode 4: blk_done required");
+            MOKB_REQUIRE(g->N2 >= 0 && g->N2 % BN == 0, "grouped_gemm_mxfp8 mode 4: N2 must be a multiple of 256");
+            p.blk_done = g->blk_done;
+            p.win_done = g->win_done;
+            if (g->N2 > 0) {
+                // the down projection reads the hidden rows this launch writes: A2 = hid_q [rows, N], contraction over N
+                MOKB_REQUIRE(g->B3 && g->B3_sc && (g->D || g->push_ptrs_host), "grouped_gemm_mxfp8 mode 4: B3, B3_sc and D (or push pointers) required");
+                const uint64_t b3rows = static_cast<uint64_t>(g->G) * g->N2;
+                MOKB_TRY(data_map(&m.A2, g->hid_q, g->N, rows));
+                MOKB_TRY(scale_map(&m.SA2, g->hid_sc, (rows / 128) * (g->N / 128)));
+                MOKB_TRY(data_map(&m.B3, g->B3, g->N, b3rows));
+                MOKB_TRY(scale_map(&m.SB3, g->B3_sc, (b3rows / 128) * (g->N / 128)));
+                p.N2 = g->N2; p.K2 = g->N; p.b3_rows_per_group = g->N2;
+                p.a2_ktiles = p.b3_ktiles = g->N / 128;
+            }
+            return launch<FMODE_FWD>(m, p, m_tiles * (g->N / 128 + g->N2 / BN), stream);
+        }
         return launch<FMODE_GATEUP_QUANT>(m, p, m_tiles * (g->N / 128), stream);
     }
     if (g->A2) {

@@ -89,11 +89,11 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_arg
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
     cudaStream_t s_in = overlap ? as->s1 : stream;
-    const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
+    const int comm_blocks = overlap ? a->num_comm_sms * kCommBlocksPerSm : 0;
     // recompute only rebuilds macrobatch 0 (the saved context); the forward walks all of them, last first
     const int n_macro = with_down ? macrobatches(C, MB) : 1;
 
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, s, a->status, stream));
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, a->peer_rank, E_l, C, MB, T, s, a->status, stream));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
     bool shared_done = false;
 
@@ -184,17 +184,19 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
     cudaStream_t s_in = overlap ? as->s1 : stream;
-    const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
+    const int comm_blocks = overlap ? a->num_comm_sms * kCommBlocksPerSm : 0;
     const int lim = a->has_swiglu_limit;
     const float limv = a->swiglu_limit;
     const int n_macro = macrobatches(C, MB);
 
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, s, a->status, stream));
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, a->peer_rank, E_l, C, MB, T, s, a->status, stream));
     const void* d_y_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->d_y_ptrs_host[a->ep_rank]));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
-    auto wgrad = [&](const void* A, int M, const void* B, int N, void* D, int G, int rows, const int32_t* offs, int accumulate) -> int {
+    auto wgrad = [&](const void* A, int M, const void* B, int N, void* D, int G, int rows, const int32_t* offs, int accumulate,
+                     const int32_t* k_end = nullptr) -> int {
         mokb_gemm_args w = gemm_base(a->status);
         w.mode = 3; w.rows_static = rows; w.G = G; w.M = M; w.N = N; w.group_offsets = offs; w.accumulate = accumulate;
+        w.group_k_end = k_end;       // the padding rows at the end of every expert's segment are zero: not multiplied
         w.A = A; w.lda = M; w.B = B; w.ldb = N; w.D = D; w.ldd = N;
         return mokb_grouped_gemm_bf16(&w, stream);
     };
@@ -289,9 +291,10 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
         g.push_values = d_w_row; g.push_value_ptrs_host = a->d_router_weight_ptrs_host;
         MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
         const int32_t* offs = s.mb_offsets + static_cast<size_t>(m) * (E_l + 1);
-        MOKB_TRY(wgrad(d_y_r, H, hidden_r, I, a->d_w_routed_down, E_l, hi, offs, m > 0));
-        MOKB_TRY(wgrad(d_gate_r, I, x_routed, H, a->d_w_routed_gate, E_l, hi, offs, m > 0));
-        MOKB_TRY(wgrad(d_up_r, I, x_routed, H, a->d_w_routed_up, E_l, hi, offs, m > 0));
+        const int32_t* k_end = s.mb_k_end + static_cast<size_t>(m) * (E_l + 1);
+        MOKB_TRY(wgrad(d_y_r, H, hidden_r, I, a->d_w_routed_down, E_l, hi, offs, m > 0, k_end));
+        MOKB_TRY(wgrad(d_gate_r, I, x_routed, H, a->d_w_routed_gate, E_l, hi, offs, m > 0, k_end));
+        MOKB_TRY(wgrad(d_up_r, I, x_routed, H, a->d_w_routed_up, E_l, hi, offs, m > 0, k_end));
     }
     return MOKB_OK;
 }

@@ -20,6 +20,7 @@ struct Scratch {
     int32_t* n_rows;           // [1] validated number of routed rows (0 if the schedule is unusable)
     int32_t* mb_rows;          // [n_macro] rows of macrobatch m
     int32_t* mb_offsets;       // [n_macro][E_l + 1] expert offsets clamped to macrobatch m's row range
+    int32_t* mb_k_end;         // [n_macro][E_l] end of each expert's scheduled rows (the rest of its segment is padding), clamped likewise
     int32_t* group_of_block;   // [capacity / 128]
     float* w_row;              // [MB] router weight of each routed row of the current macrobatch (backward)
     float* d_w_row;            // [MB] router-weight gradient of each routed row (backward)
@@ -34,10 +35,12 @@ inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 inline int macrobatches(int capacity, int MB) { return (capacity + MB - 1) / MB; }
 
 constexpr int kMaxChunks = 32;     // windows per macrobatch (side-stream events, counters)
+// `num_comm_sms` SMs' worth of communication threads: 2048 per SM, in blocks of 128 (see comm.cu)
+constexpr int kCommBlocksPerSm = 16;
 
 inline size_t scratch_bytes(int capacity, int E_l, int MB) {
     const size_t nm = macrobatches(capacity, MB);
-    return align256((E_l + 1) * 4) + 512 + align256(nm * 4) + align256(nm * (E_l + 1) * 4) +
+    return align256((E_l + 1) * 4) + 512 + align256(nm * 4) + 2 * align256(nm * (E_l + 1) * 4) +
            align256(static_cast<size_t>(capacity / 128) * 4) + 2 * align256(static_cast<size_t>(MB) * 4) +
            2 * align256(kMaxChunks * 4) + align256(static_cast<size_t>(capacity / 256) * 4);
 }
@@ -51,6 +54,7 @@ inline Scratch carve(void* base, int capacity, int E_l, int MB) {
     s.n_rows = reinterpret_cast<int32_t*>(p); p += 256;
     s.mb_rows = reinterpret_cast<int32_t*>(p); p += align256(nm * 4);
     s.mb_offsets = reinterpret_cast<int32_t*>(p); p += align256(nm * (E_l + 1) * 4);
+    s.mb_k_end = reinterpret_cast<int32_t*>(p); p += align256(nm * (E_l + 1) * 4);
     s.group_of_block = reinterpret_cast<int32_t*>(p); p += align256(static_cast<size_t>(capacity / 128) * 4);
     s.w_row = reinterpret_cast<float*>(p); p += align256(static_cast<size_t>(MB) * 4);
     s.d_w_row = reinterpret_cast<float*>(p); p += align256(static_cast<size_t>(MB) * 4);
@@ -63,7 +67,7 @@ inline Scratch carve(void* base, int capacity, int E_l, int MB) {
 // One CTA: segment offsets from tokens_per_expert, row-block -> expert table, per-macrobatch
 // offsets, and the capacity check that the reference turns into a trap.
 __global__ void prologue_kernel(const int32_t* __restrict__ tokens_per_expert, const int32_t* __restrict__ num_tokens,
-                                int E_l, int capacity, int MB, int T, Scratch s, int32_t* status) {
+                                const int32_t* __restrict__ peer_rank, int E_l, int capacity, int MB, int T, Scratch s, int32_t* status) {
     __shared__ int32_t offs[2049];
     __shared__ int32_t ok_s;
     if (threadIdx.x == 0) {
@@ -86,6 +90,21 @@ __global__ void prologue_kernel(const int32_t* __restrict__ tokens_per_expert, c
     const int total = ok ? offs[E_l] : 0;
     for (int e = threadIdx.x; e <= E_l; e += blockDim.x) s.expert_offsets[e] = ok ? offs[e] : 0;
     const int nm = (capacity + MB - 1) / MB;
+    for (int e = threadIdx.x; e < E_l; e += blockDim.x) {
+        // the scheduled rows of an expert come first in its segment and fewer than 256 padding rows follow
+        // (csrc/scheduler.cuh:134-139): find where the padding starts in the segment's last 256 rows
+        int end = ok ? offs[e + 1] : 0;
+        const int begin = ok ? offs[e] : 0;
+        if (end > begin) {
+            int lo = end - 256, hi = end;          // first row in [lo, hi) with peer_rank < 0, or hi
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (peer_rank[mid] < 0) hi = mid; else lo = mid + 1;
+            }
+            end = lo;
+        }
+        for (int m = 0; m < nm; ++m) s.mb_k_end[m * (E_l + 1) + e] = min(max(end, m * MB), m * MB + MB);
+    }
     for (int m = 0; m < nm; ++m) {
         const int lo = m * MB, hi = lo + MB;
         for (int e = threadIdx.x; e <= E_l; e += blockDim.x) {
@@ -112,9 +131,10 @@ __global__ void prologue_kernel(const int32_t* __restrict__ tokens_per_expert, c
     for (int i = threadIdx.x; i < capacity / 256; i += blockDim.x) s.blk_done[i] = 0;
 }
 
-inline int run_prologue(const int32_t* tpe, const int32_t* num_tokens, int E_l, int C, int MB, int T, const Scratch& s, int32_t* status, cudaStream_t stream) {
+inline int run_prologue(const int32_t* tpe, const int32_t* num_tokens, const int32_t* peer_rank, int E_l, int C, int MB, int T, const Scratch& s,
+                        int32_t* status, cudaStream_t stream) {
     MOKB_REQUIRE(E_l <= 2048, "layer: at most 2048 local experts");
-    prologue_kernel<<<1, 256, 0, stream>>>(tpe, num_tokens, E_l, C, MB, T, s, status);
+    prologue_kernel<<<1, 256, 0, stream>>>(tpe, num_tokens, peer_rank, E_l, C, MB, T, s, status);
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     return MOKB_OK;

@@ -109,7 +109,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
     MOKB_REQUIRE(a->x_routed && a->x_fp8 && a->x_sc && a->hidden_fp8 && a->hidden_sc, "fwd_mxfp8: null work buffer");
     const bool with_down = !a->skip_down_combine;
     if (with_down)
-        MOKB_REQUIRE(a->combine_ptrs_host && a->w_shared_down && a->w_routed_down && a->w_routed_down_sc && a->y_shared && a->y_routed,
+        MOKB_REQUIRE(a->combine_ptrs_host && a->w_shared_down && a->w_routed_down && a->w_routed_down_sc && a->y_shared,
                      "fwd_mxfp8: null down/combine pointer");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
     const int C = a->schedule_capacity;
@@ -117,39 +117,46 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
-    cudaStream_t s_in = overlap ? as->s1 : stream, s_out = overlap ? as->s2 : stream;
-    const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
+    cudaStream_t s_in = overlap ? as->s1 : stream;
+    const int comm_blocks = overlap ? a->num_comm_sms * kCommBlocksPerSm : 0;
     // recompute only rebuilds macrobatch 0 (the saved context); the forward walks all of them, last first
     const int n_macro = with_down ? macrobatches(C, MB) : 1;
     const GateUpWeights wgu{a->w_routed_gate, a->w_routed_gate_sc, a->w_routed_up, a->w_routed_up_sc};
 
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, s, a->status, stream));
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, a->peer_rank, E_l, C, MB, T, s, a->status, stream));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
     bool shared_done = false;
 
     for (int mi = 0; mi < n_macro; ++mi) {
         const int m = n_macro - 1 - mi;
         const int lo = m * MB, hi = (lo + MB < C) ? lo + MB : C;
-        // only macrobatch 0 (the one that is always populated) is cut into overlap windows
+        // only macrobatch 0 (the one that is always populated) is cut into overlap windows, which are tied to the one
+        // persistent GEMM launch by counters (layer.cu)
         const int chunk = m == 0 ? chunk_rows_for(MB, a->minibatch_size) : MB;
         const int nchunks = (hi - lo + chunk - 1) / chunk;
+        const bool flags = overlap && m == 0;
         const FwdView v = fwd_view(lo, H, I, a->x_routed, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, a->gate_fp8,
                                    a->gate_sc, a->up_fp8, a->up_sc, a->hidden_fp8, a->hidden_sc, a->hidden_fp8_t, a->hidden_sc_t);
-        void* y_r = with_down ? rebase(a->y_routed, lo, 2ull * H) : nullptr;
+        void* y_r = (with_down && a->y_routed) ? rebase(a->y_routed, lo, 2ull * H) : nullptr;
 
         if (overlap) {     // everything enqueued so far (previous macrobatch included) precedes this one's side work
             MOKB_CUDA(cudaEventRecord(as->fork, stream));
             MOKB_CUDA(cudaStreamWaitEvent(s_in, as->fork, 0));
-            if (with_down) MOKB_CUDA(cudaStreamWaitEvent(s_out, as->fork, 0));
         }
-        // dispatch + quantise (row-wise for the GEMM, token-wise for the weight gradients), window by window
+        // dispatch, window by window: the pull also quantises every row along its columns (what the GEMM reads) and
+        // raises the window's counter; the token-wise form (for the weight gradients of the backward pass) follows
+        // from the bf16 rows, under the GEMMs
         for (int c = 0; c < nchunks; ++c) {
             const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
             MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
-                                        v.x_routed, nullptr, nullptr, comm_blocks, s_in));
-            MOKB_TRY(quantize_impl(v.x_routed, 1, MB, H, s.n_rows, r0, r1, v.x_fp8, v.x_sc, v.x_fp8_t, v.x_sc_t, s_in));
-            if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+                                        v.x_routed, nullptr, nullptr, comm_blocks, s_in, flags ? s.win_ready + c : nullptr,
+                                        v.x_fp8, v.x_sc));
         }
+        for (int c = 0; c < nchunks; ++c) {
+            const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
+            MOKB_TRY(quantize_impl(v.x_routed, 1, MB, H, s.n_rows, r0, r1, nullptr, nullptr, v.x_fp8_t, v.x_sc_t, s_in, comm_blocks));
+        }
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
 
         if (!shared_done) {
             // shared expert (BF16): gate/up + SwiGLU in one pass, then down (independent of the dispatch)
@@ -168,29 +175,28 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
             }
         }
 
-        // routed experts (MXFP8), window by window behind the dispatch
-        for (int c = 0; c < nchunks; ++c) {
-            const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
-            if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
-            MOKB_TRY(gate_up_swiglu(v, wgu, s, r0, r1, hi, MB, E_l, H, I, a->has_swiglu_limit, a->swiglu_limit, a->status, stream));
-            if (!with_down) continue;
-            mokb_gemm_fp8_args f = fp8_base(a->status);
-            f.mode = 0; f.rows_static = hi; f.row_begin = r0; f.row_end = r1;
-            f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = H; f.K = I;
-            f.A = v.hidden_fp8; f.A_sc = v.hidden_sc; f.B = a->w_routed_down; f.B_sc = a->w_routed_down_sc; f.D = y_r; f.ldd = H;
-            MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-            // combine: push the window's rows back to slot t*K+k of their home ranks
-            if (overlap) {
-                MOKB_CUDA(cudaEventRecord(as->ev_out[c], stream));
-                MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[c], 0));
-            }
-            MOKB_TRY(combine_rows_impl(y_r, a->combine_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, H,
-                                       nullptr, nullptr, comm_blocks, s_out));
+        // routed experts (MXFP8): gate|up + SwiGLU + quantisation and the down projection of every window in one launch;
+        // the down epilogue stores every row into its home rank's combine buffer
+        if (overlap && !flags) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
+        mokb_gemm_fp8_args f = fp8_base(a->status);
+        f.mode = 4; f.rows_static = hi; f.row_begin = lo; f.row_end = hi;
+        f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
+        f.A = v.x_fp8; f.A_sc = v.x_sc; f.B = wgu.gate; f.B_sc = wgu.gate_sc; f.B2 = wgu.up; f.B2_sc = wgu.up_sc;
+        f.gate_q = v.gate_fp8; f.gate_sc = v.gate_sc; f.up_q = v.up_fp8; f.up_sc = v.up_sc;
+        f.hid_q = v.hidden_fp8; f.hid_sc = v.hidden_sc; f.hid_qt = v.hidden_fp8_t; f.hid_sct = v.hidden_sc_t;
+        f.t_rows = MB; f.has_swiglu_limit = a->has_swiglu_limit; f.swiglu_limit = a->swiglu_limit;
+        f.window_rows = chunk;
+        f.blk_done = s.blk_done + lo / 256;
+        if (flags) { f.win_ready = s.win_ready; f.win_ready_target = comm_blocks; }
+        f.ldd = H;
+        if (with_down) {
+            f.B3 = a->w_routed_down; f.B3_sc = a->w_routed_down_sc; f.N2 = H; f.D = y_r;
+            f.push_ptrs_host = a->combine_ptrs_host; f.push_ep_size = a->ep_size;
+            f.push_rank = a->peer_rank; f.push_idx = a->peer_token_idx;
         }
-        if (overlap && with_down) {    // the next macrobatch overwrites y_routed: the combine must be done with it
-            MOKB_CUDA(cudaEventRecord(as->join2, s_out));
-            MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
-        }
+        MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
+        // the next macrobatch (or the caller) reuses the pulled rows: the side stream must be done with them
+        if (flags) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
     }
     return MOKB_OK;
 }
@@ -204,7 +210,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
                  a->w_routed_up_t_sc && a->w_routed_down_t && a->w_routed_down_t_sc, "bwd_mxfp8: null weight");
     MOKB_REQUIRE(a->x_fp8_t && a->x_sc_t && a->gate_shared && a->gate_fp8 && a->gate_sc && a->up_shared && a->up_fp8 && a->up_sc &&
                  a->hidden_shared && a->hidden_fp8_t && a->hidden_sc_t, "bwd_mxfp8: null forward context");
-    MOKB_REQUIRE(a->d_x_shared && a->d_x_routed && a->d_gate_shared && a->d_gate_fp8 && a->d_gate_sc && a->d_up_shared && a->d_up_fp8 &&
+    MOKB_REQUIRE(a->d_x_shared && a->d_gate_shared && a->d_gate_fp8 && a->d_gate_sc && a->d_up_shared && a->d_up_fp8 &&
                  a->d_up_sc && a->d_hidden_shared && a->d_hidden_routed && a->d_y_fp8 && a->d_y_sc && a->d_w_shared_gate &&
                  a->d_w_routed_gate && a->d_w_shared_up && a->d_w_routed_up && a->d_w_shared_down && a->d_w_routed_down, "bwd_mxfp8: null output");
     MOKB_REQUIRE(a->d_y_routed && a->d_y_fp8_t && a->d_y_sc_t && a->d_gate_fp8_t && a->d_gate_sc_t && a->d_up_fp8_t && a->d_up_sc_t && a->partials,
@@ -220,13 +226,13 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
-    cudaStream_t s_in = overlap ? as->s1 : stream, s_out = overlap ? as->s2 : stream;
-    const int comm_blocks = overlap ? a->num_comm_sms * 8 : 0;
+    cudaStream_t s_in = overlap ? as->s1 : stream;
+    const int comm_blocks = overlap ? a->num_comm_sms * kCommBlocksPerSm : 0;
     const int lim = a->has_swiglu_limit;
     const float limv = a->swiglu_limit;
     const GateUpWeights wgu{a->w_routed_gate, a->w_routed_gate_sc, a->w_routed_up, a->w_routed_up_sc};
 
-    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, E_l, C, MB, T, s, a->status, stream));
+    MOKB_TRY(run_prologue(a->tokens_per_expert, a->num_tokens, a->peer_rank, E_l, C, MB, T, s, a->status, stream));
     const void* d_y_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->d_y_ptrs_host[a->ep_rank]));
     const void* x_local = reinterpret_cast<const void*>(static_cast<uintptr_t>(a->x_ptrs_host[a->ep_rank]));
 
@@ -249,7 +255,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
         void* d_up_sc = rebase_scales(a->d_up_sc, lo, I);
         void* d_up_fp8_t = rebase_t(a->d_up_fp8_t, lo);
         void* d_up_sc_t = rebase_scales_t(a->d_up_sc_t, lo);
-        void* d_x_r = rebase(a->d_x_routed, lo, 2ull * H);
+        void* d_x_r = a->d_x_routed ? rebase(a->d_x_routed, lo, 2ull * H) : nullptr;
         float* w_row = rebase(s.w_row, lo, 4);
         float* d_w_row = rebase(s.d_w_row, lo, 4);
         float* partials = rebase(static_cast<float*>(a->partials), lo, 4ull * (I / 128));
@@ -260,20 +266,27 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
         }
         if (m > 0) {       // replay: pull x again and quantise it both ways
             MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
-                                        v.x_routed, nullptr, nullptr, comm_blocks, s_in));
-            MOKB_TRY(quantize_impl(v.x_routed, 1, MB, H, s.n_rows, lo, hi, v.x_fp8, v.x_sc, v.x_fp8_t, v.x_sc_t, s_in));
+                                        v.x_routed, nullptr, nullptr, comm_blocks, s_in, nullptr, v.x_fp8, v.x_sc));
+            MOKB_TRY(quantize_impl(v.x_routed, 1, MB, H, s.n_rows, lo, hi, nullptr, nullptr, v.x_fp8_t, v.x_sc_t, s_in, comm_blocks));
         }
         if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));     // the replayed x is in place
         // reverse combine: pull d_y rows scaled by the route's router weight and quantise them both ways, in a few windows
+        // (macrobatch 0: the pull's blocks raise the window's counter for the one d_hidden launch below)
+        const bool flags = overlap && m == 0;
         const int bchunk = bwd_chunk_rows(hi - lo, m == 0);
         const int nb = (hi - lo + bchunk - 1) / bchunk;
         for (int c = 0; c < nb; ++c) {
             const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
             MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
-                                        d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in));
-            MOKB_TRY(quantize_impl(d_y_r, 1, MB, H, s.n_rows, r0, r1, d_y_fp8, d_y_sc, d_y_fp8_t, d_y_sc_t, s_in));
-            if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+                                        d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in, flags ? s.win_ready + c : nullptr,
+                                        d_y_fp8, d_y_sc));
         }
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[0], s_in));
+        for (int c = 0; c < nb; ++c) {       // the token-wise form of d_y, for the weight gradients at the end
+            const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
+            MOKB_TRY(quantize_impl(d_y_r, 1, MB, H, s.n_rows, r0, r1, nullptr, nullptr, d_y_fp8_t, d_y_sc_t, s_in, comm_blocks));
+        }
+        if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[1], s_in));
 
         if (m == 0) {
             // ---- shared expert (BF16; overlaps the dispatch above)
@@ -303,16 +316,15 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
         if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
         if (m > 0)         // replay gate|up + SwiGLU + quantisation into the context buffers
             MOKB_TRY(gate_up_swiglu(v, wgu, s, lo, hi, hi, MB, E_l, H, I, lim, limv, a->status, stream));
-        mokb_gemm_fp8_args f;
-        for (int c = 0; c < nb; ++c) {       // d_hidden = d_y_q * WdT_q^T, window by window behind the pull
-            const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
-            if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[c], 0));
-            f = fp8_base(a->status);
-            f.mode = 0; f.rows_static = hi; f.row_begin = r0; f.row_end = r1;
-            f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
-            f.A = d_y_fp8; f.A_sc = d_y_sc; f.B = a->w_routed_down_t; f.B_sc = a->w_routed_down_t_sc; f.D = d_hidden_r; f.ldd = I;
-            MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-        }
+        // d_hidden = d_y_q * WdT_q^T: one launch, window by window behind the pull
+        if (overlap && !flags) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[0], 0));
+        mokb_gemm_fp8_args f = fp8_base(a->status);
+        f.mode = 0; f.rows_static = hi; f.row_begin = lo; f.row_end = hi;
+        f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = I; f.K = H;
+        f.A = d_y_fp8; f.A_sc = d_y_sc; f.B = a->w_routed_down_t; f.B_sc = a->w_routed_down_t_sc; f.D = d_hidden_r; f.ldd = I;
+        if (flags) { f.window_rows = bchunk; f.win_ready = s.win_ready; f.win_ready_target = comm_blocks; }
+        MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
+        if (flags) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[0], 0));
         MOKB_TRY(swiglu_bwd_quant_impl(v.gate_fp8, v.gate_sc, v.up_fp8, v.up_sc, d_hidden_r, MB, I, s.n_rows, lo, hi, lim, limv, w_row,
                                        d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t, d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t,
                                        partials, d_w_row, stream));
@@ -321,15 +333,11 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
         f.num_rows = s.n_rows; f.group_of_block = s.group_of_block; f.G = E_l; f.N = H; f.K = I;
         f.A = d_gate_fp8; f.A_sc = d_gate_sc; f.B = a->w_routed_gate_t; f.B_sc = a->w_routed_gate_t_sc;
         f.A2 = d_up_fp8; f.A2_sc = d_up_sc; f.B2 = a->w_routed_up_t; f.B2_sc = a->w_routed_up_t_sc; f.D = d_x_r; f.ldd = H;
+        // reverse dispatch: the epilogue stores every d_x row and its router-weight gradient into the home rank's buffers
+        f.push_ptrs_host = a->d_x_routed_ptrs_host; f.push_ep_size = a->ep_size;
+        f.push_rank = a->peer_rank; f.push_idx = a->peer_token_idx;
+        f.push_values = d_w_row; f.push_value_ptrs_host = a->d_router_weight_ptrs_host;
         MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
-        // reverse dispatch: push d_x rows and the per-route router-weight gradient home (overlaps the weight gradients)
-        if (overlap) {
-            MOKB_CUDA(cudaEventRecord(as->ev_out[0], stream));
-            MOKB_CUDA(cudaStreamWaitEvent(s_out, as->ev_out[0], 0));
-        }
-        MOKB_TRY(combine_rows_impl(d_x_r, a->d_x_routed_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi,
-                                   H, d_w_row, a->d_router_weight_ptrs_host, comm_blocks, s_out));
-        if (overlap) MOKB_CUDA(cudaEventRecord(as->join2, s_out));
         const int32_t* offs = s.mb_offsets + static_cast<size_t>(m) * (E_l + 1);
         auto wgrad_fp8 = [&](const void* A, const void* A_sc, int M, const void* B, const void* B_sc, int N, void* D) -> int {
             mokb_gemm_fp8_args w = fp8_base(a->status);
@@ -338,10 +346,10 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
             return mokb_grouped_gemm_mxfp8(&w, stream);
         };
         // the token-wise tensors are passed as they lie in memory ([., MB], first token column = lo)
-        MOKB_TRY(wgrad_fp8(a->d_y_fp8_t, a->d_y_sc_t, H, a->hidden_fp8_t, a->hidden_sc_t, I, a->d_w_routed_down));
         MOKB_TRY(wgrad_fp8(a->d_gate_fp8_t, a->d_gate_sc_t, I, a->x_fp8_t, a->x_sc_t, H, a->d_w_routed_gate));
         MOKB_TRY(wgrad_fp8(a->d_up_fp8_t, a->d_up_sc_t, I, a->x_fp8_t, a->x_sc_t, H, a->d_w_routed_up));
-        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
+        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->ev_in[1], 0));      // the token-wise d_y is complete
+        MOKB_TRY(wgrad_fp8(a->d_y_fp8_t, a->d_y_sc_t, H, a->hidden_fp8_t, a->hidden_sc_t, I, a->d_w_routed_down));
     }
     return MOKB_OK;
 }

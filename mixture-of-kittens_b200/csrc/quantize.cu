@@ -108,20 +108,95 @@ __device__ __forceinline__ bool tile_in_window(const RowWindow& w, int64_t* r0) 
     return *r0 < live;
 }
 
-// grid (N/128, window rows/128, E), 256 threads.
-__global__ void __launch_bounds__(256) quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64_t N,
+// 256 threads per block; the blocks of the launch walk the 128 x 128 tiles of the window (column tiles fastest).
+__global__ void __launch_bounds__(256) quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t E, int64_t M, int64_t N,
                                                        RowWindow win,
                                                        uint8_t* __restrict__ q, uint8_t* __restrict__ sc,
-                                                       uint8_t* __restrict__ qt, uint8_t* __restrict__ sct) {
+                                                       uint8_t* __restrict__ qt, uint8_t* __restrict__ sct, int32_t* done_counter) {
     __shared__ uint32_t tile[TILE_WORDS];
-    const int64_t e = blockIdx.z;
-    const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
-    int64_t r0;
-    if (!tile_in_window(win, &r0)) return;
-    load_tile_bf16(tile, x + (e * M + r0) * N + c0, N);
-    __syncthreads();
-    if (q) quantize_tile_rows(tile, q, sc, e * M, r0, c0, N);
-    if (qt) quantize_tile_cols(tile, qt, sct, e * N, r0, c0, M);
+    const int live = win.num_rows ? min(max(*win.num_rows, 0), win.end) : win.end;
+    const int64_t row_tiles = live > win.begin ? (live - win.begin + TILE - 1) / TILE : 0;
+    const int64_t col_tiles = N / TILE;
+    const int64_t ntiles = E * row_tiles * col_tiles;
+    for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const int64_t e = t / (row_tiles * col_tiles);
+        const int64_t rem = t - e * row_tiles * col_tiles;
+        const int64_t rt = rem / col_tiles;
+        const int64_t c0 = (rem - rt * col_tiles) * TILE;
+        const int64_t r0 = win.begin + rt * TILE;
+        load_tile_bf16(tile, x + (e * M + r0) * N + c0, N);
+        __syncthreads();
+        if (q) quantize_tile_rows(tile, q, sc, e * M, r0, c0, N);
+        if (qt) quantize_tile_cols(tile, qt, sct, e * N, r0, c0, M);
+        __syncthreads();          // the tile is free for the next load
+    }
+    if (done_counter) {      // one arrival per block of the launch (also those without tiles): the window is quantised
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            red_release_gpu_add(done_counter, 1);
+        }
+    }
+}
+
+// Column-wise ("transposed") quantisation only, for tensors whose row-wise form already exists (the dispatch kernel
+// writes it as the rows arrive): qt [N, M] + scales from x [M, N].  128 rows x 64 columns per tile and 128 threads, so
+// that a block (17 KB of shared memory, one warp per SM quarter) fits on an SM beside a GEMM CTA and the pass can run
+// under the GEMMs instead of after them.  Same arithmetic as quantize_tile_cols.
+constexpr int CTILE_COLS = 64;
+constexpr int CPITCH = CTILE_COLS / 2 + 1;     // 33 words per staged row
+__global__ void __launch_bounds__(128) quantize_cols_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64_t N, RowWindow win,
+                                                            uint8_t* __restrict__ qt, uint8_t* __restrict__ sct) {
+    __shared__ uint32_t tile[TILE * CPITCH];
+    const int live = win.num_rows ? min(max(*win.num_rows, 0), win.end) : win.end;
+    const int64_t row_tiles = live > win.begin ? (live - win.begin + TILE - 1) / TILE : 0;
+    const int64_t col_tiles = N / CTILE_COLS;
+    const int64_t ntiles = row_tiles * col_tiles;
+    for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const int64_t rt = t / col_tiles;
+        const int64_t c0 = (t - rt * col_tiles) * CTILE_COLS;
+        const int64_t r0 = win.begin + rt * TILE;
+        // 128 rows x 128 bytes = 512 chunks of 32 bytes over 128 threads: four loads in flight per thread
+        uint32_t val[4][8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x + 128 * k;
+            ld_global_32B(x + (r0 + (i >> 2)) * N + c0 + (i & 3) * 16, val[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x + 128 * k;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) tile[(i >> 2) * CPITCH + (i & 3) * 8 + j] = val[k][j];
+        }
+        __syncthreads();
+        {
+            const int cp = threadIdx.x & 31, kb = threadIdx.x >> 5;      // a pair of adjacent columns, a block of 32 rows
+            uint32_t w[32];
+            uint32_t m = 0u;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                w[i] = tile[(kb * 32 + i) * CPITCH + cp];
+                m = absmax2(m, w[i]);
+            }
+            float inv_a, inv_b;
+            const uint32_t byte_a = scale_byte(bf16_lo(m), &inv_a);
+            const uint32_t byte_b = scale_byte(bf16_hi(m), &inv_b);
+            uint32_t out[8];
+            const int64_t col = c0 + 2 * cp;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                out[i] = e4m3x4(bf16_lo(w[4 * i]) * inv_a, bf16_lo(w[4 * i + 1]) * inv_a, bf16_lo(w[4 * i + 2]) * inv_a, bf16_lo(w[4 * i + 3]) * inv_a);
+            st_global_32B(qt + col * M + r0 + kb * 32, out);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                out[i] = e4m3x4(bf16_hi(w[4 * i]) * inv_b, bf16_hi(w[4 * i + 1]) * inv_b, bf16_hi(w[4 * i + 2]) * inv_b, bf16_hi(w[4 * i + 3]) * inv_b);
+            st_global_32B(qt + (col + 1) * M + r0 + kb * 32, out);
+            sct[scale_offset(col, (r0 >> 5) + kb, M >> 7)] = static_cast<uint8_t>(byte_a);
+            sct[scale_offset(col + 1, (r0 >> 5) + kb, M >> 7)] = static_cast<uint8_t>(byte_b);
+        }
+        __syncthreads();          // the tile is free for the next load
+    }
 }
 
 struct Clamp {
@@ -249,7 +324,7 @@ int check_window(const char* who, int row_begin, int* row_end, int64_t rows) {
 }  // namespace
 
 int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int32_t* num_rows, int row_begin, int row_end,
-                  void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, cudaStream_t stream) {
+                  void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, cudaStream_t stream, int blocks, int32_t* done_counter) {
     TraceScope trace(stream, "quantize", row_begin);
     MOKB_REQUIRE(x_bf16 != nullptr, "mxfp8_quantize: null input");
     MOKB_REQUIRE(E > 0 && M > 0 && N > 0 && M % 128 == 0 && N % 128 == 0, "mxfp8_quantize: M and N must be positive multiples of 128");
@@ -259,12 +334,24 @@ int quantize_impl(const void* x_bf16, int64_t E, int64_t M, int64_t N, const int
     MOKB_REQUIRE(aligned32(x_bf16) && aligned32(x_fp8) && aligned32(x_fp8_t), "mxfp8_quantize: tensors must be 32-byte aligned");
     MOKB_TRY(check_window("mxfp8_quantize", row_begin, &row_end, M));
     if (row_begin == row_end) return MOKB_OK;
-    MOKB_REQUIRE(E <= 65535 && M / 128 <= 65535, "mxfp8_quantize: tensor too large for one launch");
-    const dim3 grid(static_cast<unsigned>(N / 128), static_cast<unsigned>((row_end - row_begin) / 128), static_cast<unsigned>(E));
+    if (x_fp8 == nullptr && E == 1 && done_counter == nullptr) {
+        const int64_t ct = ((row_end - row_begin) / 128) * (N / CTILE_COLS);
+        if (blocks <= 0) blocks = static_cast<int>(ct < 8ll * sm_count() ? ct : 8ll * sm_count());
+        share_sms_with_gemm(quantize_cols_kernel);
+        quantize_cols_kernel<<<static_cast<unsigned>(blocks), 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), M, N,
+                                                                                RowWindow{num_rows, row_begin, row_end},
+                                                                                static_cast<uint8_t*>(x_fp8_t), static_cast<uint8_t*>(x_sc_t));
+        MOKB_CUDA(cudaGetLastError());
+        note_launch();
+        return MOKB_OK;
+    }
+    const int64_t tiles = E * ((row_end - row_begin) / 128) * (N / 128);
+    if (blocks <= 0) blocks = static_cast<int>(tiles < 16ll * sm_count() ? tiles : 16ll * sm_count());
     share_sms_with_gemm(quantize_kernel);
-    quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), M, N, RowWindow{num_rows, row_begin, row_end},
-                                              static_cast<uint8_t*>(x_fp8), static_cast<uint8_t*>(x_sc),
-                                              static_cast<uint8_t*>(x_fp8_t), static_cast<uint8_t*>(x_sc_t));
+    quantize_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), E, M, N,
+                                                                       RowWindow{num_rows, row_begin, row_end},
+                                                                       static_cast<uint8_t*>(x_fp8), static_cast<uint8_t*>(x_sc),
+                                                                       static_cast<uint8_t*>(x_fp8_t), static_cast<uint8_t*>(x_sc_t), done_counter);
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     return MOKB_OK;

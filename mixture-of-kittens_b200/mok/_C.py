@@ -76,7 +76,7 @@ class GemmArgs(ctypes.Structure):
                 ("B3", c_vp), ("D4", c_vp), ("N2", c_int), ("ldb3", c_int), ("ldd4", c_int), ("window_rows", c_int),
                 ("win_ready", c_vp), ("win_ready_target", c_int), ("blk_done", c_vp), ("win_done", c_vp),
                 ("push_ptrs_host", c_u64p), ("push_ep_size", c_int), ("push_rank", c_vp), ("push_idx", c_vp),
-                ("push_values", c_vp), ("push_value_ptrs_host", c_u64p)]
+                ("push_values", c_vp), ("push_value_ptrs_host", c_u64p), ("group_k_end", c_vp)]
 
 
 class GemmFp8Args(ctypes.Structure):
@@ -86,7 +86,10 @@ class GemmFp8Args(ctypes.Structure):
          ("A", c_vp), ("A_sc", c_vp), ("B", c_vp), ("B_sc", c_vp), ("A2", c_vp), ("A2_sc", c_vp), ("B2", c_vp),
          ("B2_sc", c_vp), ("D", c_vp), ("D2", c_vp), ("ldd", c_int), ("t_first", c_int), ("accumulate", c_int)]
         + [(n, c_vp) for n in ("gate_q", "gate_sc", "up_q", "up_sc", "hid_q", "hid_sc", "hid_qt", "hid_sct")]
-        + [("t_rows", c_int), ("has_swiglu_limit", c_int), ("swiglu_limit", c_f32), ("status", c_vp)])
+        + [("t_rows", c_int), ("has_swiglu_limit", c_int), ("swiglu_limit", c_f32), ("status", c_vp)]
+        + [("B3", c_vp), ("B3_sc", c_vp), ("N2", c_int), ("window_rows", c_int), ("win_ready", c_vp), ("win_ready_target", c_int),
+           ("blk_done", c_vp), ("win_done", c_vp), ("push_ptrs_host", c_u64p), ("push_ep_size", c_int), ("push_rank", c_vp),
+           ("push_idx", c_vp), ("push_values", c_vp), ("push_value_ptrs_host", c_u64p)])
 
 
 def _sig(name, restype, *argtypes):
@@ -233,6 +236,22 @@ def raise_for_status(device: torch.device | None = None) -> None:
         raise MokError(f"device status {code}: {STATUS_TEXT.get(code, 'unknown')}")
 
 
+_SCRATCH: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _layer_scratch(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """The layer's work area (tables, counters, per-row router weights): one tensor per (device, stream), grown when a
+    call needs more and otherwise reused -- every call's prologue re-initialises what it reads, and calls on one
+    stream run one after the other (the reference allocates and zeroes its counters per call, csrc/megakernel/
+    forward.cuh:345-368, and marks that as removable)."""
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream())
+    t = _SCRATCH.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        _SCRATCH[key] = t
+    return t
+
+
 def launch_count() -> int:
     return int(lib.mokb_launch_count())
 
@@ -340,8 +359,7 @@ def _common(args, *, x_ptrs, x_like, w_shared_gate, w_routed_gate, schedule_peer
     args.peer_rank, args.peer_token_idx = _p(schedule_peer_rank), _p(schedule_peer_token_idx)
     args.num_tokens, args.tokens_per_expert = _p(num_tokens), _p(tokens_per_expert)
     dev = x_like.device
-    scratch = torch.empty(lib.mokb_layer_scratch_bytes(args.schedule_capacity, E_l, macrobatch_size),
-                          dtype=torch.uint8, device=dev)
+    scratch = _layer_scratch(dev, lib.mokb_layer_scratch_bytes(args.schedule_capacity, E_l, macrobatch_size))
     args.scratch = _p(scratch)
     args.status = _p(status_tensor(dev))
     return T, H, I, E_l, dev, scratch
@@ -453,7 +471,7 @@ def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None
                  M=0, N=0, K=0, A2=None, B2=None, D2=None, D3=None, lda=None, ldb=None, ldd=None, swiglu_limit=None,
                  row_begin=0, row_end=0, accumulate=False, B3=None, D4=None, N2=0, window_rows=0, win_ready=None,
                  win_ready_target=0, blk_done=None, win_done=None, push_ptrs=None, push_rank=None, push_idx=None,
-                 push_values=None, push_value_ptrs=None, N2_ld=None):
+                 push_values=None, push_value_ptrs=None, N2_ld=None, group_k_end=None):
     """Modes 0-3 as in the header; mode 4 = gate/up + SwiGLU (B, B2 -> D, D2, D3) and the down projection
     (D3, B3 -> D4 [rows, N2]) in one launch, with the optional window counters."""
     g = GemmArgs()
@@ -470,6 +488,7 @@ def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None
             g.push_value_ptrs_host = keep[-1]
     g.window_rows, g.win_ready, g.win_ready_target = window_rows, _p(win_ready), win_ready_target
     g.blk_done, g.win_done = _p(blk_done), _p(win_done)
+    g.group_k_end = _p(group_k_end)
     g.mode = mode
     g.accumulate = 1 if accumulate else 0
     g.row_begin, g.row_end = row_begin, row_end
@@ -489,9 +508,23 @@ def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None
 
 def grouped_gemm_mxfp8(mode, A, A_sc, B, B_sc, D, *, rows=None, num_rows=None, group_of_block=None, group_offsets=None,
                        G=1, M=0, N=0, K=0, A2=None, A2_sc=None, B2=None, B2_sc=None, D2=None, ldd=None, row_begin=0, row_end=0,
-                       t_first=0, accumulate=False, quantised_outputs=None, t_rows=0, swiglu_limit=None):
-    """`quantised_outputs` (mode 3): (gate_q, gate_sc, up_q, up_sc, hid_q, hid_sc, hid_qt, hid_sct); D is then unused."""
+                       t_first=0, accumulate=False, quantised_outputs=None, t_rows=0, swiglu_limit=None, B3=None, B3_sc=None,
+                       N2=0, window_rows=0, win_ready=None, win_ready_target=0, blk_done=None, win_done=None, push_ptrs=None,
+                       push_rank=None, push_idx=None, push_values=None, push_value_ptrs=None):
+    """`quantised_outputs` (modes 3, 4): (gate_q, gate_sc, up_q, up_sc, hid_q, hid_sc, hid_qt, hid_sct); D is unused in
+    mode 3 and the down projection's output [rows, N2] in mode 4 (B3, B3_sc: its weights)."""
     g = GemmFp8Args()
+    g.B3, g.B3_sc, g.N2 = _p(B3), _p(B3_sc), N2
+    g.window_rows, g.win_ready, g.win_ready_target = window_rows, _p(win_ready), win_ready_target
+    g.blk_done, g.win_done = _p(blk_done), _p(win_done)
+    keep = []
+    if push_ptrs is not None:
+        keep.append(_ptr_array(push_ptrs))
+        g.push_ptrs_host, g.push_ep_size = keep[-1], len(push_ptrs)
+        g.push_rank, g.push_idx, g.push_values = _p(push_rank), _p(push_idx), _p(push_values)
+        if push_value_ptrs is not None:
+            keep.append(_ptr_array(push_value_ptrs))
+            g.push_value_ptrs_host = keep[-1]
     g.mode = mode
     g.rows_static = (A.shape[0] if mode != 2 else A.shape[1]) if rows is None else rows
     g.row_begin, g.row_end = row_begin, row_end

@@ -104,7 +104,7 @@ def _fwd(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_routed
     (a.x_fp8_t, a.x_sc_t, a.gate_shared, a.up_shared, a.hidden_shared, a.gate_fp8, a.gate_sc, a.up_fp8, a.up_sc,
      a.hidden_fp8_t, a.hidden_sc_t, a.y_shared, a.y_routed) = map(_p, (
         x_fp8_t, x_sc_t, gate_shared, up_shared, hidden_shared, gate_fp8, gate_sc, up_fp8, up_sc, hidden_fp8_t,
-        hidden_sc_t, y_shared, y_routed))
+        hidden_sc_t, y_shared, y_routed if _C.KEEP_STAGING_ROWS else None))      # staging rows: see _C.KEEP_STAGING_ROWS
     (a.x_routed, a.x_fp8, a.x_sc, a.hidden_fp8, a.hidden_sc) = map(_p, work)
     a.skip_down_combine = 1 if skip else 0
     _ck(lib.mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(ctypes.byref(a), _stream()))
@@ -173,9 +173,9 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
     (a.d_x_shared, a.d_x_routed, a.d_gate_shared, a.d_gate_fp8, a.d_gate_sc, a.d_up_shared, a.d_up_fp8, a.d_up_sc,
      a.d_hidden_shared, a.d_hidden_routed, a.d_y_fp8, a.d_y_sc, a.d_w_shared_gate, a.d_w_routed_gate, a.d_w_shared_up,
      a.d_w_routed_up, a.d_w_shared_down, a.d_w_routed_down) = map(_p, (
-        d_x_shared, d_x_routed, d_gate_shared, d_gate_fp8, d_gate_sc, d_up_shared, d_up_fp8, d_up_sc, d_hidden_shared,
-        d_hidden_routed, d_y_fp8, d_y_sc, d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up,
-        d_w_shared_down, d_w_routed_down))
+        d_x_shared, d_x_routed if _C.KEEP_STAGING_ROWS else None, d_gate_shared, d_gate_fp8, d_gate_sc, d_up_shared, d_up_fp8,
+        d_up_sc, d_hidden_shared, d_hidden_routed, d_y_fp8, d_y_sc, d_w_shared_gate, d_w_routed_gate, d_w_shared_up,
+        d_w_routed_up, d_w_shared_down, d_w_routed_down))
     work = [torch.empty(MB, H, **bf), *_q(H, MB, dev), *_q(I, MB, dev), *_q(I, MB, dev),
             torch.empty(MB, I // 128, dtype=torch.float32, device=dev)]
     (a.d_y_routed, a.d_y_fp8_t, a.d_y_sc_t, a.d_gate_fp8_t, a.d_gate_sc_t, a.d_up_fp8_t, a.d_up_sc_t,

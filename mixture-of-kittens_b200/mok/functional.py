@@ -330,8 +330,11 @@ def _stage(buffer: torch.Tensor, value: torch.Tensor) -> None:
     """Copies `value` into the workspace's symmetric `buffer` (reference: mok/functional.py:509-510, 709-711, each
     marked there as removable).  A caller that produced the value in the buffer itself (it passes `workspace.x_buffer`,
     `workspace.d_y_buffer` or `workspace.router_weight_buffer` as the argument) pays no copy."""
-    if value.data_ptr() == buffer.data_ptr() and value.shape == buffer.shape and value.stride() == buffer.stride():
+    if value is buffer:
         return
+    if not torch.compiler.is_compiling() and not isinstance(value, torch._subclasses.FakeTensor):
+        if value.data_ptr() == buffer.data_ptr() and value.shape == buffer.shape and value.stride() == buffer.stride():
+            return
     buffer.copy_(value)
 
 

@@ -145,3 +145,51 @@ def test_mxfp8_gemm_wgrad(cols_per_group, M, N):
             continue
         ref = (Ad[:, s:e] @ Bd[:, s:e].T).to(torch.bfloat16)
         assert_close(f"wgrad {gi}", ref, D[gi], (GEMM_TOL[0] * 8, GEMM_TOL[1]))
+
+
+@pytest.mark.parametrize("rows_per_group,H,I,window,push", [([512, 256, 0, 768], 512, 384, 512, False),
+                                                            ([2048, 512, 3072], 768, 512, 1024, True)])
+def test_mxfp8_fused_forward_equals_the_two_launches_bit_for_bit(rows_per_group, H, I, window, push):
+    """Mode 4 (gate|up + SwiGLU + quantisation tiles and the down tiles of the same rows in one persistent launch, tied
+    by counters) against mode 3 followed by mode 0; with `push`, the down rows go to a (local) peer buffer instead."""
+    from mok import _C
+    offs, gob, rows = groups(rows_per_group)
+    G_ = len(rows_per_group)
+    g = torch.Generator().manual_seed(35)
+    Aq, As, _ = quant(torch.randn(rows, H, generator=g).to(torch.bfloat16))
+    Gq, Gs, _ = quant((torch.randn(G_, I, H, generator=g) * 0.1).to(torch.bfloat16))
+    Uq, Us, _ = quant((torch.randn(G_, I, H, generator=g) * 0.1).to(torch.bfloat16))
+    Dq, Ds, _ = quant((torch.randn(G_, H, I, generator=g) * 0.1).to(torch.bfloat16))
+    u8 = dict(dtype=torch.uint8, device="cuda")
+
+    def outs():
+        sc = lambda r, c: torch.zeros(r // 128, c // 128, 32, 16, **u8)
+        return [torch.zeros(rows, I, **u8), sc(rows, I), torch.zeros(rows, I, **u8), sc(rows, I),
+                torch.zeros(rows, I, **u8), sc(rows, I), torch.zeros(I, rows, **u8), sc(I, rows)]
+    ref = outs()
+    _C.grouped_gemm_mxfp8(3, Aq, As, Gq, Gs, None, group_of_block=gob, G=G_, N=I, K=H, B2=Uq, B2_sc=Us, quantised_outputs=ref, t_rows=rows)
+    y_ref = torch.empty(rows, H, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm_mxfp8(0, ref[4].view(torch.float8_e4m3fn), ref[5], Dq, Ds, y_ref, group_of_block=gob, G=G_, N=H, K=I)
+    got = outs()
+    blk = torch.zeros(rows // 256, dtype=torch.int32, device="cuda")
+    nwin = (rows + window - 1) // window
+    done = torch.zeros(nwin, dtype=torch.int32, device="cuda")
+    y = torch.full((rows, H), 3.0, dtype=torch.bfloat16, device="cuda")
+    extra = {}
+    if push:      # identity routing to one local "peer": row r goes to slot perm[r]
+        perm = torch.randperm(rows, generator=g).to(torch.int32).cuda()
+        home = torch.zeros(rows, H, dtype=torch.bfloat16, device="cuda")
+        extra = dict(push_ptrs=[home.data_ptr()], push_rank=torch.zeros(rows, dtype=torch.int32, device="cuda"), push_idx=perm)
+    _C.grouped_gemm_mxfp8(4, Aq, As, Gq, Gs, None if push else y, group_of_block=gob, G=G_, N=I, K=H, B2=Uq, B2_sc=Us,
+                          quantised_outputs=got, t_rows=rows, B3=Dq, B3_sc=Ds, N2=H, ldd=H, window_rows=window, blk_done=blk,
+                          win_done=done, **extra)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0, _C.status_detail()
+    for a, b in zip(ref, got):
+        assert torch.equal(a, b)
+    if push:
+        assert torch.equal(home[perm.long()], y_ref)
+    else:
+        assert torch.equal(y, y_ref)
+    assert blk.tolist() == [I // 128 * 16] * (rows // 256)
+    assert done.tolist() == [min(window, rows - c * window) // 256 * (H // 256) * 16 for c in range(nwin)]

@@ -346,3 +346,34 @@ def test_gemm_wgrad(mods, rows_per_group, M, N):
         assert_close(f"wgrad group {gi}", ref, D[gi], tol) if e > s else None
         if e == s:
             assert torch.all(D[gi] == 0)
+
+
+def test_gemm_wgrad_leaves_out_the_padding_rows_it_is_told_about(mods):
+    """group_k_end: rows of a group from there on are padding (zero in both operands).  The kernel stops at the next
+    multiple of 64 rows, so whatever lies beyond that -- NaN here -- must not reach the result."""
+    _C, ops = mods
+    rows_per_group, M, N = [512, 768, 0, 256], 256, 384
+    real = [300, 520, 0, 256]
+    offs, gob, rows = _groups(rows_per_group)
+    g = torch.Generator().manual_seed(18)
+    A = torch.randn(rows, M, generator=g).to(torch.bfloat16).cuda()
+    B = torch.randn(rows, N, generator=g).to(torch.bfloat16).cuda()
+    o = offs.cpu().numpy()
+    k_end = torch.tensor([int(o[i]) + real[i] for i in range(4)], dtype=torch.int32, device="cuda")
+    for i in range(4):
+        s, e = int(o[i]) + real[i], int(o[i + 1])
+        A[s:e] = 0
+        B[s:e] = 0
+        s64 = int(o[i]) + (real[i] + 63) // 64 * 64
+        A[s64:e] = float("nan")
+        B[s64:e] = float("nan")
+    D = torch.full((4, M, N), 5.0, dtype=torch.bfloat16, device="cuda")
+    _C.grouped_gemm(3, A, B, D, group_offsets=offs, G=4, M=M, N=N, group_k_end=k_end)
+    assert _C.check_status() == 0
+    for i in range(4):
+        s, e = int(o[i]), int(o[i]) + real[i]
+        if real[i] == 0:
+            assert torch.all(D[i] == 0)
+            continue
+        ref = (A[s:e].float().T @ B[s:e].float()).to(torch.bfloat16)
+        assert_close(f"wgrad group {i}", ref, D[i], (GEMM_TOL[0] * 8, GEMM_TOL[1]))
