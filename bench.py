@@ -690,6 +690,7 @@ def main():
         sched = prob.F.build_schedule(ws, prob.cfg, prob.te_d, num_local_experts=E_l)
         torch.cuda.synchronize()
         kern = time_dominant_kernel(_C, sched, prob.x_d, wrg, wru, T, H, I, K, E_l, MB, args.steps, args.warmup, device, wrd=wrd)
+        kern["wgrad_down"] = time_wgrad_kernel(_C, sched, T, H, I, E_l, MB, args.steps, args.warmup, device)
         if not args.no_mxfp8:
             from mok import ops
             qg, qu = (ops.mxfp8_quantize(w_, True, False) for w_ in (wrg, wru))
@@ -737,7 +738,7 @@ def main():
     if os.path.exists(tpath):
         with open(tpath) as f:
             tj = json.load(f)
-        ratio = tj.get("gate_up_gemm_dram_over_algorithmic_bytes")
+        ratio = tj.get("fwd_routed_gemm_dram_over_algorithmic_bytes")
         if ratio:
             traffic = ratio * model["total"]
             traffic_note = (f"algorithmic bytes of this launch x {ratio} = DRAM bytes / algorithmic bytes that ncu measured "
@@ -990,6 +991,37 @@ def time_dominant_kernel(_C, sched, x, wrg, wru, T, H, I, K, E_l, MB, steps, war
     padded = int(sched.num_tokens.item())
     return {"ms": ms, "flops_per_launch": flops, "tflops": flops / (ms / 1000.0) / 1e12,
             "rows": real_rows, "padded_rows": padded}
+
+
+def time_wgrad_kernel(_C, sched, T, H, I, E_l, MB, steps, warmup, device):
+    """Times one routed weight-gradient launch alone (dW_down[e] = d_y_e^T * hidden_e, mode 3) on this step's schedule,
+    each expert's padding rows left out as in the layer."""
+    tpe = sched.tokens_per_expert.to(torch.int64)
+    offs = torch.cat([torch.zeros(1, dtype=torch.int64, device=device), tpe.cumsum(0)]).to(torch.int32)
+    real = torch.zeros(E_l, dtype=torch.int64, device=device)
+    n = int(sched.num_tokens.item())
+    seg = torch.repeat_interleave(torch.arange(E_l, device=device), tpe)
+    real.index_add_(0, seg, (sched.peer_rank[:n] >= 0).to(torch.int64))
+    k_end = (offs[:-1].to(torch.int64) + real).to(torch.int32)
+    g = torch.Generator(device=device).manual_seed(5)
+    d_y = torch.randn(MB, H, generator=g, device=device).to(torch.bfloat16)
+    hid = torch.randn(MB, I, generator=g, device=device).to(torch.bfloat16)
+    dW = torch.empty(E_l, H, I, dtype=torch.bfloat16, device=device)
+
+    def launch():
+        _C.grouped_gemm(3, d_y, hid, dW, rows=MB, group_offsets=offs, G=E_l, M=H, N=I, group_k_end=k_end)
+    for _ in range(warmup):
+        launch()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        launch()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    flops = 2.0 * float(real.sum().item()) * H * I
+    return {"ms": ms, "flops_per_launch": flops, "tflops": flops / (ms / 1000.0) / 1e12}
 
 
 def time_dominant_kernel_mxfp8(_C, ops, sched, x, qg, qu, T, H, I, E_l, MB, steps, warmup, device):

@@ -100,7 +100,6 @@ struct KParams {
     const int32_t* push_idx;
     const float* push_values;        // optional: push_val[rank][idx] = push_values[r], written with the first column tile
     int32_t* status;
-    int debug;
     int line_stores;                 // the epilogue transposes through shared memory and stores whole 128-byte lines
     PeerPtrs push_dst, push_val;
 };
@@ -322,11 +321,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         waited_window = ti.window;
                         fenced = true;
                     }
-                    if (MODE == MODE_FWD && ti.phase == 1 && !(p.debug & 2)) {
+                    if (MODE == MODE_FWD && ti.phase == 1) {
                         if (!flag_wait(p.blk_done + (ti.m_blk - sched.m_first), sched.n_gu * 4 * NCTA, abort_flag, p.status, kWaitBlockDone, ti.m_blk - sched.m_first)) { ok = false; break; }
                         fenced = true;
                     }
-                    if (fenced && !(p.debug & 1)) fence_proxy_async_global();
+                    if (fenced) fence_proxy_async_global();
                 }
                 for (int it = 0; it < ti.k_iters; ++it) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, MOKB_ST_PIPELINE_TIMEOUT)) { ok = false; break; }
@@ -701,7 +700,6 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
     p.limit = g->swiglu_limit;
     p.status = g->status;
     p.dual = 0;
-    { const char* e = getenv("MOKB_DEBUG"); p.debug = e ? atoi(e) : 0; }
     { const char* e = getenv("MOKB_LINE_STORES"); p.line_stores = e ? atoi(e) : 1; }
     if (g->push_ptrs_host) {
         MOKB_REQUIRE(g->mode == MODE_NT || g->mode == MODE_NN || g->mode == MODE_FWD, "grouped_gemm: push is for modes 0, 2 and 4");
