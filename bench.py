@@ -497,17 +497,14 @@ def in_step_summary(recs, prefix, prob, real_rows, peak_tf):
     out = {"step_ms_traced": span, "gemm_launches": len(gemm), "gemm_busy_ms": busy,
            "gemm_tflops": prob.flops() / (busy / 1000.0) / 1e12,
            "note": "algorithmic FLOPs (padding and replay not counted) over the GEMM launch intervals of one traced step"}
+    # the routed forward is one persistent launch: gate/up + SwiGLU and the down projection of every window
+    fr_ms = sum(r[4] - r[3] for r in gemm if r[0] == prefix + "_fwd_routed")
+    out["fwd_routed_ms"] = fr_ms
+    out["fwd_routed_tflops"] = 6.0 * real_rows * prob.H * prob.I / (fr_ms / 1000.0) / 1e12 if fr_ms > 0 else None
     if prefix == "gemm_bf16":
-        # the routed forward is one persistent launch: gate/up + SwiGLU and the down projection of every window
-        fr_ms = sum(r[4] - r[3] for r in gemm if r[0] == "gemm_bf16_fwd_routed")
-        out["fwd_routed_ms"] = fr_ms
-        out["fwd_routed_tflops"] = 6.0 * real_rows * prob.H * prob.I / (fr_ms / 1000.0) / 1e12 if fr_ms > 0 else None
         out["gemm_frac_of_burst"] = out["gemm_tflops"] / peak_tf
         out["fwd_routed_frac_of_burst"] = out["fwd_routed_tflops"] / peak_tf if out["fwd_routed_tflops"] else None
     else:
-        gu_ms = sum(r[4] - r[3] for r in gemm if "gate_up" in r[0])
-        out["gate_up_ms"] = gu_ms
-        out["gate_up_tflops"] = 4.0 * real_rows * prob.H * prob.I / (gu_ms / 1000.0) / 1e12 if gu_ms > 0 else None
         out["note"] += "; the BF16 shared expert's GEMMs are not in gemm_busy_ms, its FLOPs (1/(K+1) of the layer) are"
     return out
 

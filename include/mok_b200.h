@@ -404,6 +404,9 @@ typedef struct {
     const int32_t* push_idx;
     const float* push_values;
     const uint64_t* push_value_ptrs_host;
+    /* A launch with win_ready leaves this many SMs (0 = 2) to the kernels that produce the rows it waits for (the
+     * reference sets whole SMs aside for communication: num_comm_sms).  The layer uses 2. */
+    int reserve_sms;
 } mokb_gemm_fp8_args;
 int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* args, void* stream);
 

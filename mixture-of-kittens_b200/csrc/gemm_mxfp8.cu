@@ -51,7 +51,8 @@ constexpr int TMEM_COLS = 512;
 constexpr int SF_COL0 = 256;                       // scale columns start after the accumulator
 constexpr int SF_SET_COLS = 16;                    // SFA 4 + SFB 8, padded
 constexpr int GROUP_M = 4;
-constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * (DATA_BYTES + SF_BYTES) + 1024 + 256;
+// + one 2 KB transposition buffer per epilogue warp (32 rows x 64 bytes) for rows that are pushed to a peer
+constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * (DATA_BYTES + SF_BYTES) + 1024 + 256 + 8 * 2048;
 
 enum { FMODE_NT = 0, FMODE_DUALB = 1, FMODE_WGRAD = 2, FMODE_GATEUP_QUANT = 3, FMODE_FWD = 4 };
 template <int MODE> constexpr bool kGateUp = MODE == FMODE_DUALB || MODE == FMODE_GATEUP_QUANT;
@@ -82,6 +83,7 @@ struct FParams {
     int N2, K2, b3_rows_per_group, a2_ktiles, b3_ktiles;     // down: N2 columns, contraction K2 = N
     int32_t* blk_done;
     int32_t* win_done;
+    int reserve_pairs;               // SM pairs a waiting launch leaves to the kernels it waits for
     // push (FMODE_NT and the down tiles of FMODE_FWD): row r goes to row push_idx[r] of rank push_rank[r]'s buffer
     int push, push_ranks, push_wide;
     const int32_t* push_rank;
@@ -537,16 +539,31 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
                             st_global_v4(dst + 8 * q, packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                 }
             }
-            if (pdst) {
-                if (p.push_wide) {
+            if ((MODE == FMODE_NT || MODE == FMODE_FWD) && p.push) {
+                // Rows that go to a peer cross NVLink: 32 rows x 32 columns at a time are transposed through shared memory
+                // so that four lanes store 64 contiguous bytes of a row (two stores fill a 128-byte line) instead of every
+                // lane storing 32 bytes of a row of its own.  Whole warp; rows without a home have a null pointer.
+                const uint32_t stage = bars + 256u + static_cast<uint32_t>(warp - 2) * 2048u;
+                const unsigned long long own_home = reinterpret_cast<unsigned long long>(pdst);
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        if (q * 16 < cols_left) st_global_v8(pdst + 16 * q, &packed[8 * q]);
-                } else {
+                for (int st = 0; st < 4; ++st) {
+                    if (st * 32 >= cols_left) break;
+                    __syncwarp();             // the previous piece has been read out of the buffer
 #pragma unroll
-                    for (int q = 0; q < 16; ++q)
-                        if (q * 8 < cols_left)
-                            st_global_v4(pdst + 8 * q, packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                    for (int u = 0; u < 4; ++u)      // row `lane`, 16-byte unit u at u ^ ((lane >> 1) & 3): conflict-free both ways
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 64u + static_cast<uint32_t>((u ^ ((lane >> 1) & 3)) << 4)),
+                                     "r"(packed[16 * st + 4 * u]), "r"(packed[16 * st + 4 * u + 1]), "r"(packed[16 * st + 4 * u + 2]),
+                                     "r"(packed[16 * st + 4 * u + 3]) : "memory");
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int rr = 8 * i + (lane >> 2), unit = lane & 3;
+                        uint32_t v0, v1, v2, v3;
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                                     : "r"(stage + rr * 64u + static_cast<uint32_t>((unit ^ ((rr >> 1) & 3)) << 4)) : "memory");
+                        __nv_bfloat16* home = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, own_home, rr));
+                        if (home) st_global_v4(home + st * 32 + unit * 8, v0, v1, v2, v3);
+                    }
                 }
             }
             if (MODE == FMODE_FWD && p.win_done) {
@@ -576,7 +593,7 @@ int launch(const Maps& m, const FParams& p, int tiles_upper_bound, cudaStream_t 
     MOKB_CUDA(cudaFuncSetAttribute(grouped_gemm_mxfp8_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     int pairs = sm_count() / 2;
     // a launch that waits for another kernel's rows leaves one pair of SMs to that kernel (see gemm.cu)
-    if (p.win_ready && pairs > 2) pairs -= 1;
+    if (p.win_ready) pairs -= p.reserve_pairs < pairs - 1 ? p.reserve_pairs : pairs - 1;
     if (tiles_upper_bound < pairs) pairs = tiles_upper_bound;
     if (pairs < 1) return MOKB_OK;
     cudaLaunchConfig_t cfg = {};
@@ -659,6 +676,8 @@ extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream
         p.window_rows = g->window_rows;
         p.win_ready = g->win_ready;
         p.win_ready_target = g->win_ready_target;
+        MOKB_REQUIRE(g->reserve_sms >= 0, "grouped_gemm_mxfp8: reserve_sms must not be negative");
+        p.reserve_pairs = g->reserve_sms > 0 ? (g->reserve_sms + 1) / 2 : 1;
     }
     Maps m;
     memset(&m, 0, sizeof(m));

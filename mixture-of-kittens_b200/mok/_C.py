@@ -89,7 +89,7 @@ class GemmFp8Args(ctypes.Structure):
         + [("t_rows", c_int), ("has_swiglu_limit", c_int), ("swiglu_limit", c_f32), ("status", c_vp)]
         + [("B3", c_vp), ("B3_sc", c_vp), ("N2", c_int), ("window_rows", c_int), ("win_ready", c_vp), ("win_ready_target", c_int),
            ("blk_done", c_vp), ("win_done", c_vp), ("push_ptrs_host", c_u64p), ("push_ep_size", c_int), ("push_rank", c_vp),
-           ("push_idx", c_vp), ("push_values", c_vp), ("push_value_ptrs_host", c_u64p)])
+           ("push_idx", c_vp), ("push_values", c_vp), ("push_value_ptrs_host", c_u64p), ("reserve_sms", c_int)])
 
 
 def _sig(name, restype, *argtypes):
@@ -510,11 +510,12 @@ def grouped_gemm_mxfp8(mode, A, A_sc, B, B_sc, D, *, rows=None, num_rows=None, g
                        G=1, M=0, N=0, K=0, A2=None, A2_sc=None, B2=None, B2_sc=None, D2=None, ldd=None, row_begin=0, row_end=0,
                        t_first=0, accumulate=False, quantised_outputs=None, t_rows=0, swiglu_limit=None, B3=None, B3_sc=None,
                        N2=0, window_rows=0, win_ready=None, win_ready_target=0, blk_done=None, win_done=None, push_ptrs=None,
-                       push_rank=None, push_idx=None, push_values=None, push_value_ptrs=None):
+                       push_rank=None, push_idx=None, push_values=None, push_value_ptrs=None, reserve_sms=0):
     """`quantised_outputs` (modes 3, 4): (gate_q, gate_sc, up_q, up_sc, hid_q, hid_sc, hid_qt, hid_sct); D is unused in
     mode 3 and the down projection's output [rows, N2] in mode 4 (B3, B3_sc: its weights)."""
     g = GemmFp8Args()
     g.B3, g.B3_sc, g.N2 = _p(B3), _p(B3_sc), N2
+    g.reserve_sms = reserve_sms
     g.window_rows, g.win_ready, g.win_ready_target = window_rows, _p(win_ready), win_ready_target
     g.blk_done, g.win_done = _p(blk_done), _p(win_done)
     keep = []
