@@ -530,10 +530,16 @@ def fwd_routed_bytes(prob, padded_rows, experts_used):
 
 
 def comm_alone(prob, sched, timed, _C, rank):
-    """Dispatch (row pull) and combine (row push) kernels alone over all scheduled rows, every rank at once."""
-    remote = int(((sched.peer_rank >= 0) & (sched.peer_rank != rank)).sum().item())
+    """Dispatch (row pull) and combine (row push) kernels alone over the first macrobatch's rows, every rank at once.  The rate is
+    the remote rows of the busiest rank (its inbound bytes when pulling, outbound when pushing) over the slowest rank's time."""
+    # entries past num_tokens are not written by the schedule; the kernels below move the first macrobatch
+    live = sched.peer_rank[: min(int(sched.num_tokens.item()), prob.MB)]
+    whole = sched.peer_rank[: int(sched.num_tokens.item())]
+    remote_t = torch.stack([((live >= 0) & (live != rank)).sum(), ((whole >= 0) & (whole != rank)).sum()]).to(torch.int64)
+    dist.all_reduce(remote_t, op=dist.ReduceOp.MAX)              # the busiest rank: the time below is the slowest rank's
+    remote, remote_step = (int(v) for v in remote_t.tolist())
     buf = torch.empty(prob.MB, prob.H, dtype=torch.bfloat16, device=prob.device)
-    ws, out = prob.ws, {"remote_rows": remote}
+    ws, out = prob.ws, {"remote_rows": remote, "remote_rows_step": remote_step}
     for name, fn in (
         ("dispatch", lambda: _C.dispatch_rows(ws.x_buffer_ptrs, sched.peer_rank, sched.peer_token_idx, sched.num_tokens,
                                               prob.MB, prob.K, prob.H, buf)),
@@ -584,7 +590,7 @@ def run_sweep(args, rank, world, device, group, timed, _C):
         if world > 1:
             comm = comm_alone(prob, sched, timed, _C, rank)
             # bytes that cross NVLink in one step (forward pull + push, backward pull + push) over the step time
-            step_bytes = 4.0 * comm["remote_rows"] * prob.H * 2
+            step_bytes = 4.0 * comm["remote_rows_step"] * prob.H * 2
             comm["in_step_gbs_bf16"] = step_bytes / (cell["bf16"]["ms_per_step"] / 1000.0) / 1e9
             cell["comm"] = comm
         prob.q = None
@@ -755,7 +761,7 @@ def main():
     if world > 1:
         comm = {"rows": padded_rows, "nvlink_peak_gbs_per_direction": 900.0, "measured_peer_copy_gbs": 770.0,
                 **comm_alone(prob, sched, timed, _C, rank)}
-        comm["in_step_gbs_bf16"] = 4.0 * comm["remote_rows"] * H * 2 / (ms_per_step / 1000.0) / 1e9
+        comm["in_step_gbs_bf16"] = 4.0 * comm["remote_rows_step"] * H * 2 / (ms_per_step / 1000.0) / 1e9
 
     # ---- the same step with the routed experts in MXFP8 (weights pre-quantised outside the step, as the reference does)
     mx = None

@@ -433,6 +433,9 @@ int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
  *   done_counter  -- optional; every block of the dispatch launch adds 1 once its rows have landed.  A GEMM given this
  *                    word as win_ready[w] with win_ready_target = the launch's block count (`blocks`, or
  *                    mokb_comm_default_blocks() when blocks is 0) starts window w only then.
+ *   q_out, q_sc_out -- optional, together (hidden % 128 == 0, 32-byte aligned rows): the pulled (and scaled) rows also in
+ *                    MXFP8, E4M3 [max_rows, hidden] + packed scales, quantised along the columns from the registers
+ *                    they pass through (dispatch_combine.cuh:88-114); byte for byte what mokb_mxfp8_quantize gives.
  *   wait_counter  -- optional; the combine launch first waits (2 s at most, then MOKB_ST_FLAG_TIMEOUT in `status` and
  *                    no row is copied) until it holds ((rows of the window) / 256) * arrivals_per_row_block arrivals:
  *                    win_done[w] of a mode-4 GEMM with arrivals_per_row_block = (N2 / 256) * 8.  row_begin must be a
@@ -442,7 +445,7 @@ int mokb_dispatch_rows_window(const uint64_t* src_ptrs_host, int ep_size, const 
                               const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin,
                               int row_end, int row_divisor, int64_t hidden, void* dst,
                               const uint64_t* row_scale_ptrs_host, float* row_scale_out, int blocks,
-                              int32_t* done_counter, void* stream);
+                              int32_t* done_counter, void* q_out, void* q_sc_out, void* stream);
 int mokb_combine_rows_window(const void* src, const uint64_t* dst_ptrs_host, int ep_size,
                              const int32_t* peer_rank, const int32_t* peer_token_idx,
                              const int32_t* num_rows, int max_rows, int row_begin, int row_end, int64_t hidden,

@@ -99,7 +99,7 @@ struct RowQuant {
 // values, two neighbouring lanes one 32-value block (the reference quantises the tile it has just pulled,
 // csrc/megakernel/dispatch_combine.cuh:88-114; the values are those of quantize_kernel, byte for byte).
 template <bool SCALE, int W, bool QUANT>
-__global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t* __restrict__ peer_rank,
+__global__ void __maxnreg__(64) dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t* __restrict__ peer_rank,
                                 const int32_t* __restrict__ peer_token_idx, const int32_t* __restrict__ num_rows,
                                 int max_rows, int row_begin, int row_end, int R, int row_divisor, int vec_per_row,
                                 Words<W>* __restrict__ dst, float* __restrict__ row_scale_out, int32_t* done_counter, RowQuant rq) {
@@ -110,8 +110,25 @@ __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t*
     const int warps_per_block = blockDim.x >> 5;
     const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int nwarps = gridDim.x * warps_per_block;
-    for (int row = row_begin + warp; row < rows; row += nwarps) {
-        const int pr = peer_rank[row];
+    // The indices (and the remote scale) of a warp's next row are fetched while it moves the current one: three
+    // dependent round trips (indices, scale over NVLink, data over NVLink) would otherwise sit in front of every row.
+    int row = row_begin + warp;
+    int pr_next = -1, tok_next = 0;
+    float w_next = 1.f;
+    auto fetch_indices = [&](int r) {
+        pr_next = -1;
+        if (r < rows) {
+            pr_next = peer_rank[r];
+            tok_next = peer_token_idx[r];
+            if (SCALE && pr_next >= 0 && pr_next < R) w_next = static_cast<const float*>(scale_src.p[pr_next])[tok_next];
+        }
+    };
+    fetch_indices(row);
+    for (; row < rows; row += nwarps) {
+        const int pr = pr_next;
+        const int tok = tok_next;
+        const float w = SCALE ? w_next : 1.f;
+        fetch_indices(row + nwarps);
         Words<W>* out = dst + static_cast<size_t>(row) * vec_per_row;
         if (pr < 0 || pr >= R) {      // padding row (or a rank outside the pointer list: treated as padding, never dereferenced)
             Words<W> zero;
@@ -129,13 +146,8 @@ __global__ void dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t*
             }
             continue;
         }
-        const int tok = peer_token_idx[row];
         const Words<W>* in = static_cast<const Words<W>*>(src.p[pr]) + static_cast<size_t>(tok / row_divisor) * vec_per_row;
-        float w = 1.f;
-        if (SCALE) {
-            w = static_cast<const float*>(scale_src.p[pr])[tok];
-            if (lane == 0 && row_scale_out) row_scale_out[row] = w;
-        }
+        if (SCALE && lane == 0 && row_scale_out) row_scale_out[row] = w;
         // (every lane makes the same number of trips: the quantising variant shuffles between lanes inside)
         for (int vb = 0; vb < vec_per_row; vb += 128) {
             const int v0 = vb + lane;
@@ -410,10 +422,10 @@ extern "C" int mokb_dispatch_rows_window(const uint64_t* src_ptrs_host, int ep_s
                                          const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin,
                                          int row_end, int row_divisor, int64_t hidden, void* dst,
                                          const uint64_t* row_scale_ptrs_host, float* row_scale_out, int blocks,
-                                         int32_t* done_counter, void* stream) {
+                                         int32_t* done_counter, void* q_out, void* q_sc_out, void* stream) {
     return dispatch_rows_impl(src_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, row_divisor,
                               hidden, dst, row_scale_ptrs_host, row_scale_out, blocks, static_cast<cudaStream_t>(stream), done_counter,
-                              nullptr, nullptr);
+                              q_out, q_sc_out);
 }
 
 extern "C" int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_size,

@@ -124,7 +124,7 @@ _sig("mokb_dispatch_rows", c_int, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int,
 _sig("mokb_combine_rows", c_int, c_vp, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_vp, c_u64p, c_vp)
 _sig("mokb_comm_default_blocks", c_int)
 _sig("mokb_dispatch_rows_window", c_int, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_i64, c_vp, c_u64p, c_vp, c_int,
-     c_vp, c_vp)
+     c_vp, c_vp, c_vp, c_vp)
 _sig("mokb_combine_rows_window", c_int, c_vp, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_i64, c_vp, c_u64p, c_int, c_vp,
      c_int, c_vp, c_vp)
 _sig("mokb_swiglu_fwd", c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_f32, c_vp)
@@ -564,11 +564,11 @@ def comm_default_blocks() -> int:
 
 
 def dispatch_rows_window(src_ptrs, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, row_divisor, hidden, dst,
-                         row_scale_ptrs=None, row_scale_out=None, blocks=0, done_counter=None):
+                         row_scale_ptrs=None, row_scale_out=None, blocks=0, done_counter=None, q_out=None, q_sc_out=None):
     _ck(lib.mokb_dispatch_rows_window(_ptr_array(src_ptrs), len(src_ptrs), _p(peer_rank), _p(peer_token_idx), _p(num_rows),
                                       max_rows, row_begin, row_end, row_divisor, hidden, _p(dst),
                                       None if row_scale_ptrs is None else _ptr_array(row_scale_ptrs), _p(row_scale_out),
-                                      blocks, _p(done_counter), _stream()))
+                                      blocks, _p(done_counter), _p(q_out), _p(q_sc_out), _stream()))
 
 
 def combine_rows_window(src, dst_ptrs, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, hidden,

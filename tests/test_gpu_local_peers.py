@@ -143,3 +143,43 @@ def test_gemm_epilogue_pushes_rows_to_local_peers_like_a_combine_launch(R, T, K,
         assert torch.equal(got_dx[r], want_dx[r]) and torch.equal(got_val[r], want_val[r]), f"mode 2: rank {r}'s buffers differ"
         assert torch.equal(got4[r], want4[r]), f"mode 4: rank {r}'s buffer differs"
     assert torch.equal(dx2[:N], dx[:N]) and torch.all(dx2[N:] == 3.0)
+
+
+@pytest.mark.parametrize("R,T,K,H,scaled", [(2, 512, 2, 256, False), (4, 512, 4, 512, True), (2, 512, 2, 7168, True)])
+def test_dispatch_quantises_the_rows_it_pulls_like_the_quantiser(R, T, K, H, scaled):
+    """The pull's row-wise MXFP8 output (from the registers the row passes through) against the quantiser kernel run
+    on the pulled bf16 rows: bytes and scales identical, padding rows included; hidden 256 is the case where only half
+    of a warp's lanes hold data."""
+    from mok import _C, ops
+    E_l = 2
+    routes = make_routes(R, T, K, E_l, seed=90 + R)
+    g = torch.Generator().manual_seed(91)
+    x = [(torch.randn(T, H, generator=g) * torch.exp(torch.randn(T, 1, generator=g) * 2)).to(torch.bfloat16).cuda() for _ in range(R)]
+    w = [torch.rand(T, K, generator=g).cuda() for _ in range(R)]
+    C = T * K * R
+    pr, pt, nt, tpe = O.schedule(routes, E_l, C, R - 1)
+    N = int(nt[0])
+    prd, ptd, ntd = (torch.from_numpy(a).cuda() for a in (pr, pt, nt))
+    out = torch.zeros(C, H, dtype=torch.bfloat16, device="cuda")
+    q = torch.zeros(C, H, dtype=torch.uint8, device="cuda")
+    sc = torch.zeros(C // 128, H // 128, 32, 16, dtype=torch.uint8, device="cuda")
+    wrow = torch.empty(C, device="cuda") if scaled else None
+    _C.dispatch_rows_window([t.data_ptr() for t in x], prd, ptd, ntd, C, 0, C, K, H, out,
+                            [t.data_ptr() for t in w] if scaled else None, wrow, blocks=32, q_out=q, q_sc_out=sc)
+    torch.cuda.synchronize()
+    live = (N + 127) // 128 * 128
+    ref_q, ref_s, _, _ = ops.mxfp8_quantize(out[:live].contiguous(), True, False)
+    assert torch.equal(q[:N], ref_q.view(torch.uint8)[:N])
+    assert torch.equal(O.unpack_scales(sc.cpu())[:N], O.unpack_scales(ref_s.cpu())[:N])
+    assert int((torch.from_numpy(pr[:N]) < 0).sum()) > 0          # the case has padding rows
+
+
+def test_transposed_only_quantiser_matches_the_two_way_quantiser():
+    from mok import ops
+    g = torch.Generator().manual_seed(92)
+    x = (torch.randn(384, 640, generator=g) * torch.exp(torch.randn(384, 1, generator=g) * 3)).to(torch.bfloat16).cuda()
+    x[5] = 0
+    _, _, qt, st = ops.mxfp8_quantize(x, True, True)
+    n1, n2, qt2, st2 = ops.mxfp8_quantize(x, False, True)       # the column-only kernel (128 x 64 tiles)
+    assert n1 is None and n2 is None
+    assert torch.equal(qt.view(torch.uint8), qt2.view(torch.uint8)) and torch.equal(st, st2)
