@@ -186,7 +186,14 @@ def _ck(rc: int) -> None:
         raise MokError(f"mok_b200 error {rc}: {_last_error().decode(errors='replace')}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle (the raw getter when this torch has it: building a Stream object costs several
+    microseconds, and every launcher call asks)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

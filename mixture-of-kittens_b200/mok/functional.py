@@ -238,7 +238,8 @@ def clear_workspace_cache() -> None:
 
 
 def _barrier(ws: MoKWorkspace) -> None:
-    ops.barrier_all(ws.barrier_buffer, ws.barrier_buffer_ptrs, ws.barrier_buffer_multicast_ptr, ws.barrier_target)
+    ops.call(ops.barrier_all, ws.barrier_buffer, ws.barrier_buffer_ptrs, ws.barrier_buffer_multicast_ptr,
+             ws.barrier_target)
 
 
 def validate_config(config: MoKConfig, num_sms: int, route_buffer_bytes: int, smem_optin: int = 232448) -> None:
@@ -287,13 +288,14 @@ def build_schedule(workspace: MoKWorkspace, config: MoKConfig, top_experts: torc
     if type(num_local_experts) is not int or num_local_experts <= 0:
         raise ValueError("num_local_experts must be a positive integer")
 
-    ops.all_gather_top_experts(
-        top_experts.to(torch.int32), workspace.all_gather_top_experts_buffer,
+    ops.call(
+        ops.all_gather_top_experts, top_experts.to(torch.int32), workspace.all_gather_top_experts_buffer,
         workspace.all_gather_top_experts_buffer_multicast_ptr, workspace.ep_rank,
         config.all_gather_top_experts_chunk_bytes, workspace.all_gather_top_experts_buffer_ptrs)
     _barrier(workspace)
-    peer_rank, peer_token_idx, num_tokens, tokens_per_expert = ops.schedule(
-        workspace.all_gather_top_experts_buffer, num_local_experts, workspace.schedule_capacity, workspace.ep_rank)
+    peer_rank, peer_token_idx, num_tokens, tokens_per_expert = ops.call(
+        ops.schedule, workspace.all_gather_top_experts_buffer, num_local_experts, workspace.schedule_capacity,
+        workspace.ep_rank)
     return MoKSchedule(peer_rank=peer_rank, peer_token_idx=peer_token_idx, num_tokens=num_tokens,
                        tokens_per_expert=tokens_per_expert)
 
@@ -353,7 +355,8 @@ def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x
         from . import ops_mxfp8
         (gq, gs), (uq, us), (dq, ds) = routed_gate_weights, routed_up_weights, routed_down_weights
         (x_fp8_t, x_sc_t, gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc, hidden_shared, hidden_fp8_t,
-         hidden_sc_t, y_shared, _y_routed) = ops_mxfp8.dispatch_mlp_swiglu_combine_fwd_mxfp8(
+         hidden_sc_t, y_shared, _y_routed) = ops.call(
+            ops_mxfp8.dispatch_mlp_swiglu_combine_fwd_mxfp8,
             ws.x_buffer, ws.x_buffer_ptrs, ws.combine_buffer, ws.combine_buffer_ptrs,
             shared_gate_weights, gq, gs, shared_up_weights, uq, us, shared_down_weights, dq, ds,
             schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens, schedule.tokens_per_expert,
@@ -363,7 +366,8 @@ def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x
                                 hidden_routed=(hidden_fp8_t, hidden_sc_t))
     else:
         (x_routed, gate_shared, gate_routed, up_shared, up_routed, hidden_shared, hidden_routed, y_shared,
-         _y_routed) = ops.dispatch_mlp_swiglu_combine_fwd_bf16(
+         _y_routed) = ops.call(
+            ops.dispatch_mlp_swiglu_combine_fwd_bf16,
             ws.x_buffer, ws.x_buffer_ptrs, ws.combine_buffer, ws.combine_buffer_ptrs,
             shared_gate_weights, routed_gate_weights, shared_up_weights, routed_up_weights,
             shared_down_weights, routed_down_weights,
@@ -373,7 +377,7 @@ def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x
                                 up_shared=up_shared, up_routed=up_routed, hidden_shared=hidden_shared,
                                 hidden_routed=hidden_routed)
     _barrier(ws)
-    output = ops.fwd_epilogue(y_shared, ws.combine_buffer, ws.router_weight_buffer)
+    output = ops.call(ops.fwd_epilogue, y_shared, ws.combine_buffer, ws.router_weight_buffer)
     return output, ctx
 
 
@@ -394,7 +398,8 @@ def recompute_forward_context(config: MoKConfig, workspace: MoKWorkspace, schedu
         from . import ops_mxfp8
         (gq, gs), (uq, us) = routed_gate_weights, routed_up_weights
         (x_fp8_t, x_sc_t, gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc, hidden_shared, hidden_fp8_t,
-         hidden_sc_t) = ops_mxfp8.recompute_forward_context_mxfp8(
+         hidden_sc_t) = ops.call(
+            ops_mxfp8.recompute_forward_context_mxfp8,
             ws.x_buffer, ws.x_buffer_ptrs, shared_gate_weights, gq, gs, shared_up_weights, uq, us,
             schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens, schedule.tokens_per_expert,
             ws.topk, swiglu_limit, config.fwd_num_comm_sms, config.macrobatch_size, config.minibatch_size)
@@ -403,7 +408,8 @@ def recompute_forward_context(config: MoKConfig, workspace: MoKWorkspace, schedu
                                 hidden_routed=(hidden_fp8_t, hidden_sc_t))
     else:
         (x_routed, gate_shared, gate_routed, up_shared, up_routed, hidden_shared,
-         hidden_routed) = ops.recompute_forward_context_bf16(
+         hidden_routed) = ops.call(
+            ops.recompute_forward_context_bf16,
             ws.x_buffer, ws.x_buffer_ptrs, shared_gate_weights, routed_gate_weights, shared_up_weights,
             routed_up_weights, schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens,
             schedule.tokens_per_expert, ws.topk, swiglu_limit, config.fwd_num_comm_sms, config.macrobatch_size,
@@ -436,7 +442,8 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
         gq, gs, gtq, gts = routed_gate_weights
         uq, us, utq, uts = routed_up_weights
         dtq, dts = routed_down_weights
-        outs = ops_mxfp8.dispatch_mlp_swiglu_combine_bwd_mxfp8(
+        outs = ops.call(
+            ops_mxfp8.dispatch_mlp_swiglu_combine_bwd_mxfp8,
             ws.d_y_buffer, ws.d_y_buffer_ptrs, ws.d_x_routed_buffer, ws.d_x_routed_buffer_ptrs,
             ws.router_weight_buffer, ws.router_weight_buffer_ptrs, ws.d_router_weight_buffer,
             ws.d_router_weight_buffer_ptrs,
@@ -449,7 +456,8 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
         d_x_shared = outs[0]
         d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up, d_w_shared_down, d_w_routed_down = outs[-6:]
     else:
-        outs = ops.dispatch_mlp_swiglu_combine_bwd_bf16(
+        outs = ops.call(
+            ops.dispatch_mlp_swiglu_combine_bwd_bf16,
             ws.d_y_buffer, ws.d_y_buffer_ptrs, ws.d_x_routed_buffer, ws.d_x_routed_buffer_ptrs,
             ws.router_weight_buffer, ws.router_weight_buffer_ptrs, ws.d_router_weight_buffer,
             ws.d_router_weight_buffer_ptrs,
@@ -462,7 +470,7 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
         d_x_shared = outs[0]
         d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up, d_w_shared_down, d_w_routed_down = outs[-6:]
     _barrier(ws)
-    d_x = ops.bwd_epilogue(d_x_shared, ws.d_x_routed_buffer)
+    d_x = ops.call(ops.bwd_epilogue, d_x_shared, ws.d_x_routed_buffer)
     d_router_weights = ws.d_router_weight_buffer.clone()
     return (d_x, d_router_weights, d_w_routed_gate, d_w_routed_up, d_w_routed_down,
             d_w_shared_gate, d_w_shared_up, d_w_shared_down)

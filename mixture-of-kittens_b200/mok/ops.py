@@ -12,12 +12,54 @@ Differences a caller can see:
   * a schedule that does not fit sets a device status word (mok._C.check_status)
     instead of trapping the GPU.
 """
+import inspect
+
 import torch
 
 from . import _C
 from . import _fake_impls
 
 MAX_EP = 64
+
+# operator -> (its Python body, positions of the arguments it mutates): what `call` needs to run it without the dispatcher
+_EAGER: dict = {}
+
+
+def _op(name: str, *, mutates_args=(), **kw):
+    """`torch.library.custom_op` that also remembers the operator's body for `call`."""
+    def deco(fn):
+        op = torch.library.custom_op(name, mutates_args=mutates_args, **kw)(fn)
+        params = list(inspect.signature(fn).parameters)
+        _EAGER[op] = (fn, tuple(params.index(m) for m in mutates_args))
+        return op
+    return deco
+
+
+def _plain_eager(args) -> bool:
+    if torch.compiler.is_compiling() or torch._C._len_torch_dispatch_stack() or torch._C._len_torch_function_stack():
+        return False
+    if torch._C._functorch.peek_interpreter_stack() is not None:
+        return False
+    for a in args:
+        if isinstance(a, torch.Tensor) and (type(a) is not torch.Tensor or a.requires_grad):
+            return False
+    return True
+
+
+def call(op, *args):
+    """How `mok.functional` invokes an operator.  Under `torch.compile`, a dispatch or function mode (FakeTensorMode,
+    make_fx, ...), a functorch transform, or with tensor subclasses / tensors that require grad, this is `op(*args)`.
+    In plain eager mode the operator's body runs directly and the version counters of the arguments it mutates are
+    bumped as the dispatcher would do: one dispatcher round trip costs about as much host time as launching ten small
+    kernels, and a layer step makes eleven of them."""
+    if not _plain_eager(args):
+        return op(*args)
+    fn, mutated = _EAGER[op]
+    out = fn(*args)
+    for i in mutated:
+        if i < len(args) and args[i] is not None:
+            torch.autograd.graph.increment_version(args[i])
+    return out
 
 
 def _is_pos_int(v) -> bool:
@@ -91,7 +133,7 @@ def _check_shapes_devices(device, table) -> None:
             raise ValueError(f"{name} must be on {device}")
 
 
-@torch.library.custom_op("mok::all_gather_top_experts", mutates_args=("all_gather_top_experts_buffer",))
+@_op("mok::all_gather_top_experts", mutates_args=("all_gather_top_experts_buffer",))
 def all_gather_top_experts(
     top_experts: torch.Tensor,
     all_gather_top_experts_buffer: torch.Tensor,
@@ -142,7 +184,7 @@ def all_gather_top_experts(
                               all_gather_top_experts_buffer_ptrs)
 
 
-@torch.library.custom_op("mok::barrier_all", mutates_args=("barrier_buffer", "target"))
+@_op("mok::barrier_all", mutates_args=("barrier_buffer", "target"))
 def barrier_all(
     barrier_buffer: torch.Tensor,
     barrier_buffer_ptrs: list[int],
@@ -171,7 +213,7 @@ def barrier_all(
     _C.barrier_all(barrier_buffer, barrier_buffer_ptrs, barrier_buffer_multicast_ptr, target)
 
 
-@torch.library.custom_op("mok::schedule", mutates_args=())
+@_op("mok::schedule", mutates_args=())
 def schedule(
     topk_all: torch.Tensor,
     num_local_experts: int,
@@ -202,7 +244,7 @@ def schedule(
     return _C.schedule(topk_all, num_local_experts, schedule_capacity, rank)
 
 
-@torch.library.custom_op(
+@_op(
     "mok::mxfp8_quantize", mutates_args=(),
     schema="(Tensor x_bf16, bool return_normal, bool return_transposed) -> (Tensor?, Tensor?, Tensor?, Tensor?)",
 )
@@ -246,7 +288,7 @@ def _validate_fwd_bf16(x, x_ptrs, w_shared_gate, w_routed_gate, w_shared_up, w_r
     _check_shapes_devices(x.device, table)
 
 
-@torch.library.custom_op("mok::dispatch_mlp_swiglu_combine_fwd_bf16", mutates_args=("combine_buffer",))
+@_op("mok::dispatch_mlp_swiglu_combine_fwd_bf16", mutates_args=("combine_buffer",))
 def dispatch_mlp_swiglu_combine_fwd_bf16(
     x: torch.Tensor,
     x_ptrs: list[int],
@@ -282,7 +324,7 @@ def dispatch_mlp_swiglu_combine_fwd_bf16(
         topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size)
 
 
-@torch.library.custom_op("mok::recompute_forward_context_bf16", mutates_args=())
+@_op("mok::recompute_forward_context_bf16", mutates_args=())
 def recompute_forward_context_bf16(
     x: torch.Tensor,
     x_ptrs: list[int],
@@ -311,7 +353,7 @@ def recompute_forward_context_bf16(
         minibatch_size)
 
 
-@torch.library.custom_op(
+@_op(
     "mok::dispatch_mlp_swiglu_combine_bwd_bf16",
     mutates_args=("d_x_routed_buffer", "d_router_weight_buffer", "x_routed", "gate_routed", "up_routed", "hidden_routed"),
 )
@@ -386,7 +428,7 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(
         tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size)
 
 
-@torch.library.custom_op("mok::fwd_epilogue", mutates_args=())
+@_op("mok::fwd_epilogue", mutates_args=())
 def fwd_epilogue(y_shared: torch.Tensor, combine_buffer: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
     """output = y_shared + sum_k topk_weights[:, k] * combine_buffer[t*K+k] (reference: mok/ops.py:1279-1313)."""
     T, H = _check_activation("y_shared", y_shared)
@@ -402,7 +444,7 @@ def fwd_epilogue(y_shared: torch.Tensor, combine_buffer: torch.Tensor, topk_weig
     return _C.fwd_epilogue(y_shared, combine_buffer, topk_weights)
 
 
-@torch.library.custom_op("mok::bwd_epilogue", mutates_args=())
+@_op("mok::bwd_epilogue", mutates_args=())
 def bwd_epilogue(d_x_shared: torch.Tensor, d_x_routed_buffer: torch.Tensor) -> torch.Tensor:
     """d_x = d_x_shared + sum_k d_x_routed_buffer[t*K+k] (reference: mok/ops.py:1316-1349)."""
     T, H = _check_activation("d_x_shared", d_x_shared)

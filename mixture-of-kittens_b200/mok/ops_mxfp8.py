@@ -35,7 +35,7 @@ def _check_table(device, table):
             raise ValueError(f"{name} must be on {device}")
 
 
-@torch.library.custom_op("mok::dispatch_mlp_swiglu_combine_fwd_mxfp8", mutates_args=("combine_buffer",))
+@_ops._op("mok::dispatch_mlp_swiglu_combine_fwd_mxfp8", mutates_args=("combine_buffer",))
 def dispatch_mlp_swiglu_combine_fwd_mxfp8(
     x: torch.Tensor,
     x_ptrs: list[int],
@@ -84,7 +84,7 @@ def dispatch_mlp_swiglu_combine_fwd_mxfp8(
         minibatch_size)
 
 
-@torch.library.custom_op("mok::recompute_forward_context_mxfp8", mutates_args=())
+@_ops._op("mok::recompute_forward_context_mxfp8", mutates_args=())
 def recompute_forward_context_mxfp8(
     x: torch.Tensor,
     x_ptrs: list[int],
@@ -121,7 +121,7 @@ def recompute_forward_context_mxfp8(
         macrobatch_size, minibatch_size)
 
 
-@torch.library.custom_op(
+@_ops._op(
     "mok::dispatch_mlp_swiglu_combine_bwd_mxfp8",
     mutates_args=("d_x_routed_buffer", "d_router_weight_buffer", "x_fp8_t_routed", "x_sc_t_routed", "gate_fp8_routed",
                   "gate_sc_routed", "up_fp8_routed", "up_sc_routed", "hidden_fp8_t_routed", "hidden_sc_t_routed"),

@@ -186,3 +186,35 @@ def test_stage_copies_unless_the_value_already_is_the_buffer():
     wide = torch.arange(64.0).view(4, 16)
     _stage(buf, wide[:, :8])                           # same start address but another stride: copied, not aliased
     assert torch.equal(buf, wide[:, :8])
+
+
+def test_functional_runs_operator_bodies_directly_only_in_plain_eager_mode():
+    """`ops.call` skips the dispatcher in plain eager mode (same errors, version counters of mutated arguments still
+    bumped) and goes through the registered operator under a dispatch mode, for subclasses and for tensors that
+    require grad."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from mok import ops
+    t = torch.zeros(4)
+    assert ops._plain_eager((t, 3, [1, 2], None))
+    assert not ops._plain_eager((torch.nn.Parameter(t),))
+    assert not ops._plain_eager((t.clone().requires_grad_(),))
+    with FakeTensorMode():
+        assert not ops._plain_eager((t,))
+    assert set(ops._EAGER) >= {ops.all_gather_top_experts, ops.barrier_all, ops.schedule, ops.fwd_epilogue, ops.bwd_epilogue,
+                               ops.dispatch_mlp_swiglu_combine_fwd_bf16, ops.dispatch_mlp_swiglu_combine_bwd_bf16}
+    assert ops._EAGER[ops.barrier_all][1] == (0, 3) and ops._EAGER[ops.dispatch_mlp_swiglu_combine_fwd_bf16][1] == (2,)
+    # the body's own validation error, raised without a device in sight
+    with pytest.raises(ValueError, match="CUDA"):
+        ops.call(ops.barrier_all, torch.zeros(1, dtype=torch.int32), [1], 0, torch.zeros(1, dtype=torch.int32))
+
+    seen = []
+
+    @ops._op("mok_test::bump", mutates_args=("buf",))
+    def bump(buf: torch.Tensor, by: int) -> None:
+        seen.append(by)
+        buf.add_(by)
+
+    buf = torch.zeros(2)
+    v0 = buf._version
+    ops.call(bump, buf, 2)
+    assert seen == [2] and buf._version > v0 and float(buf[0]) == 2.0
