@@ -49,6 +49,8 @@ extern "C" {
 #define MOKB_ST_PIPELINE_TIMEOUT 3    /* an mbarrier wait inside a GEMM ran out */
 #define MOKB_ST_MACROBATCH_OVERFLOW 4 /* reserved: every layer entry point splits the rows into macrobatches */
 #define MOKB_ST_FLAG_TIMEOUT 5        /* a wait on a counter that another kernel or CTA raises ran out (2 s) */
+#define MOKB_ST_BAD_INDEX 6           /* a schedule entry names a route outside [0, tokens * topk): the row was skipped.
+                                       * Words 1..3: 1 pull / 2 push kernel / 3 GEMM epilogue push, the row, the index */
 
 const char* mokb_last_error(void);
 /* Compute capability major*10+minor of the current device, or a negative error. */
@@ -349,6 +351,9 @@ typedef struct {
     const int32_t* push_idx;
     const float* push_values;
     const uint64_t* push_value_ptrs_host;
+    /* rows of each destination buffer (0 = unchecked): a push_idx outside [0, push_index_limit) is not stored anywhere and
+     * sets MOKB_ST_BAD_INDEX -- a stale or foreign schedule must not become a store into a peer's memory */
+    int64_t push_index_limit;
     /* mode 3, optional, device [G]: rows of group g from group_k_end[g] on (up to off[g+1]) are zero in A and B -- the
      * padding at the end of an expert's segment -- and are left out of the contraction, in steps of 64 rows */
     const int32_t* group_k_end;
@@ -404,6 +409,7 @@ typedef struct {
     const int32_t* push_idx;
     const float* push_values;
     const uint64_t* push_value_ptrs_host;
+    int64_t push_index_limit;      /* as in mokb_gemm_args */
     /* A launch with win_ready leaves this many SMs (0 = 2) to the kernels that produce the rows it waits for (the
      * reference sets whole SMs aside for communication: num_comm_sms).  The layer uses 2. */
     int reserve_sms;
@@ -436,6 +442,10 @@ int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
  *   q_out, q_sc_out -- optional, together (hidden % 128 == 0, 32-byte aligned rows): the pulled (and scaled) rows also in
  *                    MXFP8, E4M3 [max_rows, hidden] + packed scales, quantised along the columns from the registers
  *                    they pass through (dispatch_combine.cuh:88-114); byte for byte what mokb_mxfp8_quantize gives.
+ *   index_limit   -- routes per rank (tokens * topk; 0 = unchecked): a row whose peer_token_idx is outside [0, index_limit)
+ *                    is treated as padding (pull: zeros; push: not stored) and sets MOKB_ST_BAD_INDEX in `status`, so
+ *                    that a stale or foreign schedule cannot turn into an access outside a peer's buffer.  The layer
+ *                    entry points always pass it.
  *   wait_counter  -- optional; the combine launch first waits (2 s at most, then MOKB_ST_FLAG_TIMEOUT in `status` and
  *                    no row is copied) until it holds ((rows of the window) / 256) * arrivals_per_row_block arrivals:
  *                    win_done[w] of a mode-4 GEMM with arrivals_per_row_block = (N2 / 256) * 8.  row_begin must be a
@@ -445,12 +455,14 @@ int mokb_dispatch_rows_window(const uint64_t* src_ptrs_host, int ep_size, const 
                               const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin,
                               int row_end, int row_divisor, int64_t hidden, void* dst,
                               const uint64_t* row_scale_ptrs_host, float* row_scale_out, int blocks,
-                              int32_t* done_counter, void* q_out, void* q_sc_out, void* stream);
+                              int32_t* done_counter, void* q_out, void* q_sc_out, int64_t index_limit, int32_t* status,
+                              void* stream);
 int mokb_combine_rows_window(const void* src, const uint64_t* dst_ptrs_host, int ep_size,
                              const int32_t* peer_rank, const int32_t* peer_token_idx,
                              const int32_t* num_rows, int max_rows, int row_begin, int row_end, int64_t hidden,
                              const float* row_values, const uint64_t* value_ptrs_host, int blocks,
-                             const int32_t* wait_counter, int arrivals_per_row_block, int32_t* status, void* stream);
+                             const int32_t* wait_counter, int arrivals_per_row_block, int32_t* status, int64_t index_limit,
+                             void* stream);
 
 /* SwiGLU forward / backward on [rows, cols] bf16 (csrc/megakernel/swiglu.cuh:38-207, 209-566).
  * Backward also emits per-row sum(d_hidden * silu(g)*u) / w (w = row_scale[i], 1/w := 0 if w <= 0)

@@ -102,7 +102,8 @@ template <bool SCALE, int W, bool QUANT>
 __global__ void __maxnreg__(64) dispatch_kernel(PeerPtrs src, PeerPtrs scale_src, const int32_t* __restrict__ peer_rank,
                                 const int32_t* __restrict__ peer_token_idx, const int32_t* __restrict__ num_rows,
                                 int max_rows, int row_begin, int row_end, int R, int row_divisor, int vec_per_row,
-                                Words<W>* __restrict__ dst, float* __restrict__ row_scale_out, int32_t* done_counter, RowQuant rq) {
+                                Words<W>* __restrict__ dst, float* __restrict__ row_scale_out, int32_t* done_counter, RowQuant rq,
+                                IndexGuard guard) {
     int rows = num_rows ? *num_rows : max_rows;
     rows = rows < 0 ? 0 : (rows > max_rows ? 0 : rows);
     rows = min(rows, row_end);
@@ -120,6 +121,7 @@ __global__ void __maxnreg__(64) dispatch_kernel(PeerPtrs src, PeerPtrs scale_src
         if (r < rows) {
             pr_next = peer_rank[r];
             tok_next = peer_token_idx[r];
+            if (pr_next >= 0 && pr_next < R && !index_ok(guard, tok_next, kBadIndexPull, r)) pr_next = -1;
             if (SCALE && pr_next >= 0 && pr_next < R) w_next = static_cast<const float*>(scale_src.p[pr_next])[tok_next];
         }
     };
@@ -207,7 +209,7 @@ __global__ void combine_kernel(const Words<W>* __restrict__ src, PeerPtrs dst, P
                                const int32_t* __restrict__ peer_rank, const int32_t* __restrict__ peer_token_idx,
                                const int32_t* __restrict__ num_rows, int max_rows, int row_begin, int row_end, int R,
                                int vec_per_row, const float* __restrict__ row_values, const int32_t* wait_counter,
-                               int arrivals_per_row_block, int32_t* status) {
+                               int arrivals_per_row_block, int32_t* status, int index_limit) {
     int rows = num_rows ? *num_rows : max_rows;
     rows = rows < 0 ? 0 : (rows > max_rows ? 0 : rows);
     rows = min(rows, row_end);
@@ -229,6 +231,7 @@ __global__ void combine_kernel(const Words<W>* __restrict__ src, PeerPtrs dst, P
         const int pr = peer_rank[row];
         if (pr < 0 || pr >= R) continue;
         const int tok = peer_token_idx[row];
+        if (!index_ok(IndexGuard{index_limit, status}, tok, kBadIndexPush, row)) continue;
         const Words<W>* in = src + static_cast<size_t>(row) * vec_per_row;
         Words<W>* out = static_cast<Words<W>*>(dst.p[pr]) + static_cast<size_t>(tok) * vec_per_row;
         for (int v0 = lane; v0 < vec_per_row; v0 += 128) {
@@ -321,13 +324,17 @@ int comm_default_blocks() { return sm_count() * 16; }
 int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t* peer_rank,
                        const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                        int row_divisor, int64_t hidden, void* dst, const uint64_t* row_scale_ptrs_host,
-                       float* row_scale_out, int blocks, cudaStream_t s, int32_t* done_counter, void* q_out, void* q_sc_out) {
+                       float* row_scale_out, int blocks, cudaStream_t s, int32_t* done_counter, void* q_out, void* q_sc_out,
+                       int64_t index_limit, int32_t* status) {
     TraceScope trace(s, row_scale_ptrs_host ? "dispatch_scaled" : "dispatch", row_begin);
     MOKB_REQUIRE((q_out == nullptr) == (q_sc_out == nullptr), "dispatch_rows: the quantised rows and their scales go together");
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "dispatch_rows: bad ep_size");
     MOKB_REQUIRE(peer_rank && peer_token_idx && dst, "dispatch_rows: null pointer");
     MOKB_REQUIRE(max_rows >= 0 && row_divisor >= 1 && hidden > 0 && hidden % 8 == 0, "dispatch_rows: bad sizes");
     MOKB_REQUIRE(row_begin >= 0 && row_begin <= row_end, "dispatch_rows: bad row window");
+    MOKB_REQUIRE(index_limit >= 0 && index_limit <= INT32_MAX && (index_limit == 0 || status != nullptr),
+                 "dispatch_rows: index_limit needs a status word and must fit 31 bits");
+    const IndexGuard guard{static_cast<int>(index_limit), status};
     MOKB_REQUIRE((reinterpret_cast<uintptr_t>(dst) & 15) == 0, "dispatch_rows: dst not 16-byte aligned");
     PeerPtrs src, scale;
     MOKB_TRY(fill_peers(&src, src_ptrs_host, ep_size, "src_ptrs"));
@@ -352,7 +359,7 @@ int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t
         share_sms_with_gemm(dispatch_kernel<SC, WW, QQ>);                                                                      \
         dispatch_kernel<SC, WW, QQ><<<blocks, threads, 0, s>>>(src, scale, peer_rank, peer_token_idx, num_rows, max_rows,      \
             row_begin, row_end, ep_size, row_divisor, vec, static_cast<Words<WW>*>(dst), SC ? row_scale_out : nullptr,         \
-            done_counter, rq);                                                                                                 \
+            done_counter, rq, guard);                                                                                          \
     } while (0)
     if (row_scale_ptrs_host) {
         if (q_out) MOKB_DISPATCH(true, 8, true);
@@ -372,8 +379,10 @@ int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t
 int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_size, const int32_t* peer_rank,
                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                       int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s,
-                      const int32_t* wait_counter, int arrivals_per_row_block, int32_t* status) {
+                      const int32_t* wait_counter, int arrivals_per_row_block, int32_t* status, int64_t index_limit) {
     TraceScope trace(s, "combine", row_begin);
+    MOKB_REQUIRE(index_limit >= 0 && index_limit <= INT32_MAX && (index_limit == 0 || status != nullptr),
+                 "combine_rows: index_limit needs a status word and must fit 31 bits");
     MOKB_REQUIRE(wait_counter == nullptr || (arrivals_per_row_block > 0 && status != nullptr && row_begin % 256 == 0),
                  "combine_rows: a wait counter needs arrivals_per_row_block, a status word and a window that starts on a 256-row block");
     MOKB_REQUIRE(ep_size >= 1 && ep_size <= MOKB_MAX_EP, "combine_rows: bad ep_size");
@@ -396,11 +405,11 @@ int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_siz
     if (rows_aligned32(src, dst, ep_size, hidden))
         combine_kernel<8><<<blocks, 128, 0, s>>>(static_cast<const Words<8>*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
                                                  row_begin, row_end, ep_size, static_cast<int>(hidden / 16), row_values, wait_counter,
-                                                 arrivals_per_row_block, status);
+                                                 arrivals_per_row_block, status, static_cast<int>(index_limit));
     else
         combine_kernel<4><<<blocks, 128, 0, s>>>(static_cast<const Words<4>*>(src), dst, val, peer_rank, peer_token_idx, num_rows, max_rows,
                                                  row_begin, row_end, ep_size, static_cast<int>(hidden / 8), row_values, wait_counter,
-                                                 arrivals_per_row_block, status);
+                                                 arrivals_per_row_block, status, static_cast<int>(index_limit));
     MOKB_CUDA(cudaGetLastError());
     note_launch();
     return MOKB_OK;
@@ -422,10 +431,11 @@ extern "C" int mokb_dispatch_rows_window(const uint64_t* src_ptrs_host, int ep_s
                                          const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin,
                                          int row_end, int row_divisor, int64_t hidden, void* dst,
                                          const uint64_t* row_scale_ptrs_host, float* row_scale_out, int blocks,
-                                         int32_t* done_counter, void* q_out, void* q_sc_out, void* stream) {
+                                         int32_t* done_counter, void* q_out, void* q_sc_out, int64_t index_limit,
+                                         int32_t* status, void* stream) {
     return dispatch_rows_impl(src_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, row_divisor,
                               hidden, dst, row_scale_ptrs_host, row_scale_out, blocks, static_cast<cudaStream_t>(stream), done_counter,
-                              q_out, q_sc_out);
+                              q_out, q_sc_out, index_limit, status);
 }
 
 extern "C" int mokb_combine_rows(const void* src, const uint64_t* dst_ptrs_host, int ep_size,
@@ -440,8 +450,9 @@ extern "C" int mokb_combine_rows_window(const void* src, const uint64_t* dst_ptr
                                         const int32_t* peer_rank, const int32_t* peer_token_idx,
                                         const int32_t* num_rows, int max_rows, int row_begin, int row_end, int64_t hidden,
                                         const float* row_values, const uint64_t* value_ptrs_host, int blocks,
-                                        const int32_t* wait_counter, int arrivals_per_row_block, int32_t* status, void* stream) {
+                                        const int32_t* wait_counter, int arrivals_per_row_block, int32_t* status,
+                                        int64_t index_limit, void* stream) {
     return combine_rows_impl(src, dst_ptrs_host, ep_size, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, hidden,
                              row_values, value_ptrs_host, blocks, static_cast<cudaStream_t>(stream), wait_counter,
-                             arrivals_per_row_block, status);
+                             arrivals_per_row_block, status, index_limit);
 }

@@ -73,11 +73,12 @@ int dispatch_rows_impl(const uint64_t* src_ptrs_host, int ep_size, const int32_t
                        const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                        int row_divisor, int64_t hidden, void* dst, const uint64_t* row_scale_ptrs_host,
                        float* row_scale_out, int blocks, cudaStream_t s, int32_t* done_counter = nullptr,
-                       void* q_out = nullptr, void* q_sc_out = nullptr);
+                       void* q_out = nullptr, void* q_sc_out = nullptr, int64_t index_limit = 0, int32_t* status = nullptr);
 int combine_rows_impl(const void* src, const uint64_t* dst_ptrs_host, int ep_size, const int32_t* peer_rank,
                       const int32_t* peer_token_idx, const int32_t* num_rows, int max_rows, int row_begin, int row_end,
                       int64_t hidden, const float* row_values, const uint64_t* value_ptrs_host, int blocks, cudaStream_t s,
-                      const int32_t* wait_counter = nullptr, int arrivals_per_row_block = 0, int32_t* status = nullptr);
+                      const int32_t* wait_counter = nullptr, int arrivals_per_row_block = 0, int32_t* status = nullptr,
+                      int64_t index_limit = 0);
 
 // MXFP8 codec launchers (quantize.cu).  Rows [row_begin, min(row_end, *num_rows)) are processed (row_end = 0: all
 // M / rows_cap rows; `num_rows` is a device pointer, optional).  Row numbers are the caller's: a buffer holding only
@@ -217,6 +218,24 @@ __device__ __forceinline__ bool flag_wait(const int* flag, int target, volatile 
             }
         }
     }
+}
+
+// Routes are numbered [0, limit) on every rank; an index outside (a stale or foreign schedule) must not become an access
+// to a peer's memory: the row is skipped and the status words say where (limit <= 0: unchecked).
+struct IndexGuard {
+    int limit;
+    int32_t* status;
+};
+enum { kBadIndexPull = 1, kBadIndexPush = 2, kBadIndexGemmPush = 3 };
+
+__device__ __forceinline__ bool index_ok(const IndexGuard& g, int idx, int kind, int row) {
+    if (g.limit <= 0 || (idx >= 0 && idx < g.limit)) return true;
+    if (g.status && atomicCAS(g.status, 0, MOKB_ST_BAD_INDEX) == 0) {
+        g.status[1] = kind;
+        g.status[2] = row;
+        g.status[3] = idx;
+    }
+    return false;
 }
 
 // ---- TMA

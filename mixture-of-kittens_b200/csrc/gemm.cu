@@ -95,7 +95,7 @@ struct KParams {
     int32_t* win_done;               // [windows from row_begin], optional
     // push (MODE_NT, MODE_NN, the down tiles of MODE_FWD): row r of the result goes to row push_idx[r] of rank
     // push_rank[r]'s buffer (rows with a rank outside [0, push_ranks) go nowhere) -- combine without a combine kernel
-    int push, push_ranks, push_wide;
+    int push, push_ranks, push_wide, push_limit;
     const int32_t* push_rank;
     const int32_t* push_idx;
     const float* push_values;        // optional: push_val[rank][idx] = push_values[r], written with the first column tile
@@ -478,7 +478,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 __nv_bfloat16* pdst = nullptr;                // this row's place in its home rank's buffer
                 if ((MODE == MODE_NT || MODE == MODE_NN || MODE == MODE_FWD) && p.push) {
                     const int pr = p.push_rank[tile_row];
-                    if (pr >= 0 && pr < p.push_ranks) {
+                    if (pr >= 0 && pr < p.push_ranks &&
+                        index_ok(IndexGuard{p.push_limit, p.status}, p.push_idx[tile_row], kBadIndexGemmPush, tile_row)) {
                         const size_t slot = static_cast<size_t>(p.push_idx[tile_row]);
                         pdst = static_cast<__nv_bfloat16*>(p.push_dst.p[pr]) + slot * ld_out + static_cast<size_t>(ti.n_blk) * BN;
                         if (p.push_values && ti.n_blk == 0) static_cast<float*>(p.push_val.p[pr])[slot] = p.push_values[tile_row];
@@ -706,6 +707,8 @@ extern "C" int mokb_grouped_gemm_bf16(const mokb_gemm_args* g, void* stream_) {
         MOKB_REQUIRE(g->push_ep_size >= 1 && g->push_ep_size <= MOKB_MAX_EP && g->push_rank && g->push_idx, "grouped_gemm: push needs ranks and indices");
         MOKB_REQUIRE((g->push_values == nullptr) == (g->push_value_ptrs_host == nullptr), "grouped_gemm: push_values and push_value_ptrs_host go together");
         const int ld_out = g->mode == MODE_FWD ? g->ldd4 : g->ldd;
+        MOKB_REQUIRE(g->push_index_limit >= 0 && g->push_index_limit <= INT32_MAX, "grouped_gemm: push_index_limit must fit 31 bits");
+        p.push_limit = static_cast<int>(g->push_index_limit);
         p.push = 1; p.push_ranks = g->push_ep_size; p.push_rank = g->push_rank; p.push_idx = g->push_idx; p.push_values = g->push_values;
         p.push_wide = ld_out % 16 == 0;
         for (int r = 0; r < kPeerMax; ++r) p.push_dst.p[r] = p.push_val.p[r] = nullptr;

@@ -85,7 +85,7 @@ struct FParams {
     int32_t* win_done;
     int reserve_pairs;               // SM pairs a waiting launch leaves to the kernels it waits for
     // push (FMODE_NT and the down tiles of FMODE_FWD): row r goes to row push_idx[r] of rank push_rank[r]'s buffer
-    int push, push_ranks, push_wide;
+    int push, push_ranks, push_wide, push_limit;
     const int32_t* push_rank;
     const int32_t* push_idx;
     const float* push_values;
@@ -491,7 +491,8 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ Maps tm, const FParams p) {
             __nv_bfloat16* pdst = nullptr;                 // this row's place in its home rank's buffer
             if ((MODE == FMODE_NT || MODE == FMODE_FWD) && p.push) {
                 const int pr = p.push_rank[tile_row];
-                if (pr >= 0 && pr < p.push_ranks) {
+                if (pr >= 0 && pr < p.push_ranks &&
+                    index_ok(IndexGuard{p.push_limit, p.status}, p.push_idx[tile_row], kBadIndexGemmPush, tile_row)) {
                     const size_t slot = static_cast<size_t>(p.push_idx[tile_row]);
                     pdst = static_cast<__nv_bfloat16*>(p.push_dst.p[pr]) + slot * p.ldd + static_cast<size_t>(ti.n_blk) * BN + half * 128;
                     if (p.push_values && ti.n_blk == 0 && half == 0) static_cast<float*>(p.push_val.p[pr])[slot] = p.push_values[tile_row];
@@ -657,6 +658,8 @@ extern "C" int mokb_grouped_gemm_mxfp8(const mokb_gemm_fp8_args* g, void* stream
         MOKB_REQUIRE(g->mode == FMODE_NT || g->mode == FMODE_FWD, "grouped_gemm_mxfp8: push is for modes 0 and 4");
         MOKB_REQUIRE(g->push_ep_size >= 1 && g->push_ep_size <= MOKB_MAX_EP && g->push_rank && g->push_idx, "grouped_gemm_mxfp8: push needs ranks and indices");
         MOKB_REQUIRE((g->push_values == nullptr) == (g->push_value_ptrs_host == nullptr), "grouped_gemm_mxfp8: push_values and push_value_ptrs_host go together");
+        MOKB_REQUIRE(g->push_index_limit >= 0 && g->push_index_limit <= INT32_MAX, "grouped_gemm_mxfp8: push_index_limit must fit 31 bits");
+        p.push_limit = static_cast<int>(g->push_index_limit);
         p.push = 1; p.push_ranks = g->push_ep_size; p.push_rank = g->push_rank; p.push_idx = g->push_idx; p.push_values = g->push_values;
         p.push_wide = g->ldd % 16 == 0;
         for (int r = 0; r < kPeerMax; ++r) p.push_dst.p[r] = p.push_val.p[r] = nullptr;

@@ -84,6 +84,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_arg
         MOKB_REQUIRE(a->combine_ptrs_host && a->w_shared_down && a->w_routed_down && a->y_shared, "fwd_bf16: null down/combine pointer");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
     const int C = a->schedule_capacity;
+    const int64_t routes = static_cast<int64_t>(T) * a->topk;      // every rank's routes are numbered [0, routes)
     const Scratch s = carve(a->scratch, C, E_l, MB);
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
@@ -120,7 +121,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_arg
         for (int c = 0; c < nchunks; ++c) {
             const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
             MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
-                                        x_routed, nullptr, nullptr, comm_blocks, s_in, flags ? s.win_ready + c : nullptr));
+                                        x_routed, nullptr, nullptr, comm_blocks, s_in, flags ? s.win_ready + c : nullptr, nullptr, nullptr, routes, a->status));
         }
         if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
 
@@ -157,7 +158,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_bf16(const mokb_fwd_bf16_arg
             // combine buffers (y_routed, when the caller wants it, gets a copy)
             g.B3 = a->w_routed_down; g.ldb3 = I; g.D4 = y_r; g.ldd4 = H; g.N2 = H;
             g.push_ptrs_host = a->combine_ptrs_host; g.push_ep_size = a->ep_size;
-            g.push_rank = a->peer_rank; g.push_idx = a->peer_token_idx;
+            g.push_rank = a->peer_rank; g.push_idx = a->peer_token_idx; g.push_index_limit = routes;
         }
         MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
         // the next macrobatch (or the caller) reuses x_routed: the side stream must be done with it
@@ -179,6 +180,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
                  a->d_w_shared_up && a->d_w_routed_up && a->d_w_shared_down && a->d_w_routed_down, "bwd_bf16: null output");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
     const int C = a->schedule_capacity;
+    const int64_t routes = static_cast<int64_t>(T) * a->topk;      // every rank's routes are numbered [0, routes)
     const Scratch s = carve(a->scratch, C, E_l, MB);
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
@@ -223,7 +225,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
         // replay (later macrobatches only): pull x again; the saved context holds macrobatch 0
         if (m > 0)
             MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
-                                        x_routed, nullptr, nullptr, comm_blocks, s_in));
+                                        x_routed, nullptr, nullptr, comm_blocks, s_in, nullptr, nullptr, nullptr, routes, a->status));
         if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));     // the replayed x is in place
         // reverse combine: pull d_y rows, scaled by the route's router weight, in a few windows; in macrobatch 0 the
         // first routed GEMM is one launch that starts each window when the window's dispatch blocks have arrived
@@ -233,7 +235,8 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
         for (int c = 0; c < nb; ++c) {
             const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
             MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
-                                        d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in, flags ? s.win_ready + c : nullptr));
+                                        d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in, flags ? s.win_ready + c : nullptr, nullptr, nullptr,
+                                        routes, a->status));
         }
         if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[0], s_in));
 
@@ -287,7 +290,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_bf16(const mokb_bwd_bf16_arg
         g.A = d_gate_r; g.B = a->w_routed_gate; g.A2 = d_up_r; g.B2 = a->w_routed_up; g.lda = I; g.ldb = H;
         g.D = d_x_r; g.ldd = H;
         g.push_ptrs_host = a->d_x_routed_ptrs_host; g.push_ep_size = a->ep_size;
-        g.push_rank = a->peer_rank; g.push_idx = a->peer_token_idx;
+        g.push_rank = a->peer_rank; g.push_idx = a->peer_token_idx; g.push_index_limit = routes;
         g.push_values = d_w_row; g.push_value_ptrs_host = a->d_router_weight_ptrs_host;
         MOKB_TRY(mokb_grouped_gemm_bf16(&g, stream));
         const int32_t* offs = s.mb_offsets + static_cast<size_t>(m) * (E_l + 1);

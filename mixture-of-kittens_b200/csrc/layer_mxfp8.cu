@@ -113,6 +113,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
                      "fwd_mxfp8: null down/combine pointer");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
     const int C = a->schedule_capacity;
+    const int64_t routes = static_cast<int64_t>(T) * a->topk;      // every rank's routes are numbered [0, routes)
     const Scratch s = carve(a->scratch, C, E_l, MB);
     const bool overlap = overlap_enabled();
     Async* as = nullptr;
@@ -150,7 +151,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
             const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
             MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
                                         v.x_routed, nullptr, nullptr, comm_blocks, s_in, flags ? s.win_ready + c : nullptr,
-                                        v.x_fp8, v.x_sc));
+                                        v.x_fp8, v.x_sc, routes, a->status));
         }
         for (int c = 0; c < nchunks; ++c) {
             const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
@@ -192,7 +193,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
         if (with_down) {
             f.B3 = a->w_routed_down; f.B3_sc = a->w_routed_down_sc; f.N2 = H; f.D = y_r;
             f.push_ptrs_host = a->combine_ptrs_host; f.push_ep_size = a->ep_size;
-            f.push_rank = a->peer_rank; f.push_idx = a->peer_token_idx;
+            f.push_rank = a->peer_rank; f.push_idx = a->peer_token_idx; f.push_index_limit = routes;
         }
         MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
         // the next macrobatch (or the caller) reuses the pulled rows: the side stream must be done with them
@@ -217,6 +218,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
                  "bwd_mxfp8: null work buffer");
     const int T = a->num_local_tokens, H = a->hidden, I = a->intermediate, E_l = a->num_local_experts, MB = a->macrobatch_size;
     const int C = a->schedule_capacity;
+    const int64_t routes = static_cast<int64_t>(T) * a->topk;      // every rank's routes are numbered [0, routes)
     const int n_macro = macrobatches(C, MB);
     if (n_macro > 1)
         MOKB_REQUIRE(a->w_routed_gate && a->w_routed_gate_sc && a->w_routed_up && a->w_routed_up_sc && a->x_routed && a->x_fp8 && a->x_sc &&
@@ -266,7 +268,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
         }
         if (m > 0) {       // replay: pull x again and quantise it both ways
             MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, lo, hi, a->topk, H,
-                                        v.x_routed, nullptr, nullptr, comm_blocks, s_in, nullptr, v.x_fp8, v.x_sc));
+                                        v.x_routed, nullptr, nullptr, comm_blocks, s_in, nullptr, v.x_fp8, v.x_sc, routes, a->status));
             MOKB_TRY(quantize_impl(v.x_routed, 1, MB, H, s.n_rows, lo, hi, nullptr, nullptr, v.x_fp8_t, v.x_sc_t, s_in, comm_blocks));
         }
         if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));     // the replayed x is in place
@@ -279,7 +281,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
             const int r0 = lo + c * bchunk, r1 = r0 + bchunk < hi ? r0 + bchunk : hi;
             MOKB_TRY(dispatch_rows_impl(a->d_y_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
                                         d_y_r, a->router_weight_ptrs_host, w_row, comm_blocks, s_in, flags ? s.win_ready + c : nullptr,
-                                        d_y_fp8, d_y_sc));
+                                        d_y_fp8, d_y_sc, routes, a->status));
         }
         if (overlap) MOKB_CUDA(cudaEventRecord(as->ev_in[0], s_in));
         for (int c = 0; c < nb; ++c) {       // the token-wise form of d_y, for the weight gradients at the end
@@ -335,7 +337,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_bwd_mxfp8(const mokb_bwd_mxfp8_a
         f.A2 = d_up_fp8; f.A2_sc = d_up_sc; f.B2 = a->w_routed_up_t; f.B2_sc = a->w_routed_up_t_sc; f.D = d_x_r; f.ldd = H;
         // reverse dispatch: the epilogue stores every d_x row and its router-weight gradient into the home rank's buffers
         f.push_ptrs_host = a->d_x_routed_ptrs_host; f.push_ep_size = a->ep_size;
-        f.push_rank = a->peer_rank; f.push_idx = a->peer_token_idx;
+        f.push_rank = a->peer_rank; f.push_idx = a->peer_token_idx; f.push_index_limit = routes;
         f.push_values = d_w_row; f.push_value_ptrs_host = a->d_router_weight_ptrs_host;
         MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
         const int32_t* offs = s.mb_offsets + static_cast<size_t>(m) * (E_l + 1);

@@ -25,7 +25,8 @@ lib = ctypes.CDLL(_LIB_PATH)
 c_int, c_i64, c_f32, c_vp, c_sz = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
 c_u64p = ctypes.POINTER(ctypes.c_uint64)
 
-ST_OK, ST_SCHEDULE_OVERFLOW, ST_BARRIER_TIMEOUT, ST_PIPELINE_TIMEOUT, ST_MACROBATCH_OVERFLOW, ST_FLAG_TIMEOUT = range(6)
+(ST_OK, ST_SCHEDULE_OVERFLOW, ST_BARRIER_TIMEOUT, ST_PIPELINE_TIMEOUT, ST_MACROBATCH_OVERFLOW, ST_FLAG_TIMEOUT,
+ ST_BAD_INDEX) = range(7)
 STATUS_TEXT = {
     ST_OK: "ok",
     ST_SCHEDULE_OVERFLOW: "the padded routed rows exceed schedule_capacity",
@@ -33,6 +34,7 @@ STATUS_TEXT = {
     ST_PIPELINE_TIMEOUT: "a pipeline wait inside a GEMM kernel ran out",
     ST_MACROBATCH_OVERFLOW: "the padded routed rows exceed macrobatch_size",
     ST_FLAG_TIMEOUT: "a wait on a counter raised by another kernel or CTA ran out",
+    ST_BAD_INDEX: "a schedule entry names a route outside [0, tokens * topk); the row was skipped",
 }
 
 
@@ -76,7 +78,7 @@ class GemmArgs(ctypes.Structure):
                 ("B3", c_vp), ("D4", c_vp), ("N2", c_int), ("ldb3", c_int), ("ldd4", c_int), ("window_rows", c_int),
                 ("win_ready", c_vp), ("win_ready_target", c_int), ("blk_done", c_vp), ("win_done", c_vp),
                 ("push_ptrs_host", c_u64p), ("push_ep_size", c_int), ("push_rank", c_vp), ("push_idx", c_vp),
-                ("push_values", c_vp), ("push_value_ptrs_host", c_u64p), ("group_k_end", c_vp)]
+                ("push_values", c_vp), ("push_value_ptrs_host", c_u64p), ("push_index_limit", c_i64), ("group_k_end", c_vp)]
 
 
 class GemmFp8Args(ctypes.Structure):
@@ -89,7 +91,8 @@ class GemmFp8Args(ctypes.Structure):
         + [("t_rows", c_int), ("has_swiglu_limit", c_int), ("swiglu_limit", c_f32), ("status", c_vp)]
         + [("B3", c_vp), ("B3_sc", c_vp), ("N2", c_int), ("window_rows", c_int), ("win_ready", c_vp), ("win_ready_target", c_int),
            ("blk_done", c_vp), ("win_done", c_vp), ("push_ptrs_host", c_u64p), ("push_ep_size", c_int), ("push_rank", c_vp),
-           ("push_idx", c_vp), ("push_values", c_vp), ("push_value_ptrs_host", c_u64p), ("reserve_sms", c_int)])
+           ("push_idx", c_vp), ("push_values", c_vp), ("push_value_ptrs_host", c_u64p), ("push_index_limit", c_i64),
+           ("reserve_sms", c_int)])
 
 
 def _sig(name, restype, *argtypes):
@@ -124,9 +127,9 @@ _sig("mokb_dispatch_rows", c_int, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int,
 _sig("mokb_combine_rows", c_int, c_vp, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_vp, c_u64p, c_vp)
 _sig("mokb_comm_default_blocks", c_int)
 _sig("mokb_dispatch_rows_window", c_int, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_i64, c_vp, c_u64p, c_vp, c_int,
-     c_vp, c_vp, c_vp, c_vp)
+     c_vp, c_vp, c_vp, c_i64, c_vp, c_vp)
 _sig("mokb_combine_rows_window", c_int, c_vp, c_u64p, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_i64, c_vp, c_u64p, c_int, c_vp,
-     c_int, c_vp, c_vp)
+     c_int, c_vp, c_i64, c_vp)
 _sig("mokb_swiglu_fwd", c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_f32, c_vp)
 _sig("mokb_swiglu_bwd", c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_f32, c_vp)
 
@@ -478,7 +481,7 @@ def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None
                  M=0, N=0, K=0, A2=None, B2=None, D2=None, D3=None, lda=None, ldb=None, ldd=None, swiglu_limit=None,
                  row_begin=0, row_end=0, accumulate=False, B3=None, D4=None, N2=0, window_rows=0, win_ready=None,
                  win_ready_target=0, blk_done=None, win_done=None, push_ptrs=None, push_rank=None, push_idx=None,
-                 push_values=None, push_value_ptrs=None, N2_ld=None, group_k_end=None):
+                 push_values=None, push_value_ptrs=None, N2_ld=None, group_k_end=None, push_index_limit=0):
     """Modes 0-3 as in the header; mode 4 = gate/up + SwiGLU (B, B2 -> D, D2, D3) and the down projection
     (D3, B3 -> D4 [rows, N2]) in one launch, with the optional window counters."""
     g = GemmArgs()
@@ -490,6 +493,7 @@ def grouped_gemm(mode, A, B, D, *, rows=None, num_rows=None, group_of_block=None
         keep.append(_ptr_array(push_ptrs))
         g.push_ptrs_host, g.push_ep_size = keep[-1], len(push_ptrs)
         g.push_rank, g.push_idx, g.push_values = _p(push_rank), _p(push_idx), _p(push_values)
+        g.push_index_limit = push_index_limit
         if push_value_ptrs is not None:
             keep.append(_ptr_array(push_value_ptrs))
             g.push_value_ptrs_host = keep[-1]
@@ -517,7 +521,8 @@ def grouped_gemm_mxfp8(mode, A, A_sc, B, B_sc, D, *, rows=None, num_rows=None, g
                        G=1, M=0, N=0, K=0, A2=None, A2_sc=None, B2=None, B2_sc=None, D2=None, ldd=None, row_begin=0, row_end=0,
                        t_first=0, accumulate=False, quantised_outputs=None, t_rows=0, swiglu_limit=None, B3=None, B3_sc=None,
                        N2=0, window_rows=0, win_ready=None, win_ready_target=0, blk_done=None, win_done=None, push_ptrs=None,
-                       push_rank=None, push_idx=None, push_values=None, push_value_ptrs=None, reserve_sms=0):
+                       push_rank=None, push_idx=None, push_values=None, push_value_ptrs=None, reserve_sms=0,
+                       push_index_limit=0):
     """`quantised_outputs` (modes 3, 4): (gate_q, gate_sc, up_q, up_sc, hid_q, hid_sc, hid_qt, hid_sct); D is unused in
     mode 3 and the down projection's output [rows, N2] in mode 4 (B3, B3_sc: its weights)."""
     g = GemmFp8Args()
@@ -530,6 +535,7 @@ def grouped_gemm_mxfp8(mode, A, A_sc, B, B_sc, D, *, rows=None, num_rows=None, g
         keep.append(_ptr_array(push_ptrs))
         g.push_ptrs_host, g.push_ep_size = keep[-1], len(push_ptrs)
         g.push_rank, g.push_idx, g.push_values = _p(push_rank), _p(push_idx), _p(push_values)
+        g.push_index_limit = push_index_limit
         if push_value_ptrs is not None:
             keep.append(_ptr_array(push_value_ptrs))
             g.push_value_ptrs_host = keep[-1]
@@ -571,19 +577,22 @@ def comm_default_blocks() -> int:
 
 
 def dispatch_rows_window(src_ptrs, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, row_divisor, hidden, dst,
-                         row_scale_ptrs=None, row_scale_out=None, blocks=0, done_counter=None, q_out=None, q_sc_out=None):
+                         row_scale_ptrs=None, row_scale_out=None, blocks=0, done_counter=None, q_out=None, q_sc_out=None,
+                         index_limit=0):
     _ck(lib.mokb_dispatch_rows_window(_ptr_array(src_ptrs), len(src_ptrs), _p(peer_rank), _p(peer_token_idx), _p(num_rows),
                                       max_rows, row_begin, row_end, row_divisor, hidden, _p(dst),
                                       None if row_scale_ptrs is None else _ptr_array(row_scale_ptrs), _p(row_scale_out),
-                                      blocks, _p(done_counter), _p(q_out), _p(q_sc_out), _stream()))
+                                      blocks, _p(done_counter), _p(q_out), _p(q_sc_out), index_limit,
+                                      _p(status_tensor(dst.device)), _stream()))
 
 
 def combine_rows_window(src, dst_ptrs, peer_rank, peer_token_idx, num_rows, max_rows, row_begin, row_end, hidden,
-                        row_values=None, value_ptrs=None, blocks=0, wait_counter=None, arrivals_per_row_block=0):
+                        row_values=None, value_ptrs=None, blocks=0, wait_counter=None, arrivals_per_row_block=0,
+                        index_limit=0):
     _ck(lib.mokb_combine_rows_window(_p(src), _ptr_array(dst_ptrs), len(dst_ptrs), _p(peer_rank), _p(peer_token_idx),
                                      _p(num_rows), max_rows, row_begin, row_end, hidden, _p(row_values),
                                      None if value_ptrs is None else _ptr_array(value_ptrs), blocks, _p(wait_counter),
-                                     arrivals_per_row_block, _p(status_tensor(src.device)), _stream()))
+                                     arrivals_per_row_block, _p(status_tensor(src.device)), index_limit, _stream()))
 
 
 def swiglu_fwd(gate, up, swiglu_limit=None, num_rows=None):

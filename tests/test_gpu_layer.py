@@ -174,3 +174,35 @@ def test_inputs_already_in_the_workspace_buffers_skip_the_staging_copies_and_cha
     torch.cuda.synchronize()
     assert _C.check_status() == 0
     assert torch.equal(out, out_ref) and all(torch.equal(a, b) for a, b in zip(grads, grads_ref))
+
+
+@pytest.mark.parametrize("mxfp8", [False, True], ids=["bf16", "mxfp8"])
+def test_a_corrupted_schedule_sets_a_status_code_instead_of_reaching_outside_the_buffers(mxfp8):
+    """One schedule entry rewritten to a route index far outside [0, tokens * topk): forward and backward run to the
+    end, the row is treated as padding, and the status words say MOKB_ST_BAD_INDEX with the row and the index."""
+    from mok import _C, ops, functional as F
+    group = init_single_rank_group()
+    E_l, T, H, I, K = 4, 512, 256, 256, 2
+    inp = to_dev(O.make_inputs(R=1, T=T, H=H, I=I, E=E_l, K=K, seed=21, routing="gaussian")[0])
+    cfg = F.MoKConfig(minibatch_size=256, macrobatch_size=T * K * 2)
+    ws = F.get_workspace(cfg, group, device=torch.device("cuda", 0), num_local_tokens=T, hidden_size=H, topk=K)
+    sched = F.build_schedule(ws, cfg, inp.top_experts, num_local_experts=E_l)
+    live = torch.nonzero(sched.peer_rank[: int(sched.num_tokens.item())] >= 0).flatten()
+    bad_row, bad_idx = int(live[live.numel() // 3]), 1 << 27
+    sched.peer_token_idx[bad_row] = bad_idx
+    if mxfp8:
+        q = [ops.mxfp8_quantize(w, True, True) for w in (inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down)]
+        fw = [(a, b) for a, b, _, _ in q]
+        bw = [q[0], q[1], (q[2][2], q[2][3])]
+    else:
+        fw = bw = [inp.w_routed_gate, inp.w_routed_up, inp.w_routed_down]
+    out, ctx = F.forward(cfg, ws, sched, inp.x, inp.router_weights, inp.w_shared_gate, inp.w_shared_up, inp.w_shared_down, *fw)
+    torch.cuda.synchronize()
+    assert _C.check_status() == _C.ST_BAD_INDEX
+    assert _C.status_detail()[2:] == [bad_row, bad_idx]
+    assert torch.isfinite(out.float()).all()
+    F.backward(cfg, ws, sched, ctx, inp.grad_output, inp.x, inp.router_weights, inp.w_shared_gate, inp.w_shared_up,
+               inp.w_shared_down, *bw)
+    torch.cuda.synchronize()
+    assert _C.check_status() == _C.ST_BAD_INDEX
+    assert _C.status_detail()[2:] == [bad_row, bad_idx]

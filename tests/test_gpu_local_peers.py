@@ -183,3 +183,69 @@ def test_transposed_only_quantiser_matches_the_two_way_quantiser():
     n1, n2, qt2, st2 = ops.mxfp8_quantize(x, False, True)       # the column-only kernel (128 x 64 tiles)
     assert n1 is None and n2 is None
     assert torch.equal(qt.view(torch.uint8), qt2.view(torch.uint8)) and torch.equal(st, st2)
+
+
+def test_a_route_index_outside_the_buffers_is_skipped_and_reported():
+    """A schedule entry that names a route outside [0, tokens * topk) -- a stale or foreign schedule -- must not become
+    an access outside a peer's buffer: the pull writes a zero row, the push kernels and the GEMM epilogue store nothing
+    for that row, every other row is as without the bad entry, and the status words name the kernel kind, the row and
+    the index."""
+    from mok import _C
+    R, T, K, H, I, E_l = 2, 512, 2, 256, 256, 2
+    routes = make_routes(R, T, K, E_l, seed=95)
+    C = T * K * R
+    pr, pt, nt, tpe = O.schedule(routes, E_l, C, 1)
+    N = int(nt[0])
+    live = np.flatnonzero(pr[:N] >= 0)
+    bad_row, bad_idx = int(live[len(live) // 2]), T * K + 12345
+    pt_bad = pt.copy()
+    pt_bad[bad_row] = bad_idx
+    prd, ptd, ptb, ntd = (torch.from_numpy(a).cuda() for a in (pr, pt, pt_bad, nt))
+    g = torch.Generator().manual_seed(96)
+    x = [torch.randn(T, H, generator=g).to(torch.bfloat16).cuda() for _ in range(R)]
+    ptrs = lambda ts: [t.data_ptr() for t in ts]
+
+    def expect(kind):
+        torch.cuda.synchronize()
+        assert _C.check_status() == _C.ST_BAD_INDEX
+        assert _C.status_detail() == [_C.ST_BAD_INDEX, kind, bad_row, bad_idx]
+
+    # pull
+    good = torch.zeros(C, H, dtype=torch.bfloat16, device="cuda")
+    _C.dispatch_rows_window(ptrs(x), prd, ptd, ntd, C, 0, C, K, H, good, index_limit=T * K)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0
+    got = torch.full((C, H), 7.0, dtype=torch.bfloat16, device="cuda")
+    _C.dispatch_rows_window(ptrs(x), prd, ptb, ntd, C, 0, C, K, H, got, index_limit=T * K)
+    expect(1)
+    keep = torch.ones(N, dtype=torch.bool, device="cuda")
+    keep[bad_row] = False
+    assert torch.equal(got[:N][keep], good[:N][keep]) and torch.all(got[bad_row] == 0)
+
+    # push kernel
+    want = [torch.zeros(T * K, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+    _C.combine_rows_window(good, ptrs(want), prd, ptd, ntd, C, 0, C, H, index_limit=T * K)
+    home, slot = int(pr[bad_row]), int(pt[bad_row])
+    want[home][slot] = 0                                           # the one row that must stay untouched
+    out = [torch.zeros(T * K, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+    _C.combine_rows_window(good, ptrs(out), prd, ptb, ntd, C, 0, C, H, index_limit=T * K)
+    expect(2)
+    assert all(torch.equal(a, b) for a, b in zip(out, want))
+
+    # GEMM epilogue push (BF16 down projection)
+    gob = torch.repeat_interleave(torch.arange(E_l, dtype=torch.int32), torch.from_numpy(tpe // 128).long())
+    gob = torch.cat([gob, torch.full((C // 128 - gob.numel(),), -1, dtype=torch.int32)]).cuda()
+    gd = torch.Generator(device="cuda").manual_seed(97)
+    hid = (torch.randn(C, I, generator=gd, device="cuda")).to(torch.bfloat16)
+    Wd = (torch.randn(E_l, H, I, generator=gd, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = [torch.zeros(T * K, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+    _C.grouped_gemm(0, hid, Wd, None, rows=C, num_rows=ntd, group_of_block=gob, G=E_l, N=H, K=I, ldd=H,
+                    push_ptrs=ptrs(ref), push_rank=prd, push_idx=ptd, push_index_limit=T * K)
+    torch.cuda.synchronize()
+    assert _C.check_status() == 0
+    ref[home][slot] = 0
+    out = [torch.zeros(T * K, H, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+    _C.grouped_gemm(0, hid, Wd, None, rows=C, num_rows=ntd, group_of_block=gob, G=E_l, N=H, K=I, ldd=H,
+                    push_ptrs=ptrs(out), push_rank=prd, push_idx=ptb, push_index_limit=T * K)
+    expect(3)
+    assert all(torch.equal(a, b) for a, b in zip(out, ref))
