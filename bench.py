@@ -539,12 +539,14 @@ def comm_alone(prob, sched, timed, _C, rank):
     dist.all_reduce(remote_t, op=dist.ReduceOp.MAX)              # the busiest rank: the time below is the slowest rank's
     remote, remote_step = (int(v) for v in remote_t.tolist())
     buf = torch.empty(prob.MB, prob.H, dtype=torch.bfloat16, device=prob.device)
+    cap = sched.peer_rank.numel()
     ws, out = prob.ws, {"remote_rows": remote, "remote_rows_step": remote_step}
     for name, fn in (
-        ("dispatch", lambda: _C.dispatch_rows(ws.x_buffer_ptrs, sched.peer_rank, sched.peer_token_idx, sched.num_tokens,
-                                              prob.MB, prob.K, prob.H, buf)),
-        ("combine", lambda: _C.combine_rows(buf, ws.combine_buffer_ptrs, sched.peer_rank, sched.peer_token_idx,
-                                            sched.num_tokens, prob.MB, prob.H)),
+        # (row window [0, MB) of the schedule: a rank with more rows than one macrobatch moves the first macrobatch)
+        ("dispatch", lambda: _C.dispatch_rows_window(ws.x_buffer_ptrs, sched.peer_rank, sched.peer_token_idx, sched.num_tokens,
+                                                     cap, 0, prob.MB, prob.K, prob.H, buf, index_limit=prob.T * prob.K)),
+        ("combine", lambda: _C.combine_rows_window(buf, ws.combine_buffer_ptrs, sched.peer_rank, sched.peer_token_idx,
+                                                   sched.num_tokens, cap, 0, prob.MB, prob.H, index_limit=prob.T * prob.K)),
     ):
         fn()
         ms = timed(fn, 5)[0] / 5
@@ -623,7 +625,7 @@ def run_parity_leg(rank, world, device):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
