@@ -76,6 +76,17 @@ def measured_peaks():
     return 1590.0, 6650.0, "fallback"
 
 
+def sustained_peak():
+    """cuBLAS bf16 in a seconds-long loop under the power cap (the regime of a kernel inside a step)."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        if d.get("bf16_tflops_sustained"):
+            return float(d["bf16_tflops_sustained"]), "measured"
+    return 1400.0, "fallback"
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -715,6 +726,10 @@ def main():
         total_ms, per_step = timed(prob.step, args.steps)
     launches = _C.launch_count() - launches_before
     clock_summary = clocks.summary()
+    if world > 1:      # every rank sampled its own GPU: the step runs at the pace of the slowest one
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, clock_summary.get("sm_mhz"))
+        clock_summary["sm_mhz_per_rank"] = per_rank
     ms_per_step = total_ms / args.steps
     fwd_ms, bwd_ms = fwd_bwd_split(prob, prob.step, max(2, args.steps // 4))
     assert _C.check_status() == 0, f"device status word set during the timed region: {_C.status_detail()}"
@@ -738,6 +753,11 @@ def main():
     kern = time_dominant_kernel(_C, sched, prob.x_d, wrg, wru, T, H, I, K, E_l, MB, 5, 2, device, wrd=wrd)
     kern_gu = time_dominant_kernel(_C, sched, prob.x_d, wrg, wru, T, H, I, K, E_l, MB, 5, 2, device)
     model = fwd_routed_bytes(prob, padded_rows, experts_used)
+    kern_per_rank = [None] * world        # the same launch on every rank's own rows and GPU, at the same time
+    if world > 1:
+        dist.all_gather_object(kern_per_rank, round(kern["tflops"], 1))
+    else:
+        kern_per_rank = [round(kern["tflops"], 1)]
     traffic, traffic_note = None, None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
@@ -754,6 +774,11 @@ def main():
                 "algorithmic_bytes": model, "launch_ms": kern["ms"], "flops_per_launch": kern["flops_per_launch"],
                 "rows": real_rows, "padded_rows": padded_rows,
                 "tflops_on_padded_rows": kern["tflops"] * padded_rows / max(real_rows, 1),
+                "tflops_per_rank": kern_per_rank,
+                # `frac` is against the burst figure (the launch is timed alone); the timing loop itself runs for about a
+                # second under the power cap, so the sustained figure is given beside it
+                "frac_of_sustained": kern["tflops"] / sustained_peak()[0], "peak_sustained": sustained_peak()[0],
+                "peak_sustained_source": f"{sustained_peak()[1]} cuBLAS bf16, back to back for seconds",
                 "gate_up_launch_alone": {"ms": kern_gu["ms"], "tflops": kern_gu["tflops"], "frac": kern_gu["tflops"] / peak_tf,
                                          "note": "the gate/up + SwiGLU launch (mode 1) on the same rows: last round's dominant kernel"}}
 
