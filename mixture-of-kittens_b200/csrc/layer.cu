@@ -42,8 +42,12 @@ int get_async(Async** out) {
     MOKB_REQUIRE(dev >= 0 && dev < 64, "layer: device index %d out of range", dev);
     Async& a = g_async[dev];
     if (!a.ready) {
-        MOKB_CUDA(cudaStreamCreateWithFlags(&a.s1, cudaStreamNonBlocking));
-        MOKB_CUDA(cudaStreamCreateWithFlags(&a.s2, cudaStreamNonBlocking));
+        // s1 carries the pulls a waiting GEMM depends on, s2 work that is only needed later (the token-wise MXFP8 copies):
+        // where both have blocks ready for the same free slot of an SM, the pull goes first
+        int prio_low = 0, prio_high = 0;
+        MOKB_CUDA(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high));
+        MOKB_CUDA(cudaStreamCreateWithPriority(&a.s1, cudaStreamNonBlocking, prio_high));
+        MOKB_CUDA(cudaStreamCreateWithPriority(&a.s2, cudaStreamNonBlocking, prio_low));
         cudaEvent_t* single[3] = {&a.fork, &a.join1, &a.join2};
         for (auto e : single) MOKB_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
         for (int c = 0; c < kMaxChunks; ++c) {

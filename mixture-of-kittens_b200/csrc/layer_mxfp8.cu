@@ -119,6 +119,7 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
     Async* as = nullptr;
     if (overlap) MOKB_TRY(get_async(&as));
     cudaStream_t s_in = overlap ? as->s1 : stream;
+    cudaStream_t s_q = overlap ? as->s2 : stream;
     const int comm_blocks = overlap ? a->num_comm_sms * kCommBlocksPerSm : 0;
     // recompute only rebuilds macrobatch 0 (the saved context); the forward walks all of them, last first
     const int n_macro = with_down ? macrobatches(C, MB) : 1;
@@ -146,18 +147,22 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
         }
         // dispatch, window by window: the pull also quantises every row along its columns (what the GEMM reads) and
         // raises the window's counter; the token-wise form (for the weight gradients of the backward pass) follows
-        // from the bf16 rows, under the GEMMs
+        // from the bf16 rows on a second, lower-priority side stream, window by window behind the pull, under the GEMM
         for (int c = 0; c < nchunks; ++c) {
             const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
             MOKB_TRY(dispatch_rows_impl(a->x_ptrs_host, a->ep_size, a->peer_rank, a->peer_token_idx, s.n_rows, C, r0, r1, a->topk, H,
                                         v.x_routed, nullptr, nullptr, comm_blocks, s_in, flags ? s.win_ready + c : nullptr,
                                         v.x_fp8, v.x_sc, routes, a->status));
+            if (overlap) {
+                MOKB_CUDA(cudaEventRecord(as->ev_in[c], s_in));
+                MOKB_CUDA(cudaStreamWaitEvent(s_q, as->ev_in[c], 0));
+            }
+            MOKB_TRY(quantize_impl(v.x_routed, 1, MB, H, s.n_rows, r0, r1, nullptr, nullptr, v.x_fp8_t, v.x_sc_t, s_q, comm_blocks));
         }
-        for (int c = 0; c < nchunks; ++c) {
-            const int r0 = lo + c * chunk, r1 = r0 + chunk < hi ? r0 + chunk : hi;
-            MOKB_TRY(quantize_impl(v.x_routed, 1, MB, H, s.n_rows, r0, r1, nullptr, nullptr, v.x_fp8_t, v.x_sc_t, s_in, comm_blocks));
+        if (overlap) {
+            MOKB_CUDA(cudaEventRecord(as->join1, s_in));
+            MOKB_CUDA(cudaEventRecord(as->join2, s_q));
         }
-        if (overlap) MOKB_CUDA(cudaEventRecord(as->join1, s_in));
 
         if (!shared_done) {
             // shared expert (BF16): gate/up + SwiGLU in one pass, then down (independent of the dispatch)
@@ -198,6 +203,8 @@ extern "C" int mokb_dispatch_mlp_swiglu_combine_fwd_mxfp8(const mokb_fwd_mxfp8_a
         MOKB_TRY(mokb_grouped_gemm_mxfp8(&f, stream));
         // the next macrobatch (or the caller) reuses the pulled rows: the side stream must be done with them
         if (flags) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join1, 0));
+        // ... and with the token-wise copies, which are outputs of this call (and read the pulled rows)
+        if (overlap) MOKB_CUDA(cudaStreamWaitEvent(stream, as->join2, 0));
     }
     return MOKB_OK;
 }

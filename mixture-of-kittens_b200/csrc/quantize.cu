@@ -140,62 +140,59 @@ __global__ void __launch_bounds__(256) quantize_kernel(const __nv_bfloat16* __re
 }
 
 // Column-wise ("transposed") quantisation only, for tensors whose row-wise form already exists (the dispatch kernel
-// writes it as the rows arrive): qt [N, M] + scales from x [M, N].  128 rows x 64 columns per tile and 128 threads, so
-// that a block (17 KB of shared memory, one warp per SM quarter) fits on an SM beside a GEMM CTA and the pass can run
-// under the GEMMs instead of after them.  Same arithmetic as quantize_tile_cols.
+// writes it as the rows arrive): qt [N, M] + scales from x [M, N].  No shared memory and at most 64 registers, so that
+// two blocks of 128 threads fit on an SM beside any of the GEMM kernels (the MXFP8 GEMM leaves less than 8 KB of
+// shared memory and 4096 registers per SM quarter) and the pass runs under the GEMM instead of after it.  A lane owns
+// a pair of adjacent columns over a block of 32 rows: its 32 loads are independent, and a warp's load of one row is
+// one 128-byte line.  Same arithmetic as quantize_tile_cols.
 constexpr int CTILE_COLS = 64;
-constexpr int CPITCH = CTILE_COLS / 2 + 1;     // 33 words per staged row
-__global__ void __launch_bounds__(128) quantize_cols_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64_t N, RowWindow win,
-                                                            uint8_t* __restrict__ qt, uint8_t* __restrict__ sct) {
-    __shared__ uint32_t tile[TILE * CPITCH];
+__global__ void __maxnreg__(64) quantize_cols_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64_t N, RowWindow win,
+                                                     uint8_t* __restrict__ qt, uint8_t* __restrict__ sct) {
     const int live = win.num_rows ? min(max(*win.num_rows, 0), win.end) : win.end;
     const int64_t row_tiles = live > win.begin ? (live - win.begin + TILE - 1) / TILE : 0;
     const int64_t col_tiles = N / CTILE_COLS;
     const int64_t ntiles = row_tiles * col_tiles;
+    const int cp = threadIdx.x & 31, kb = threadIdx.x >> 5;      // a pair of adjacent columns, a block of 32 rows
     for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
         const int64_t rt = t / col_tiles;
         const int64_t c0 = (t - rt * col_tiles) * CTILE_COLS;
-        const int64_t r0 = win.begin + rt * TILE;
-        // 128 rows x 128 bytes = 512 chunks of 32 bytes over 128 threads: four loads in flight per thread
-        uint32_t val[4][8];
+        const int64_t r0 = win.begin + rt * TILE + kb * 32;
+        const int64_t col = c0 + 2 * cp;
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(x + r0 * N + col);
+        const int64_t pitch = N / 2;                             // 32-bit words per row
+        // pass 1: the block maximum of both columns, eight independent loads at a time; pass 2 reads the rows again
+        // (cache hits) four at a time.  Keeping the 32 values (and the 32 row addresses) in registers across the
+        // conversion would take about 170 registers; this way the kernel stays within 64.
+        uint32_t m = 0u;
+        const uint32_t* p1 = src;
+#pragma unroll 1
+        for (int g = 0; g < 4; ++g) {
+            uint32_t w[8];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int i = threadIdx.x + 128 * k;
-            ld_global_32B(x + (r0 + (i >> 2)) * N + c0 + (i & 3) * 16, val[k]);
+            for (int i = 0; i < 8; ++i) w[i] = __ldg(p1 + i * pitch);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m = absmax2(m, w[i]);
+            p1 += 8 * pitch;
         }
+        float inv_a, inv_b;
+        const uint32_t byte_a = scale_byte(bf16_lo(m), &inv_a);
+        const uint32_t byte_b = scale_byte(bf16_hi(m), &inv_b);
+        uint32_t out_a[8], out_b[8];
+        const uint32_t* p2 = src;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int i = threadIdx.x + 128 * k;
+        for (int i = 0; i < 8; ++i) {
+            uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) tile[(i >> 2) * CPITCH + (i & 3) * 8 + j] = val[k][j];
+            for (int j = 0; j < 4; ++j)       // (volatile: must stay a second load, not a reuse of pass 1's registers)
+                asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(w[j]) : "l"(p2 + j * pitch));
+            p2 += 4 * pitch;
+            out_a[i] = e4m3x4(bf16_lo(w[0]) * inv_a, bf16_lo(w[1]) * inv_a, bf16_lo(w[2]) * inv_a, bf16_lo(w[3]) * inv_a);
+            out_b[i] = e4m3x4(bf16_hi(w[0]) * inv_b, bf16_hi(w[1]) * inv_b, bf16_hi(w[2]) * inv_b, bf16_hi(w[3]) * inv_b);
         }
-        __syncthreads();
-        {
-            const int cp = threadIdx.x & 31, kb = threadIdx.x >> 5;      // a pair of adjacent columns, a block of 32 rows
-            uint32_t w[32];
-            uint32_t m = 0u;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                w[i] = tile[(kb * 32 + i) * CPITCH + cp];
-                m = absmax2(m, w[i]);
-            }
-            float inv_a, inv_b;
-            const uint32_t byte_a = scale_byte(bf16_lo(m), &inv_a);
-            const uint32_t byte_b = scale_byte(bf16_hi(m), &inv_b);
-            uint32_t out[8];
-            const int64_t col = c0 + 2 * cp;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                out[i] = e4m3x4(bf16_lo(w[4 * i]) * inv_a, bf16_lo(w[4 * i + 1]) * inv_a, bf16_lo(w[4 * i + 2]) * inv_a, bf16_lo(w[4 * i + 3]) * inv_a);
-            st_global_32B(qt + col * M + r0 + kb * 32, out);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                out[i] = e4m3x4(bf16_hi(w[4 * i]) * inv_b, bf16_hi(w[4 * i + 1]) * inv_b, bf16_hi(w[4 * i + 2]) * inv_b, bf16_hi(w[4 * i + 3]) * inv_b);
-            st_global_32B(qt + (col + 1) * M + r0 + kb * 32, out);
-            sct[scale_offset(col, (r0 >> 5) + kb, M >> 7)] = static_cast<uint8_t>(byte_a);
-            sct[scale_offset(col + 1, (r0 >> 5) + kb, M >> 7)] = static_cast<uint8_t>(byte_b);
-        }
-        __syncthreads();          // the tile is free for the next load
+        st_global_32B(qt + col * M + r0, out_a);
+        st_global_32B(qt + (col + 1) * M + r0, out_b);
+        sct[scale_offset(col, r0 >> 5, M >> 7)] = static_cast<uint8_t>(byte_a);
+        sct[scale_offset(col + 1, r0 >> 5, M >> 7)] = static_cast<uint8_t>(byte_b);
     }
 }
 
