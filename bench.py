@@ -780,7 +780,7 @@ def main():
                 "frac_of_sustained": kern["tflops"] / sustained_peak()[0], "peak_sustained": sustained_peak()[0],
                 "peak_sustained_source": f"{sustained_peak()[1]} cuBLAS bf16, back to back for seconds",
                 "gate_up_launch_alone": {"ms": kern_gu["ms"], "tflops": kern_gu["tflops"], "frac": kern_gu["tflops"] / peak_tf,
-                                         "note": "the gate/up + SwiGLU launch (mode 1) on the same rows: last round's dominant kernel"}}
+                                         "note": "the gate/up + SwiGLU launch (mode 1) on the same rows: the launch that dominated before the forward became one launch"}}
 
     # ---- the communication phases alone: dispatch (row pull) and combine (row push) over all scheduled rows,
     # every rank at once, CUDA events, max over ranks.  Bytes over NVLink = rows whose home is another rank.
