@@ -709,8 +709,9 @@ def main():
         kern["wgrad_down"] = time_wgrad_kernel(_C, sched, T, H, I, E_l, MB, args.steps, args.warmup, device)
         if not args.no_mxfp8:
             from mok import ops
-            qg, qu = (ops.mxfp8_quantize(w_, True, False) for w_ in (wrg, wru))
-            kern["mxfp8"] = time_dominant_kernel_mxfp8(_C, ops, sched, prob.x_d, qg, qu, T, H, I, E_l, MB, args.steps, args.warmup, device)
+            qg, qu, qd = (ops.mxfp8_quantize(w_, True, False) for w_ in (wrg, wru, wrd))
+            kern["mxfp8"] = time_dominant_kernel_mxfp8(_C, ops, sched, prob.x_d, qg, qu, T, H, I, E_l, MB, args.steps, args.warmup,
+                                                       device, qd=qd)
         if rank == 0:
             print(json.dumps({"kernel_only": True, **kern}), flush=True)
         dist.destroy_process_group()
@@ -966,10 +967,11 @@ def run_mxfp8_leg(prob, timed, args, _C, ops, sched, real_rows, peak_tf, trace_l
           "median_ms_per_step": statistics.median(per_step),
           "tflops_per_gpu": prob.flops() / (mx_ms / 1000.0) / 1e12, "fwd_ms": mx_f, "bwd_ms": mx_b,
           "note": "routed experts in block-scaled E4M3 (tcgen05 mxf8f6f4), shared expert BF16; inputs resident in HBM"}
-    qg, qu, _ = prob.quantise_weights()
-    mx["dominant_kernel"] = time_dominant_kernel_mxfp8(_C, ops, sched, prob.x_d, qg, qu, T, H, I, E_l, MB, 5, 2, device)
+    qg, qu, qd = prob.quantise_weights()
+    mx["dominant_kernel"] = time_dominant_kernel_mxfp8(_C, ops, sched, prob.x_d, qg, qu, T, H, I, E_l, MB, 5, 2, device, qd=qd)
+    mx["gate_up_launch_alone"] = time_dominant_kernel_mxfp8(_C, ops, sched, prob.x_d, qg, qu, T, H, I, E_l, MB, 5, 2, device)
     prob.q = None
-    del qg, qu
+    del qg, qu, qd
     torch.cuda.empty_cache()
     if rank == 0:
         lib = cublaslt_mxfp8_tflops(device)
@@ -1054,9 +1056,10 @@ def time_wgrad_kernel(_C, sched, T, H, I, E_l, MB, steps, warmup, device):
     return {"ms": ms, "flops_per_launch": flops, "tflops": flops / (ms / 1000.0) / 1e12}
 
 
-def time_dominant_kernel_mxfp8(_C, ops, sched, x, qg, qu, T, H, I, E_l, MB, steps, warmup, device):
-    """Times the routed MXFP8 gate|up grouped GEMM alone: block-scaled E4M3, both products in one launch, SwiGLU and
-    the quantisation of gate, up and hidden in its epilogue (the form the layer runs)."""
+def time_dominant_kernel_mxfp8(_C, ops, sched, x, qg, qu, T, H, I, E_l, MB, steps, warmup, device, qd=None):
+    """Times the routed MXFP8 forward GEMM alone, block-scaled E4M3: with `qd` (the down weights) the one persistent
+    launch the layer runs (mode 4: gate|up, SwiGLU and the quantisation of gate, up and hidden in the epilogue, then
+    the down projection of the same rows); without, its gate|up part (mode 3)."""
     tpe = sched.tokens_per_expert
     gob = torch.repeat_interleave(torch.arange(E_l, device=device, dtype=torch.int32), (tpe // 128).to(torch.int64))
     gob = torch.cat([gob, torch.full((MB // 128 - gob.numel(),), -1, dtype=torch.int32, device=device)])
@@ -1069,9 +1072,18 @@ def time_dominant_kernel_mxfp8(_C, ops, sched, x, qg, qu, T, H, I, E_l, MB, step
         outs += [torch.empty(MB, I, **u8), torch.empty(MB // 128, I // 128, 32, 16, **u8)]
     outs += [torch.empty(I, MB, **u8), torch.empty(I // 128, MB // 128, 32, 16, **u8)]      # hidden along tokens
 
+    y = torch.empty(MB, H, dtype=torch.bfloat16, device=device) if qd is not None else None
+    blk = torch.zeros(MB // 256, dtype=torch.int32, device=device)
+
     def launch():
-        _C.grouped_gemm_mxfp8(3, xq, xs, qg[0], qg[1], None, rows=MB, num_rows=sched.num_tokens, group_of_block=gob,
-                              G=E_l, N=I, K=H, B2=qu[0], B2_sc=qu[1], quantised_outputs=outs, t_rows=MB)
+        if qd is None:
+            _C.grouped_gemm_mxfp8(3, xq, xs, qg[0], qg[1], None, rows=MB, num_rows=sched.num_tokens, group_of_block=gob,
+                                  G=E_l, N=I, K=H, B2=qu[0], B2_sc=qu[1], quantised_outputs=outs, t_rows=MB)
+        else:
+            blk.zero_()
+            _C.grouped_gemm_mxfp8(4, xq, xs, qg[0], qg[1], y, rows=MB, num_rows=sched.num_tokens, group_of_block=gob,
+                                  G=E_l, N=I, K=H, B2=qu[0], B2_sc=qu[1], quantised_outputs=outs, t_rows=MB,
+                                  B3=qd[0], B3_sc=qd[1], N2=H, ldd=H, window_rows=8192, blk_done=blk)
     for _ in range(warmup):
         launch()
     torch.cuda.synchronize()
@@ -1083,9 +1095,10 @@ def time_dominant_kernel_mxfp8(_C, ops, sched, x, qg, qu, T, H, I, E_l, MB, step
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps
     real_rows = int((sched.peer_rank >= 0).sum().item())
-    flops = 4.0 * real_rows * H * I
-    return {"kernel": "grouped_gemm_mxfp8_kernel<gate|up + SwiGLU + quantise>", "ms": ms, "flops_per_launch": flops,
-            "tflops": flops / (ms / 1000.0) / 1e12}
+    flops = (4.0 if qd is None else 6.0) * real_rows * H * I
+    name = ("grouped_gemm_mxfp8_kernel<gate|up + SwiGLU + quantise>" if qd is None else
+            "grouped_gemm_mxfp8_kernel<MODE_FWD> (routed gate|up + SwiGLU + quantise + down, one persistent launch)")
+    return {"kernel": name, "ms": ms, "flops_per_launch": flops, "tflops": flops / (ms / 1000.0) / 1e12}
 
 
 if __name__ == "__main__":
