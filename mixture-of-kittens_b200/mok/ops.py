@@ -35,10 +35,17 @@ def _op(name: str, *, mutates_args=(), **kw):
     return deco
 
 
+# the three probes `_plain_eager` needs; a torch without them never takes the direct path
+_dispatch_depth = getattr(torch._C, "_len_torch_dispatch_stack", None)
+_function_depth = getattr(torch._C, "_len_torch_function_stack", None)
+_functorch_top = getattr(getattr(torch._C, "_functorch", None), "peek_interpreter_stack", None)
+_CAN_PROBE = None not in (_dispatch_depth, _function_depth, _functorch_top)
+
+
 def _plain_eager(args) -> bool:
-    if torch.compiler.is_compiling() or torch._C._len_torch_dispatch_stack() or torch._C._len_torch_function_stack():
+    if not _CAN_PROBE or torch.compiler.is_compiling() or _dispatch_depth() or _function_depth():
         return False
-    if torch._C._functorch.peek_interpreter_stack() is not None:
+    if _functorch_top() is not None:
         return False
     for a in args:
         if isinstance(a, torch.Tensor) and (type(a) is not torch.Tensor or a.requires_grad):
