@@ -11,7 +11,10 @@
  *   - all pointers are device pointers on the current CUDA device unless the
  *     name ends in `_host`; tensors are contiguous, row-major;
  *   - `stream` is a cudaStream_t passed as void*; work is enqueued, never
- *     synchronised: no entry point blocks the host;
+ *     synchronised: no entry point blocks the host.  The layer entry points also use two
+ *     streams of their own per device (the pulls, at high priority, and the token-wise MXFP8
+ *     copies, at low priority), forked from and joined back into `stream` with events inside the
+ *     call, so that to the caller everything is ordered on `stream` (and can be captured);
  *   - "peer pointer lists" (`*_ptrs_host`) are host arrays of `ep_size` device
  *     addresses, index = EP rank, as produced by a symmetric-memory rendezvous
  *     (mok/functional.py:224 of the reference);
