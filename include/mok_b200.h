@@ -14,7 +14,7 @@
  *     synchronised: no entry point blocks the host.  The layer entry points also use two
  *     streams of their own per device (the pulls, at high priority, and the token-wise MXFP8
  *     copies, at low priority), forked from and joined back into `stream` with events inside the
- *     call, so that to the caller everything is ordered on `stream` (and can be captured);
+ *     call, so that to the caller everything is ordered on `stream`;
  *   - "peer pointer lists" (`*_ptrs_host`) are host arrays of `ep_size` device
  *     addresses, index = EP rank, as produced by a symmetric-memory rendezvous
  *     (mok/functional.py:224 of the reference);
