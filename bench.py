@@ -1,6 +1,6 @@
 """Benchmark of the MoE layer hot path: build_schedule + forward + backward per step.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c4|c5|c2r|small]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c4|c5|c2r|small] [--graph]
                     [--trace FILE] [--comm-sms S] [--minibatch M] [--no-mxfp8] [--no-torch-baseline] [--kernel-only]
 
 For N > 1 launch under torch.distributed.run with one rank per GPU (RANK / LOCAL_RANK /
@@ -648,6 +648,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end legs (sweeps; the line then has no e2e key)")
     ap.add_argument("--no-torch-baseline", action="store_true",
                     help="skip the stock-PyTorch all-to-all + grouped_mm baseline (reported under \"torch_all_to_all\")")
+    ap.add_argument("--graph", action="store_true", help="1 GPU: also time the step replayed from a CUDA graph (always on for c1)")
     ap.add_argument("--no-share", action="store_true", help="skip the 1-GPU leg that runs one rank's EP=8 share of config 2")
     ap.add_argument("--trace", default="", help="write the launch timeline of one BF16 and one MXFP8 step of rank 0 to this file")
     ap.add_argument("--kernel-only", action="store_true", help="time only the dominant GEMM (profiler captures)")
@@ -811,6 +812,11 @@ def main():
             tb = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
         torch.cuda.empty_cache()
 
+    # ---- 1 GPU, small workloads: the same step replayed from a CUDA graph (the launch-bound regime)
+    graph_leg = None
+    if world == 1 and (args.graph or args.workload == "c1"):
+        graph_leg = run_graph_leg(prob, timed, args.steps, no_mxfp8=args.no_mxfp8)
+
     # ---- 1 GPU only: one rank's share of the EP=8 run of config 2 (32 local experts), the honest anchor for 1 -> 8 scaling
     share = None
     if world == 1 and args.workload == "c2" and not args.no_share:
@@ -868,6 +874,8 @@ def main():
             line["torch_all_to_all"] = tb
         if share is not None:
             line["ep8_share_1gpu"] = share
+        if graph_leg is not None:
+            line["cuda_graph"] = graph_leg
         if world == 1 and not args.no_cpu_baseline:
             cores = host_threads()
             Ts, Es, dt = cpu_oracle_sample(H, I, K)
@@ -985,6 +993,33 @@ def run_mxfp8_leg(prob, timed, args, _C, ops, sched, real_rows, peak_tf, trace_l
         else:
             mx["cublaslt_mxfp8_tflops"] = {"unavailable": lib}
     return mx
+
+
+def run_graph_leg(prob, timed, steps, no_mxfp8=False):
+    """The step (build_schedule + forward + backward through mok.functional) captured once in a CUDA graph and replayed:
+    the library never synchronises the host, joins its side streams inside every call and takes its outputs from
+    torch's allocator, so the step is captured as it is.  Host time per step drops to one graph launch."""
+    out = {}
+    for label, fn in (("bf16", prob.step), ("mxfp8", prob.step_mx)):
+        if label == "mxfp8" and no_mxfp8:
+            continue
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            keep = fn()
+        for _ in range(3):
+            graph.replay()
+        ms = statistics.median(timed(graph.replay, steps)[1])
+        out[label] = {"ms_per_step": ms, "tokens_per_s": prob.T / (ms / 1000.0)}
+        del keep, graph
+    out["note"] = "one graph launch per step; eager figures are in ms_per_step / mxfp8.ms_per_step"
+    return out
 
 
 def time_dominant_kernel(_C, sched, x, wrg, wru, T, H, I, K, E_l, MB, steps, warmup, device, wrd=None):
